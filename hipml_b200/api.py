@@ -1,0 +1,127 @@
+"""Thin Python view of the C-ABI launchers, for tests and the bench.
+
+Every function takes CUDA ``torch`` tensors only for their device pointers and the
+current stream; the work is done by libhipml_cuda.so. Argument names, order and units
+follow the reference's launchers (see include/hipml_cuda.h for the file:line of each).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def version() -> str:
+    return _lib.load().hipml_version().decode()
+
+
+def kv_encode(step, k_row, v_row, k_cache, v_cache, n_kv, head_dim, stride, dtype=0):
+    """Launcher::kv_encode_ptr_on: quantise one token's K/V rows at step[0]."""
+    _lib.check("kv_encode", _lib.load().hipml_kv_encode(
+        _stream(), _p(step), dtype, _p(k_row), _p(v_row), _p(k_cache), _p(v_cache), n_kv,
+        head_dim, stride))
+
+
+def kv_encode_bulk(k_f32, v_f32, k_cache, v_cache, n_kv, head_dim, stride, start, src0, rows,
+                   dtype=0):
+    """Launcher::kv_encode_bulk: rows src0+r of the f32 tile land at position start+r."""
+    _lib.check("kv_encode_bulk", _lib.load().hipml_kv_encode_bulk(
+        _stream(), dtype, _p(k_f32), _p(v_f32), _p(k_cache), _p(v_cache), n_kv, head_dim, stride,
+        start, src0, rows))
+
+
+def kv_encode_rows(k_f32, v_f32, k_cache, v_cache, n_kv, head_dim, stride, pos, slot_bytes, slots,
+                   dtype=0):
+    """Launcher::kv_encode_batch: slot s appends its row at pos[2s] in the cache at s*slot_bytes."""
+    _lib.check("kv_encode_batch", _lib.load().hipml_kv_encode_rows(
+        _stream(), dtype, _p(k_f32), _p(v_f32), _p(k_cache), _p(v_cache), n_kv, head_dim, stride,
+        _p(pos), slot_bytes, slots))
+
+
+def kv_append_f32(step, k_cache, v_cache, k_row, v_row, width):
+    _lib.check("kv_append_f32", _lib.load().hipml_kv_append_f32(
+        _stream(), _p(step), _p(k_cache), _p(v_cache), _p(k_row), _p(v_row), width))
+
+
+def kv_append_chunk_f32(k_cache, v_cache, k, v, pos0, width, tokens):
+    _lib.check("kv_append_chunk_f32", _lib.load().hipml_kv_append_chunk_f32(
+        _stream(), _p(k_cache), _p(v_cache), _p(k), _p(v), pos0, width, tokens))
+
+
+def attn_decode_kv(step, q, k, v, part_acc, part_ml, out, n_heads, n_kv, head_dim, stride, scale,
+                   splits, selector=0, k_off=0, v_off=0):
+    """launch_kv::launch_ptrs: split-K decode over the q8 cache + reduce."""
+    _lib.check("attn_decode_kv", _lib.load().hipml_attn_decode_kv(
+        _stream(), _p(step), selector, _p(q), _p(k), _p(v), _p(part_acc), _p(part_ml), _p(out),
+        n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
+
+
+def attn_decode_rows(pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads, n_kv, head_dim,
+                     stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot, q_slot, slots,
+                     dtype=0):
+    """Launcher::attn_decode_rows_ptr: multi-slot decode, runs fixed in cache positions."""
+    _lib.check("attn_decode_rows", _lib.load().hipml_attn_decode_rows(
+        _stream(), dtype, _p(pos), _p(q), _p(k_cache), _p(v_cache), _p(part_acc), _p(part_ml),
+        _p(out), n_heads, n_kv, head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot,
+        q_slot, slots))
+
+
+def attn_decode_batch(pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads, n_kv, head_dim,
+                      stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot, q_slot, slots,
+                      live_seq, dtype=0):
+    """Launcher::attn_decode_batch."""
+    _lib.check("attn_decode_batch", _lib.load().hipml_attn_decode_batch(
+        _stream(), dtype, _p(pos), _p(q), _p(k_cache), _p(v_cache), _p(part_acc), _p(part_ml),
+        _p(out), n_heads, n_kv, head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot,
+        q_slot, slots, live_seq))
+
+
+def attn_chunk_workspace_bytes(n_kv, head_dim, pos0, tokens) -> int:
+    return int(_lib.load().hipml_attn_chunk_workspace_bytes(n_kv, head_dim, pos0, tokens))
+
+
+def attn_chunk(q, k_cache, v_cache, out, n_heads, n_kv, head_dim, pos0, tokens, kv_dtype=0,
+               stride=0, part_acc=None, part_ml=None, splits=1, mode=0, workspace=None):
+    """AttnLayer::chunk_attention / chunk_attention_q8 / chunk_attention_q8_split."""
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    _lib.check("chunk_attention", _lib.load().hipml_attn_chunk(
+        _stream(), _p(q), _p(k_cache), _p(v_cache), _p(out), n_heads, n_kv, head_dim, pos0,
+        tokens, kv_dtype, stride, _p(part_acc), _p(part_ml), splits, mode, _p(workspace),
+        ws_bytes))
+
+
+def check_device_status() -> int:
+    """Synchronises the current stream; raises if a kernel's bounded wait ran out."""
+    st = C.c_int(0)
+    _lib.check("device status", _lib.load().hipml_check_device_status(_stream(), C.byref(st)))
+    return st.value
+
+
+# ---- split policies (host arithmetic of the reference's engine) -------------------------
+
+def decode_splits(seq: int) -> int:
+    """DeepKv::splits for the warp-kernel family (crates/hipml-model/src/gpu/deep_kv.rs:102-110)."""
+    fine = min(max(seq // 8, 1), 128)
+    coarse = min(max(seq // 64, 1), 256)
+    return max(fine, coarse)
+
+
+def batch_splits(stride: int, slots: int) -> int:
+    """attn_splits (crates/hipml-model/src/gpu/batch/kv.rs:39-42)."""
+    per = 64 * max((slots + 3) // 4, 1)
+    return min(max((stride + per - 1) // per, 1), 256)
+
+
+def prefill_splits(pos0: int, configured: int = 8, split_min: int = 8192) -> int:
+    """split_count (crates/hipml-model/src/gpu/attn_tile.rs:138-151)."""
+    return configured if pos0 >= split_min else 1

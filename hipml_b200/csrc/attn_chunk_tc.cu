@@ -1,0 +1,731 @@
+// Causal chunk (prefill) attention on the 5th-generation tensor cores:
+// tcgen05.mma with TMEM accumulators, operand tiles brought in by TMA.
+//
+// CPU definition: crates/hipml-core/src/attention.rs:56-102 applied per query row with
+// seq = pos0 + t + 1. Kernels replaced: crates/hipml-kernels/kernels/attn_chunk_wmma.hip:187-399
+// (one pass) and attn_chunk_full.hip:134-336 (key-split partials).
+//
+// Two launches per call.
+//
+// 1. attn_chunk_stage: converts the visible cache rows (f32 or q8_0) into the operand image
+//    the tensor cores read: K as f16 [kv head][key][256] and V transposed as f16
+//    [kv head][256][key], each as a high plane and a low plane (x = hi + lo, |lo| <= ulp(hi)/2).
+//    A dequantised q8 value (f16 scale * int8 code) has at most 18 significant bits, so
+//    hi + lo holds it exactly. Keys are padded with zeros to a multiple of 128. This pass
+//    moves ~5 bytes per cache element against ~1.5e5 tensor FLOP per element of the chunk's
+//    attention, i.e. about 1.5% of the call.
+//
+// 2. attn_chunk_tc: one CTA per (query tile, KV head[, key slice]). A query tile stacks the
+//    GQA group along M: row r = query (r / group) of the tile, head (r % group) of the
+//    group, 128 rows = 21 queries x 6 heads on the shipped shape, so one staged K/V tile
+//    feeds all six heads. Per 128-key step:
+//        S = Q K^T           tcgen05.mma  M=128 N=128 K=256, Q (A) and K (B) from shared memory
+//        P = exp2(S - m)     four softmax warps, one TMEM lane (row) per thread, P written
+//                            back over S in TMEM as f16 high/low pairs
+//        O += P V            tcgen05.mma  M=128 N=2x128 K=128, P (A) from TMEM, V^T (B) from
+//                            shared memory
+//    Q stays resident in shared memory (128 KB as hi/lo f16, 128B-swizzled K-major); K and
+//    V^T chunks of 32 KB (hi + lo tile of 128 rows x 64 elements) stream through a 3-stage
+//    TMA ring. TMEM: O 256 columns + two S/P buffers of 128 columns, so QK^T of step i+1
+//    overlaps the softmax of step i. Precision mode 0 issues three MMAs per product
+//    (hi*hi + lo*hi + hi*lo) into the same accumulator, which brings the result within
+//    ~1e-5 of the f32 definition; mode 1 issues hi*hi only (the reference kernel's own
+//    single-pass f16 precision).
+//
+// Roles: warps 0-3 softmax/epilogue (thread = row), warp 4 lane 0 TMA producer, warp 5
+// lane 0 MMA issuer. Every mbarrier wait is bounded: when a wait runs out the thread
+// records a code in the device status word, raises a CTA-wide abort flag that every other
+// wait observes, and the CTA falls through to its teardown (TMEM is always released).
+#include <cuda.h>
+
+#include "params.cuh"
+
+namespace hipml {
+
+struct ChunkTcParams {
+    const float *q;
+    float *out;        // [tokens][n_heads*256], splits < 2
+    float *part_acc;   // splits >= 2
+    float *part_ml;
+    int *status;
+    int n_heads, n_kv, group;
+    int pos0, tokens;
+    int lpad;          // staged keys per head (multiple of 128)
+    int qtile;         // queries per CTA = 128 / group
+    float scale_log2;
+    int splits, qslots;
+    int single_pass;   // 1: hi*hi only
+};
+
+namespace {
+
+constexpr int kD = 256;
+constexpr int kKeyTile = 128;
+constexpr int kStages = 3;
+constexpr int kTileBytes = 128 * 128;            // 128 rows x 64 f16, swizzled
+constexpr int kStageBytes = 2 * kTileBytes;      // hi + lo
+constexpr int kQBytes = 8 * kTileBytes;          // 4 dim-chunks x (hi, lo)
+constexpr int kTcThreads = 192;
+constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr unsigned kSpinLimit = 1u << 22;        // polls per wait before giving up
+constexpr float kRescaleThreshold = 8.0f;        // log2 units: P stays <= 256
+
+// ------------------------------------------------------------------ PTX helpers
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false when the wait ran out (status word set, abort raised) or
+// another thread of the CTA aborted.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag,
+                                          int *status, int code) {
+    for (unsigned i = 0; i < kSpinLimit; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255) == 255 && *abort_flag) return false;
+        if (i > 4096) __nanosleep(64);
+    }
+    atomicCAS(status, 0, code);
+    *abort_flag = 1;
+    __threadfence_block();
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y,
+                                            unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+        "{%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned smem_dst, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(unsigned d, uint64_t a, uint64_t b, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(unsigned d, unsigned a, uint64_t b, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
+        "%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
+        "%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile of 128-byte rows with the 128-byte
+// swizzle: 8-row groups are 1024 B apart (stride byte offset), the leading byte offset is
+// unused for swizzled K-major layouts, descriptor version 1 (Blackwell), layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(unsigned addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffff) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = 128.
+constexpr unsigned kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+// Byte offset of element (row, col) of a [128][64] f16 tile in the swizzled image.
+__device__ __forceinline__ int sw128_offset(int row, int col) {
+    return row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1));
+}
+
+__device__ __forceinline__ unsigned pack2(__half a, __half b) {
+    const __half2 h = __halves2half2(a, b);
+    return *reinterpret_cast<const unsigned *>(&h);
+}
+
+// ------------------------------------------------------------------ staging
+
+struct StageParams {
+    const void *k;
+    const void *v;
+    __half *k_hi, *k_lo;    // [n_kv][lpad][256]
+    __half *vt_hi, *vt_lo;  // [n_kv][256][lpad]
+    int n_kv, n_keys, lpad, kv_dtype, stride;
+};
+
+__device__ __forceinline__ void split_half(float x, __half &hi, __half &lo) {
+    hi = __float2half_rn(x);
+    lo = __float2half_rn(x - __half2float(hi));
+}
+
+// Dequantised (or copied) values of 8 consecutive dims of one cache row; zeros past n_keys.
+__device__ __forceinline__ void stage_fetch(const StageParams &p, const void *cache, int kvh,
+                                            int key, int d0, float (&x)[8]) {
+    if (key >= p.n_keys) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] = 0.0f;
+        return;
+    }
+    if (p.kv_dtype == 0) {
+        const float4 *r = reinterpret_cast<const float4 *>(
+            (const float *)cache + (size_t)key * (p.n_kv * kD) + kvh * kD + d0);
+        const float4 a = r[0], b = r[1];
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else {
+        const int blk = d0 >> 5, sub = (d0 >> 3) & 3;
+        const unsigned char *b = (const unsigned char *)cache +
+                                 q8_row_offset(kvh, p.stride, key, kD) + (size_t)blk * kQ8BlockBytes;
+        const float d = half_bits_to_float(*(const unsigned short *)b);
+        const unsigned short *c = (const unsigned short *)(b + 2 + sub * 8);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const unsigned short w = c[j];
+            x[2 * j] = d * (float)(signed char)(w & 0xff);
+            x[2 * j + 1] = d * (float)(signed char)(w >> 8);
+        }
+    }
+}
+
+__device__ __forceinline__ void stage_store8(__half *hi, __half *lo, size_t at, const float (&x)[8]) {
+    __half h[8], l[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) split_half(x[j], h[j], l[j]);
+    *reinterpret_cast<uint4 *>(hi + at) =
+        make_uint4(pack2(h[0], h[1]), pack2(h[2], h[3]), pack2(h[4], h[5]), pack2(h[6], h[7]));
+    *reinterpret_cast<uint4 *>(lo + at) =
+        make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
+}
+
+// grid (lpad/64, n_kv), block 256: one CTA stages 64 keys of one KV head.
+__global__ void __launch_bounds__(256) attn_chunk_stage(StageParams p) {
+    __shared__ float vs[64][129];
+    const int kvh = blockIdx.y, key0 = blockIdx.x * 64;
+    const int tid = threadIdx.x;
+    // K: row-major copy. Thread -> dims [8*(tid%32), +8) of keys tid/32 + 8*i.
+    for (int i = 0; i < 8; i++) {
+        const int key = key0 + (tid >> 5) + 8 * i, d0 = (tid & 31) * 8;
+        float x[8];
+        stage_fetch(p, p.k, kvh, key, d0, x);
+        stage_store8(p.k_hi, p.k_lo, ((size_t)kvh * p.lpad + key) * kD + d0, x);
+    }
+    // V: transposed through shared memory, 128 dims at a time.
+    for (int dh = 0; dh < 2; dh++) {
+        for (int i = 0; i < 4; i++) {
+            const int kl = (tid >> 4) + 16 * i, d0 = (tid & 15) * 8;
+            float x[8];
+            stage_fetch(p, p.v, kvh, key0 + kl, dh * 128 + d0, x);
+#pragma unroll
+            for (int j = 0; j < 8; j++) vs[kl][d0 + j] = x[j];
+        }
+        __syncthreads();
+        const int d = tid & 127, kb0 = (tid >> 7) * 32;
+        for (int kb = kb0; kb < kb0 + 32; kb += 8) {
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = vs[kb + j][d];
+            stage_store8(p.vt_hi, p.vt_lo, ((size_t)kvh * kD + dh * 128 + d) * p.lpad + key0 + kb, x);
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------ main kernel
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constant__ CUtensorMap map_k_lo,
+              const __grid_constant__ CUtensorMap map_vt_hi,
+              const __grid_constant__ CUtensorMap map_vt_lo, ChunkTcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem =
+        reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
+    unsigned char *q_smem = smem;                       // 8 tiles: hi chunks 0..3, lo chunks 0..3
+    unsigned char *ring = smem + kQBytes;               // kStages x (hi tile, lo tile)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kStages * kStageBytes);
+    // bars: full[3], empty[3], s_ready[2], p_ready[2], o_done
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 12);
+    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 13);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+    const int t0 = qt * p.qtile;
+    const int nq = min(p.qtile, p.tokens - t0);  // live queries of this tile (>= 1)
+    const int rows_live = nq * p.group;
+
+    const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 3);
+    const unsigned bar_s = smem_u32(bars + 6), bar_p = smem_u32(bars + 8), bar_o = smem_u32(bars + 10);
+
+    // Key tiles this CTA walks: rows of the tile see cache rows < pos0 + t0 + nq.
+    const int n_tiles_all = (p.pos0 + t0 + nq + kKeyTile - 1) / kKeyTile;
+    const int nsp = p.splits < 2 ? 1 : p.splits;
+    const int kt_lo = (int)((long long)n_tiles_all * sp / nsp);
+    const int kt_hi = (int)((long long)n_tiles_all * (sp + 1) / nsp);
+    const int n_tiles = kt_hi - kt_lo;
+
+    if (tid == 0) {
+        for (int i = 0; i < kStages; i++) {
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, 1);
+        }
+        mbar_init(bar_s, 1);
+        mbar_init(bar_s + 8, 1);
+        mbar_init(bar_p, 128);
+        mbar_init(bar_p + 8, 128);
+        mbar_init(bar_o, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tmem_alloc(smem_u32(tmem_slot), 512);
+    }
+
+    // Q tile: f32 -> scaled hi/lo f16 in the swizzled K-major image. Row r = query r/group,
+    // head r%group; rows past the live queries are zero.
+    for (int i = tid; i < 128 * (kD / 8); i += kTcThreads) {
+        const int r = i >> 5, seg = i & 31;  // 8 dims per item
+        float x[8];
+        if (r < rows_live) {
+            const int qi = r / p.group, hh = r - qi * p.group;
+            const float4 *src = reinterpret_cast<const float4 *>(
+                p.q + ((size_t)(t0 + qi) * p.n_heads + kvh * p.group + hh) * kD + seg * 8);
+            const float4 a = src[0], b = src[1];
+            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+            x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = 0.0f;
+        }
+        __half h[8], l[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) split_half(x[j] * p.scale_log2, h[j], l[j]);
+        const int chunk = seg >> 3, col = (seg & 7) * 8;
+        const int off = sw128_offset(r, col);
+        *reinterpret_cast<uint4 *>(q_smem + chunk * kTileBytes + off) =
+            make_uint4(pack2(h[0], h[1]), pack2(h[2], h[3]), pack2(h[4], h[5]), pack2(h[6], h[7]));
+        *reinterpret_cast<uint4 *>(q_smem + (4 + chunk) * kTileBytes + off) =
+            make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
+    }
+    // Make the generic-proxy writes of Q visible to the tensor-core (async) proxy.
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = *tmem_slot;
+    const unsigned tmem_o = tmem;                 // columns [0,256)
+    const unsigned tmem_s[2] = {tmem + 256, tmem + 384};
+    const int terms = p.single_pass ? 1 : 3;
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0 && n_tiles > 0) {
+            unsigned n = 0;  // chunks issued
+            bool ok = true;
+            auto issue = [&](const CUtensorMap *hi, const CUtensorMap *lo, int x, int y) {
+                const unsigned stage = n % kStages, phase = (n / kStages) & 1;
+                ok = ok && mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1);
+                if (!ok) return;
+                const unsigned dst = smem_u32(ring + stage * kStageBytes);
+                mbar_arrive_expect_tx(bar_full + 8 * stage, p.single_pass ? kTileBytes : kStageBytes);
+                tma_load_2d(dst, hi, x, y, bar_full + 8 * stage);
+                if (!p.single_pass) tma_load_2d(dst + kTileBytes, lo, x, y, bar_full + 8 * stage);
+                n++;
+            };
+            auto load_k = [&](int kt) {
+                for (int c = 0; c < 4 && ok; c++)
+                    issue(&map_k_hi, &map_k_lo, c * 64, kvh * p.lpad + kt * kKeyTile);
+            };
+            auto load_v = [&](int kt) {
+                for (int kc = 0; kc < 2 && ok; kc++)
+                    for (int dh = 0; dh < 2 && ok; dh++)
+                        issue(&map_vt_hi, &map_vt_lo, kt * kKeyTile + kc * 64, kvh * kD + dh * 128);
+            };
+            load_k(kt_lo);
+            for (int kt = kt_lo; kt < kt_hi && ok; kt++) {
+                if (kt + 1 < kt_hi) load_k(kt + 1);
+                load_v(kt);
+            }
+            if (!ok) {
+                // Let copies already in flight land before the CTA's shared memory is released.
+                for (unsigned i = (n > kStages ? n - kStages : 0); i < n; i++)
+                    for (unsigned spin = 0; spin < kSpinLimit; spin++)
+                        if (mbar_try_wait(bar_full + 8 * (i % kStages), (i / kStages) & 1)) break;
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0 && n_tiles > 0) {
+            unsigned n = 0;  // chunks consumed
+            bool ok = true;
+            const unsigned q_addr = smem_u32(q_smem);
+            auto qk = [&](int i) {  // i = tile index relative to kt_lo
+                const unsigned d = tmem_s[i & 1];
+                for (int c = 0; c < 4 && ok; c++) {
+                    const unsigned stage = n % kStages, phase = (n / kStages) & 1;
+                    ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const unsigned b_hi = smem_u32(ring + stage * kStageBytes), b_lo = b_hi + kTileBytes;
+                    const unsigned a_hi = q_addr + c * kTileBytes, a_lo = a_hi + 4 * kTileBytes;
+                    for (int term = 0; term < terms; term++) {
+                        const unsigned a = term == 1 ? a_lo : a_hi;
+                        const unsigned b = term == 2 ? b_lo : b_hi;
+#pragma unroll
+                        for (int k16 = 0; k16 < 4; k16++)
+                            tc_mma_ss(d, smem_desc_sw128(a + k16 * 32), smem_desc_sw128(b + k16 * 32),
+                                      kIdesc, (c | term | k16) != 0);
+                    }
+                    tc_commit(bar_empty + 8 * stage);
+                    n++;
+                }
+                if (ok) tc_commit(bar_s + 8 * (i & 1));
+            };
+            auto pv = [&](int i) {
+                const unsigned a_base = tmem_s[i & 1];
+                for (int kc = 0; kc < 2 && ok; kc++)
+                    for (int dh = 0; dh < 2 && ok; dh++) {
+                        const unsigned stage = n % kStages, phase = (n / kStages) & 1;
+                        ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 3);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const unsigned b_hi = smem_u32(ring + stage * kStageBytes), b_lo = b_hi + kTileBytes;
+                        const unsigned d = tmem_o + dh * 128;
+                        for (int term = 0; term < terms; term++) {
+                            const unsigned b = term == 2 ? b_lo : b_hi;
+#pragma unroll
+                            for (int k16 = 0; k16 < 4; k16++) {
+                                // P of keys [16*(4kc+k16), +16): hi pairs in 8 columns, lo in the next 8
+                                const unsigned a = a_base + (kc * 4 + k16) * 16 + (term == 1 ? 8 : 0);
+                                tc_mma_ts(d, a, smem_desc_sw128(b + k16 * 32), kIdesc,
+                                          (i | kc | term | k16) != 0);
+                            }
+                        }
+                        tc_commit(bar_empty + 8 * stage);
+                        n++;
+                    }
+                if (ok) tc_commit(bar_o);
+            };
+            qk(0);
+            for (int i = 0; i < n_tiles && ok; i++) {
+                if (i + 1 < n_tiles) qk(i + 1);
+                if (!ok) break;
+                ok = mbar_wait(bar_p + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 4);
+                if (!ok) break;
+                tc_fence_after();
+                pv(i);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax + epilogue
+        const int r = tid;                                  // row = TMEM lane
+        const unsigned lane_addr = (unsigned)(warp * 32) << 16;
+        const int qi = min(r / p.group, nq - 1);            // dead rows shadow a live query
+        const int kmax = p.pos0 + t0 + qi;                  // last visible cache row
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        unsigned v[32];
+        for (int i = 0; i < n_tiles && ok; i++) {
+            const int key0 = (kt_lo + i) * kKeyTile;
+            const unsigned s_addr = tmem_s[i & 1] + lane_addr;
+            ok = mbar_wait(bar_s + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 5);
+            if (!ok) break;
+            tc_fence_after();
+            // pass 1: row maximum over the visible keys
+            float m_tile = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                tmem_ld32(s_addr + 32 * j, v);
+#pragma unroll
+                for (int e = 0; e < 32; e++)
+                    if (key0 + 32 * j + e <= kmax) m_tile = fmaxf(m_tile, __uint_as_float(v[e]));
+            }
+            const float m_new = fmaxf(m_used, m_tile);
+            // Rescale O only when the maximum moved by more than the threshold (P <= 2^8
+            // otherwise); the decision is per warp because the TMEM accesses are collective.
+            const bool want = (i > 0) && (m_new > m_used + kRescaleThreshold ||
+                                          (m_used == -INFINITY && m_new > -INFINITY));
+            if (i == 0) m_used = m_new;
+            if (__any_sync(0xffffffffu, want)) {
+                ok = mbar_wait(bar_o, (i - 1) & 1, abort_flag, p.status, 6);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                tc_fence_after();
+                const float corr = (m_used == -INFINITY) ? 0.0f : exp2f(m_used - m_new);
+#pragma unroll 1
+                for (int j = 0; j < 8; j++) {
+                    tmem_ld32(tmem_o + lane_addr + 32 * j, v);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
+                    tmem_st32(tmem_o + lane_addr + 32 * j, v);
+                }
+                tmem_wait_st();
+                l *= corr;
+                m_used = m_new;
+            }
+            // pass 2: P = exp2(S - m), written over S as f16 hi/lo pairs per 16-key step
+#pragma unroll 1
+            for (int j = 0; j < 4; j++) {
+                tmem_ld32(s_addr + 32 * j, v);
+                unsigned o[32];
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const int ka = half * 16 + 2 * e;
+                        const bool va = key0 + 32 * j + ka <= kmax, vb = key0 + 32 * j + ka + 1 <= kmax;
+                        const float pa = va ? exp2f(__uint_as_float(v[ka]) - m_used) : 0.0f;
+                        const float pb = vb ? exp2f(__uint_as_float(v[ka + 1]) - m_used) : 0.0f;
+                        l += pa + pb;
+                        __half ha, la, hb, lb;
+                        split_half(pa, ha, la);
+                        split_half(pb, hb, lb);
+                        o[half * 16 + e] = pack2(ha, hb);
+                        o[half * 16 + 8 + e] = pack2(la, lb);
+                    }
+                }
+                tmem_st32(s_addr + 32 * j, o);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p + 8 * (i & 1));
+        }
+        // epilogue: O / l (or the raw partial)
+        if (ok && n_tiles > 0) {
+            ok = mbar_wait(bar_o, (n_tiles - 1) & 1, abort_flag, p.status, 7);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        const bool live = r < rows_live;
+        const int rq = r / p.group, rh = r - rq * p.group;
+        const int h = kvh * p.group + rh;
+        if (ok) {
+            tc_fence_after();
+            if (p.splits < 2) {
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                float *dst = p.out + ((size_t)(t0 + rq) * p.n_heads + h) * kD;
+#pragma unroll 1
+                for (int j = 0; j < 8; j++) {
+                    if (n_tiles > 0) tmem_ld32(tmem_o + lane_addr + 32 * j, v);
+                    if (live) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4) {
+                            float4 w;
+                            w.x = n_tiles > 0 ? __uint_as_float(v[e]) * inv : 0.0f;
+                            w.y = n_tiles > 0 ? __uint_as_float(v[e + 1]) * inv : 0.0f;
+                            w.z = n_tiles > 0 ? __uint_as_float(v[e + 2]) * inv : 0.0f;
+                            w.w = n_tiles > 0 ? __uint_as_float(v[e + 3]) * inv : 0.0f;
+                            *reinterpret_cast<float4 *>(dst + 32 * j + e) = w;
+                        }
+                    }
+                }
+            } else {
+                const size_t slot = ((size_t)sp * p.qslots + (t0 + rq)) * p.n_heads + h;
+                float *dst = p.part_acc + slot * kD;
+#pragma unroll 1
+                for (int j = 0; j < 8; j++) {
+                    if (n_tiles > 0) tmem_ld32(tmem_o + lane_addr + 32 * j, v);
+                    if (live) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4) {
+                            float4 w;
+                            w.x = n_tiles > 0 ? __uint_as_float(v[e]) : 0.0f;
+                            w.y = n_tiles > 0 ? __uint_as_float(v[e + 1]) : 0.0f;
+                            w.z = n_tiles > 0 ? __uint_as_float(v[e + 2]) : 0.0f;
+                            w.w = n_tiles > 0 ? __uint_as_float(v[e + 3]) : 0.0f;
+                            *reinterpret_cast<float4 *>(dst + 32 * j + e) = w;
+                        }
+                    }
+                }
+                if (live) {
+                    p.part_ml[slot * 2] = m_used;
+                    p.part_ml[slot * 2 + 1] = l;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+                cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2D f16 tensor [rows][cols] (cols contiguous), box 128 rows x 64 cols, 128-byte swizzle.
+int make_map(CUtensorMap *map, void *base, uint64_t cols, uint64_t rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(HIPML_ERR_INVALID_ARGUMENT, "cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "cuTensorMapEncodeTiled failed: %d", (int)r);
+    return 0;
+}
+
+}  // namespace
+
+size_t chunk_tc_workspace_bytes(int n_kv, int n_keys) {
+    const size_t lpad = ((size_t)n_keys + kKeyTile - 1) / kKeyTile * kKeyTile;
+    return 4 * (size_t)n_kv * lpad * kD * sizeof(__half);
+}
+
+// Stages the cache and launches the tensor-core kernel. Shapes are validated by the caller.
+int launch_chunk_tc(cudaStream_t stream, const float *q, const void *k_cache, const void *v_cache,
+                    float *out, float *part_acc, float *part_ml, int n_heads, int n_kv, int pos0,
+                    int tokens, int kv_dtype, int stride, int splits, int single_pass,
+                    void *workspace, int *status) {
+    const int n_keys = pos0 + tokens;
+    const int lpad = (n_keys + kKeyTile - 1) / kKeyTile * kKeyTile;
+    const size_t plane = (size_t)n_kv * lpad * kD;
+    __half *ws = reinterpret_cast<__half *>(workspace);
+
+    StageParams sp;
+    sp.k = k_cache;
+    sp.v = v_cache;
+    sp.k_hi = ws;
+    sp.k_lo = ws + plane;
+    sp.vt_hi = ws + 2 * plane;
+    sp.vt_lo = ws + 3 * plane;
+    sp.n_kv = n_kv;
+    sp.n_keys = n_keys;
+    sp.lpad = lpad;
+    sp.kv_dtype = kv_dtype;
+    sp.stride = stride;
+    attn_chunk_stage<<<dim3(lpad / 64, n_kv), 256, 0, stream>>>(sp);
+    int rc = launch_status();
+    if (rc) return rc;
+
+    CUtensorMap mk_hi, mk_lo, mv_hi, mv_lo;
+    if ((rc = make_map(&mk_hi, sp.k_hi, kD, (uint64_t)n_kv * lpad))) return rc;
+    if ((rc = make_map(&mk_lo, sp.k_lo, kD, (uint64_t)n_kv * lpad))) return rc;
+    if ((rc = make_map(&mv_hi, sp.vt_hi, lpad, (uint64_t)n_kv * kD))) return rc;
+    if ((rc = make_map(&mv_lo, sp.vt_lo, lpad, (uint64_t)n_kv * kD))) return rc;
+
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+
+    ChunkTcParams p;
+    p.q = q;
+    p.out = out;
+    p.part_acc = part_acc;
+    p.part_ml = part_ml;
+    p.status = status;
+    p.n_heads = n_heads;
+    p.n_kv = n_kv;
+    p.group = n_heads / n_kv;
+    p.pos0 = pos0;
+    p.tokens = tokens;
+    p.lpad = lpad;
+    p.qtile = 128 / p.group;
+    p.scale_log2 = (1.0f / sqrtf((float)kD)) * 1.4426950408889634f;
+    p.splits = splits;
+    p.qslots = (tokens + 31) / 32 * 32;
+    p.single_pass = single_pass;
+    const int nsp = splits < 2 ? 1 : splits;
+    dim3 grid((tokens + p.qtile - 1) / p.qtile, n_kv, nsp);
+    attn_chunk_tc<<<grid, kTcThreads, kSmemBytes, stream>>>(mk_hi, mk_lo, mv_hi, mv_lo, p);
+    return launch_status();
+}
+
+}  // namespace hipml

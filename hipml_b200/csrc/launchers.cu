@@ -1,0 +1,311 @@
+// Section B of the C ABI: the attention launchers. Each function validates its
+// arguments with the reference launcher's own rules and messages, then launches on the
+// caller's stream. Reference launch code: crates/hipml-kernels/src/launch_kv.rs:110-280,
+// crates/hipml-kernels/src/launch/device/graph_launch.rs:878-1028,
+// crates/hipml-kernels/src/launch/device/batch_launch.rs:22-316,
+// crates/hipml-kernels/src/attn_gpu/imp/attn_chunk_kv.rs:129-305.
+#include "params.cuh"
+
+using namespace hipml;
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+int check_encode(int dtype, int n_kv, int head_dim, int stride) {
+    if (dtype == 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 1 (q4_0) is not built in this library");
+    if (dtype != 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", dtype);
+    if (n_kv <= 0 || stride <= 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "n_kv %d / stride %d must be positive", n_kv, stride);
+    if (head_dim % 32 != 0 || head_dim < 32 || head_dim > 256)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "head_dim %d: must be 32..=256, multiple of 32",
+                    head_dim);
+    return 0;
+}
+
+int check_heads(int n_heads, int n_kv, int head_dim) {
+    if (n_kv <= 0 || n_heads % n_kv != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "n_heads %d is not a multiple of n_kv %d", n_heads,
+                    n_kv);
+    const int group = n_heads / n_kv;
+    if (group > 8)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "GQA group %d > 8: one block holds at most 8 warps",
+                    group);
+    if (head_dim % 32 != 0 || head_dim < 32 || head_dim > 256)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "head_dim %d: must be 32..=256, multiple of 32",
+                    head_dim);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hipml_kv_encode(hipml_stream_t stream, const int *step, int dtype, const float *k_row,
+                    const float *v_row, void *k_cache, void *v_cache, int n_kv, int head_dim,
+                    int stride) {
+    if (int e = check_encode(dtype, n_kv, head_dim, stride)) return e;
+    void *args[] = {&k_row, &v_row, &k_cache, &v_cache, &head_dim, &stride, &step};
+    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_encode_q8"), dim3(n_kv), dim3(head_dim),
+                                 args, 0, as_stream(stream));
+}
+
+int hipml_kv_encode_bulk(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
+                         void *k_cache, void *v_cache, int n_kv, int head_dim, int stride,
+                         int start, int src0, int rows) {
+    if (int e = check_encode(dtype, n_kv, head_dim, stride)) return e;
+    if (rows < 0 || start < 0 || src0 < 0 || start + rows > stride)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "rows [%d, %d) beyond KV cache %d", start,
+                    start + rows, stride);
+    if (rows == 0) return 0;
+    // One CTA per (row, head) pair up to a few waves of the device; the kernel strides.
+    const long long pairs = (long long)n_kv * rows;
+    const unsigned grid = (unsigned)(pairs < 148LL * 64 ? pairs : 148LL * 64);
+    void *args[] = {&k_f32, &v_f32, &k_cache, &v_cache, &n_kv, &head_dim, &stride, &start, &rows,
+                    &src0};
+    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_encode_bulk_q8"), dim3(grid), dim3(head_dim),
+                                 args, 0, as_stream(stream));
+}
+
+int hipml_kv_encode_rows(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
+                         void *k_cache, void *v_cache, int n_kv, int head_dim, int stride,
+                         const int *pos, int slot_bytes, int slots) {
+    if (int e = check_encode(dtype, n_kv, head_dim, stride)) return e;
+    if (slots <= 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "slots %d must be positive", slots);
+    void *args[] = {&k_f32, &v_f32, &k_cache, &v_cache, &n_kv, &head_dim, &stride, &pos,
+                    &slot_bytes};
+    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_encode_q8_b"), dim3(n_kv, slots),
+                                 dim3(head_dim), args, 0, as_stream(stream));
+}
+
+int hipml_kv_append_f32(hipml_stream_t stream, const int *step, float *k_cache, float *v_cache,
+                        const float *k_row, const float *v_row, int width) {
+    if (width <= 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "width %d must be positive", width);
+    void *args[] = {&k_cache, &v_cache, &k_row, &v_row, &step, &width};
+    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_append_f32"), dim3((2 * width + 255) / 256),
+                                 dim3(256), args, 0, as_stream(stream));
+}
+
+int hipml_kv_append_chunk_f32(hipml_stream_t stream, float *k_cache, float *v_cache,
+                              const float *k, const float *v, int pos0, int width, int tokens) {
+    if (width <= 0 || tokens < 0 || pos0 < 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "width %d / tokens %d / pos0 %d", width, tokens, pos0);
+    if (tokens == 0) return 0;
+    const long long n = (long long)tokens * width;
+    long long blocks = (n / 4 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    void *args[] = {&k_cache, &v_cache, &k, &v, &pos0, &width, &tokens};
+    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_append_chunk_f32"), dim3((unsigned)blocks),
+                                 dim3(256), args, 0, as_stream(stream));
+}
+
+int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
+                         const void *k, const void *v, float *part_acc, float *part_ml,
+                         float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
+                         int splits, size_t k_off, size_t v_off) {
+    if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
+    // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
+    // experimental variants have no counterpart here.
+    bool tensor_core;
+    if (selector == 0 || selector == 4) {
+        tensor_core = head_dim == 256;
+        if (selector == 4 && head_dim != 256)
+            return fail(HIPML_ERR_INVALID_ARGUMENT,
+                        "head_dim %d: the warp kernel is head_dim 256 only", head_dim);
+    } else if (selector == 6) {
+        tensor_core = false;
+    } else if (selector == 1) {
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 1 (q4_0) is not built in this library");
+    } else {
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", selector);
+    }
+    if (splits < 1) splits = 1;
+    if (stride <= 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "stride %d must be positive", stride);
+    if (((k_off | v_off) & 15) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "k_off/v_off must be multiples of 16 bytes");
+    DecodeParams p;
+    p.q = q;
+    p.k = (const unsigned char *)k + k_off;
+    p.v = (const unsigned char *)v + v_off;
+    p.part_acc = part_acc;
+    p.part_ml = part_ml;
+    p.len = step;
+    p.len_stride = 0;
+    p.len_offset = 1;
+    p.n_heads = n_heads;
+    p.n_kv = n_kv;
+    p.head_dim = head_dim;
+    p.stride = stride;
+    p.scale_log2 = scale * kLog2e;
+    p.splits = splits;
+    p.by_stride = 0;
+    p.kv_slot_bytes = p.acc_slot = p.ml_slot = p.q_slot = 0;
+    if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
+    if (int e = launch_decode_split(as_stream(stream), p, 1, tensor_core)) return e;
+    const float *pa = part_acc, *pm = part_ml;
+    void *args[] = {&pa, &pm, &out, &head_dim, &splits};
+    return (int)cudaLaunchKernel(lookup_decode_kernel("attn_decode_kv_reduce"), dim3(n_heads),
+                                 dim3(head_dim), args, 0, as_stream(stream));
+}
+
+static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,
+                       const void *k_cache, const void *v_cache, float *part_acc, float *part_ml,
+                       float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
+                       int splits, int kv_slot_bytes, int acc_slot, int ml_slot, int q_slot,
+                       int slots, int by_stride) {
+    if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
+    if (dtype == 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 1 (q4_0) is not built in this library");
+    if (dtype != 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", dtype);
+    if (slots <= 0 || splits < 1 || stride <= 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "slots %d / splits %d / stride %d", slots, splits,
+                    stride);
+    DecodeParams p;
+    p.q = q;
+    p.k = (const unsigned char *)k_cache;
+    p.v = (const unsigned char *)v_cache;
+    p.part_acc = part_acc;
+    p.part_ml = part_ml;
+    p.len = pos;
+    p.len_stride = 2;
+    p.len_offset = 1;
+    p.n_heads = n_heads;
+    p.n_kv = n_kv;
+    p.head_dim = head_dim;
+    p.stride = stride;
+    p.scale_log2 = scale * kLog2e;
+    p.splits = splits;
+    p.by_stride = by_stride;
+    p.kv_slot_bytes = kv_slot_bytes;
+    p.acc_slot = acc_slot;
+    p.ml_slot = ml_slot;
+    p.q_slot = q_slot;
+    const bool aligned =
+        ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v) | (size_t)kv_slot_bytes) &
+         15) == 0;
+    const bool tensor_core = head_dim == 256 && aligned;
+    if (int e = launch_decode_split(as_stream(stream), p, slots, tensor_core)) return e;
+    const float *pa = part_acc, *pm = part_ml;
+    void *args[] = {&pa, &pm, &out, &head_dim, &splits, &acc_slot, &ml_slot, &q_slot};
+    return (int)cudaLaunchKernel(lookup_decode_kernel("attn_decode_kv_reduce_b"),
+                                 dim3(n_heads, slots), dim3(head_dim), args, 0, as_stream(stream));
+}
+
+int hipml_attn_decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,
+                           const void *k_cache, const void *v_cache, float *part_acc,
+                           float *part_ml, float *out, int n_heads, int n_kv, int head_dim,
+                           int stride, float scale, int splits, int kv_slot_bytes, int acc_slot,
+                           int ml_slot, int q_slot, int slots) {
+    return decode_rows(stream, dtype, pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads,
+                       n_kv, head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot,
+                       q_slot, slots, 1);
+}
+
+int hipml_attn_decode_batch(hipml_stream_t stream, int dtype, const int *pos, const float *q,
+                            const void *k_cache, const void *v_cache, float *part_acc,
+                            float *part_ml, float *out, int n_heads, int n_kv, int head_dim,
+                            int stride, float scale, int splits, int kv_slot_bytes, int acc_slot,
+                            int ml_slot, int q_slot, int slots, int live_seq) {
+    if (n_kv <= 0 || n_heads % n_kv != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "n_heads %d is not a multiple of n_kv %d", n_heads,
+                    n_kv);
+    const int group = n_heads / n_kv;
+    const bool one = live_seq > 0 && slots == 1 && dtype == 0 && head_dim == 256 && group <= 8;
+    if (one) {
+        // A lone slot partitions over its live length, as the single-stream engine does.
+        int live = live_seq / 32;
+        live = live < 1 ? 1 : (live > 256 ? 256 : live);
+        if (live > splits) live = splits;
+        return decode_rows(stream, dtype, pos, q, k_cache, v_cache, part_acc, part_ml, out,
+                           n_heads, n_kv, head_dim, stride, scale, live, kv_slot_bytes, acc_slot,
+                           ml_slot, q_slot, 1, 0);
+    }
+    return decode_rows(stream, dtype, pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads,
+                       n_kv, head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot,
+                       q_slot, slots, 1);
+}
+
+size_t hipml_attn_chunk_workspace_bytes(int n_kv, int head_dim, int pos0, int tokens) {
+    if (head_dim != 256 || n_kv <= 0 || pos0 < 0 || tokens <= 0) return 0;
+    return chunk_tc_workspace_bytes(n_kv, pos0 + tokens);
+}
+
+int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
+                     const void *v_cache, float *out, int n_heads, int n_kv, int head_dim,
+                     int pos0, int tokens, int kv_dtype, int stride, float *part_acc,
+                     float *part_ml, int splits, int mode, void *workspace,
+                     size_t workspace_bytes) {
+    if (n_kv <= 0 || n_heads % n_kv != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "n_heads %d is not a multiple of n_kv %d", n_heads,
+                    n_kv);
+    const int group = n_heads / n_kv;
+    if (kv_dtype == 2)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 2 (q4_0) is not built in this library");
+    if (kv_dtype != 0 && kv_dtype != 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", kv_dtype);
+    if (kv_dtype != 0 && !(head_dim == 256 && group <= 8))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "quantized chunk attention: unsupported shape");
+    if (head_dim % 32 != 0 || head_dim < 32 || head_dim > 256)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "head_dim %d: must be 32..=256, multiple of 32",
+                    head_dim);
+    if (pos0 < 0 || tokens < 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "pos0 %d / tokens %d", pos0, tokens);
+    if (kv_dtype == 1 && pos0 + tokens > stride)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "position %d beyond KV cache %d", pos0 + tokens,
+                    stride);
+    if (mode < 0 || mode > 2) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown mode %d", mode);
+    if (tokens == 0) return 0;
+    if (splits >= 2 && (!part_acc || !part_ml))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "split attention needs part_acc and part_ml");
+    const int qslots = (tokens + 31) / 32 * 32;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+
+    if (mode == 2) {
+        ChunkScalarParams p;
+        p.q = q;
+        p.k = k_cache;
+        p.v = v_cache;
+        p.out = out;
+        p.part_acc = part_acc;
+        p.part_ml = part_ml;
+        p.n_heads = n_heads;
+        p.n_kv = n_kv;
+        p.head_dim = head_dim;
+        p.pos0 = pos0;
+        p.tokens = tokens;
+        p.kv_dtype = kv_dtype;
+        p.stride = stride;
+        p.scale_log2 = scale * kLog2e;
+        p.splits = splits;
+        p.qslots = qslots;
+        if (int e = launch_chunk_scalar(as_stream(stream), p)) return e;
+    } else {
+        if (head_dim != 256 || group > 8)
+            return fail(HIPML_ERR_INVALID_ARGUMENT,
+                        "tensor-core chunk attention: only head_dim 256 with a GQA group <= 8");
+        const size_t need = chunk_tc_workspace_bytes(n_kv, pos0 + tokens);
+        if (!workspace || workspace_bytes < need)
+            return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace: %zu bytes given, %zu needed",
+                        workspace_bytes, need);
+        if ((reinterpret_cast<size_t>(workspace) & 255) != 0)
+            return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace must be 256-byte aligned");
+        if (((reinterpret_cast<size_t>(q) | reinterpret_cast<size_t>(out) |
+              reinterpret_cast<size_t>(k_cache) | reinterpret_cast<size_t>(v_cache)) & 15) != 0)
+            return fail(HIPML_ERR_INVALID_ARGUMENT, "q, out and the caches must be 16-byte aligned");
+        int *status = device_status_word();
+        if (!status) return launch_status();
+        if (int e = launch_chunk_tc(as_stream(stream), q, k_cache, v_cache, out, part_acc, part_ml,
+                                    n_heads, n_kv, pos0, tokens, kv_dtype, stride, splits,
+                                    mode == 1, workspace, status))
+            return e;
+    }
+    if (splits >= 2)
+        return launch_chunk_combine(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
+                                    tokens, qslots, splits);
+    return 0;
+}
+
+}  // extern "C"

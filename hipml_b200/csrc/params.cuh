@@ -1,0 +1,54 @@
+// Parameter blocks and host-side launch helpers shared between the kernel files and
+// the C-ABI launchers.
+#pragma once
+
+#include "common.cuh"
+
+namespace hipml {
+
+// Split-K decode over the q8_0 cache (attn_decode.cu).
+struct DecodeParams {
+    const float *q;
+    const unsigned char *k;
+    const unsigned char *v;
+    float *part_acc;
+    float *part_ml;
+    const int *len;       // live length of slot s is len[s*len_stride + len_offset]
+    int len_stride;
+    int len_offset;
+    int n_heads, n_kv, head_dim, stride;
+    float scale_log2;     // scale * log2(e): scores are kept in log2 units
+    int splits;
+    int by_stride;        // 1: runs of ceil(stride/splits) cache rows; 0: ceil(len/splits)
+    long long kv_slot_bytes, acc_slot, ml_slot, q_slot;
+};
+// Launches the split pass (the caller launches the reduce).
+int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, bool tensor_core);
+
+// Scalar chunk attention (attn_chunk_scalar.cu).
+struct ChunkScalarParams {
+    const float *q;
+    const void *k;
+    const void *v;
+    float *out;        // splits < 2
+    float *part_acc;   // splits >= 2
+    float *part_ml;
+    int n_heads, n_kv, head_dim;
+    int pos0, tokens;
+    int kv_dtype;      // 0 f32 position-major, 1 q8_0 head-major
+    int stride;
+    float scale_log2;
+    int splits, qslots;
+};
+int launch_chunk_scalar(cudaStream_t stream, const ChunkScalarParams &p);
+int launch_chunk_combine(cudaStream_t stream, const float *part_acc, const float *part_ml,
+                         float *out, int n_heads, int head_dim, int tokens, int qslots, int splits);
+
+// Tensor-core chunk attention (attn_chunk_tc.cu).
+size_t chunk_tc_workspace_bytes(int n_kv, int n_keys);
+int launch_chunk_tc(cudaStream_t stream, const float *q, const void *k_cache, const void *v_cache,
+                    float *out, float *part_acc, float *part_ml, int n_heads, int n_kv, int pos0,
+                    int tokens, int kv_dtype, int stride, int splits, int single_pass,
+                    void *workspace, int *status);
+
+}  // namespace hipml

@@ -1,0 +1,231 @@
+/*
+ * hipml_cuda.h -- C ABI of libhipml_cuda.so: the B200 (sm_100a) replacement for
+ * hipml's device layer and its full-attention kernel launchers.
+ *
+ * Two groups of entry points:
+ *
+ *   A. Device layer. One flat function per symbol of the reference's vendor
+ *      binding (crates/hipml-hip/src/ffi.rs:29-105), same argument order and
+ *      the same conventions: every call returns an int, 0 is success, handles
+ *      are opaque pointers, memcpy kinds are 1 = host->device, 2 = device->host,
+ *      3 = device->device. A `hipml-cuda` crate binds these 1:1 where
+ *      `hipml-hip` binds amdhip64.
+ *
+ *   B. Attention launchers. One function per launch routine of the
+ *      reference's kernel crate for the full-attention path (KV append /
+ *      quantise, split-K decode over the q8_0 cache, multi-slot decode, causal
+ *      chunk prefill). Arguments keep the reference's order, units and
+ *      meaning; grid/block geometry, shared-memory sizes and tensor-map setup
+ *      are internal. All pointers are device pointers unless stated; `stream`
+ *      is a CUDA stream handle (NULL = the default stream); launches are
+ *      asynchronous on that stream.
+ *
+ * Errors: 0 = success. Codes 1..9999 are CUDA runtime error codes. Codes
+ * >= HIPML_ERR_BASE are argument errors raised by this library before
+ * anything is launched; hipml_last_error_message() then holds the same
+ * sentence the reference's launcher returns as Err(String).
+ *
+ * Cache layout (frozen by the reference, crates/hipml-core/src/kv.rs:22-44):
+ * q8_0 block = f16 scale (LE) + 32 int8 codes = 34 bytes; block (kvh, pos, c)
+ * at byte ((kvh*stride + pos)*(head_dim/32) + c)*34; K and V are separate
+ * arrays; slot b of a batched cache starts at b*slot_bytes. The f32 cache is
+ * position-major [n_ctx][n_kv*head_dim].
+ */
+#ifndef HIPML_CUDA_H
+#define HIPML_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *hipml_stream_t;
+typedef void *hipml_event_t;
+typedef void *hipml_graph_t;
+typedef void *hipml_graph_exec_t;
+typedef void *hipml_module_t;
+typedef void *hipml_function_t;
+
+#define HIPML_SUCCESS 0
+#define HIPML_ERR_BASE 10000
+#define HIPML_ERR_INVALID_ARGUMENT 10001 /* shape / dtype / alignment rejected */
+#define HIPML_ERR_UNKNOWN_KERNEL 10002   /* module lookup by name failed */
+#define HIPML_ERR_WORKSPACE 10003        /* workspace missing or too small */
+#define HIPML_ERR_DEVICE_STATUS 10004    /* a kernel reported a bounded-wait timeout */
+
+#define HIPML_MEMCPY_HOST_TO_DEVICE 1
+#define HIPML_MEMCPY_DEVICE_TO_HOST 2
+#define HIPML_MEMCPY_DEVICE_TO_DEVICE 3
+
+/* ------------------------------------------------------------------ A. device
+ * Each replaces the hip* symbol of the same name in
+ * crates/hipml-hip/src/ffi.rs (line given). */
+
+int hipml_init(unsigned flags);                                           /* ffi.rs:30 hipInit */
+int hipml_get_device_count(int *count);                                   /* ffi.rs:31 */
+int hipml_get_device(int *device, int ordinal);                           /* ffi.rs:32 */
+int hipml_set_device(int device);                                         /* ffi.rs:33 */
+int hipml_device_get_name(char *name, int len, int device);               /* ffi.rs:34 */
+int hipml_device_total_mem(size_t *bytes, int device);                    /* ffi.rs:35 */
+int hipml_device_compute_capability(int *major, int *minor, int device);  /* ffi.rs:36-40 */
+const char *hipml_get_error_string(int code);                             /* ffi.rs:41 */
+/* Detail of the last HIPML_ERR_* raised on the calling thread ("" if none). */
+const char *hipml_last_error_message(void);
+
+int hipml_malloc(void **ptr, size_t size);                                /* ffi.rs:43 */
+int hipml_free(void *ptr);                                                /* ffi.rs:44 */
+int hipml_memset(void *dst, int value, size_t size);                      /* ffi.rs:45 */
+int hipml_mem_get_info(size_t *free_bytes, size_t *total_bytes);          /* ffi.rs:46 */
+int hipml_memcpy(void *dst, const void *src, size_t size, int kind);      /* ffi.rs:47 */
+int hipml_memcpy_async(void *dst, const void *src, size_t size, int kind,
+                       hipml_stream_t stream);                            /* ffi.rs:76-82 */
+int hipml_device_synchronize(void);                                       /* ffi.rs:48 */
+/* Pinned host memory for the asynchronous copies (no counterpart in ffi.rs:
+ * the reference uploads from pageable memory). */
+int hipml_host_alloc(void **ptr, size_t size);
+int hipml_host_free(void *ptr);
+
+int hipml_event_create(hipml_event_t *event);                             /* ffi.rs:50 */
+int hipml_event_destroy(hipml_event_t event);                             /* ffi.rs:51 */
+int hipml_event_record(hipml_event_t event, hipml_stream_t stream);       /* ffi.rs:52 */
+int hipml_event_synchronize(hipml_event_t event);                         /* ffi.rs:53 */
+int hipml_event_elapsed_time(float *ms, hipml_event_t start, hipml_event_t stop); /* ffi.rs:54 */
+
+int hipml_stream_create(hipml_stream_t *stream);                          /* ffi.rs:56 */
+int hipml_stream_destroy(hipml_stream_t stream);                          /* ffi.rs:57 */
+int hipml_stream_synchronize(hipml_stream_t stream);                      /* ffi.rs:58 */
+int hipml_stream_wait_event(hipml_stream_t stream, hipml_event_t event, unsigned flags); /* ffi.rs:59 */
+
+int hipml_stream_begin_capture(hipml_stream_t stream, int mode);          /* ffi.rs:63 (0 = global) */
+int hipml_stream_end_capture(hipml_stream_t stream, hipml_graph_t *graph);/* ffi.rs:64 */
+int hipml_graph_instantiate(hipml_graph_exec_t *exec, hipml_graph_t graph, void *error_node,
+                            char *log_buffer, size_t log_size);           /* ffi.rs:65-71 */
+int hipml_graph_launch(hipml_graph_exec_t exec, hipml_stream_t stream);   /* ffi.rs:72 */
+int hipml_graph_upload(hipml_graph_exec_t exec, hipml_stream_t stream);   /* ffi.rs:73 */
+int hipml_graph_destroy(hipml_graph_t graph);                             /* ffi.rs:74 */
+int hipml_graph_exec_destroy(hipml_graph_exec_t exec);                    /* ffi.rs:75 */
+
+/* The kernels are linked into this library, so there is one built-in module;
+ * `file` is accepted for signature compatibility and may be NULL.
+ * hipml_module_get_function resolves the reference's kernel entry names
+ * (kv_encode_q8, kv_encode_bulk_q8, kv_encode_q8_b, kv_append_f32,
+ * kv_append_chunk_f32, attn_decode_kv_reduce, attn_decode_kv_reduce_b); those
+ * keep the reference's parameter lists and launch shapes, so
+ * hipml_module_launch_kernel(f, grid, block, shmem, stream, params, NULL)
+ * launches them exactly as `Kernel::launch` does
+ * (crates/hipml-hip/src/device.rs:543-580). The attention kernels proper need
+ * launch state that a bare parameter array cannot carry; use section B. */
+int hipml_module_load(hipml_module_t *module, const char *file);          /* ffi.rs:84 */
+int hipml_module_unload(hipml_module_t module);                           /* ffi.rs:85 */
+int hipml_module_get_function(hipml_function_t *function, hipml_module_t module,
+                              const char *name);                          /* ffi.rs:86-90 */
+int hipml_module_launch_kernel(hipml_function_t function, unsigned grid_x, unsigned grid_y,
+                               unsigned grid_z, unsigned block_x, unsigned block_y,
+                               unsigned block_z, unsigned shared_mem_bytes, hipml_stream_t stream,
+                               void **kernel_params, void **extra);       /* ffi.rs:91-104 */
+
+/* --------------------------------------------------------------- B. launchers
+ * `dtype` for encode/decode is KvDtype::id(): 0 = q8_0 (1 = q4_0 is rejected:
+ * not built). `step` is the device-resident i32[8] step buffer
+ * [pos, seq, token, 0, p0..p3] (crates/hipml-kernels/src/launch.rs:105-154):
+ * step[0] = append position, step[1] = live length. */
+
+/* Launcher::kv_encode_ptr_on (crates/hipml-kernels/src/launch/device/graph_launch.rs:932-973):
+ * quantise one token's K and V rows ([n_kv*head_dim] f32 each) into the cache at step[0]. */
+int hipml_kv_encode(hipml_stream_t stream, const int *step, int dtype, const float *k_row,
+                    const float *v_row, void *k_cache, void *v_cache, int n_kv, int head_dim,
+                    int stride);
+
+/* Launcher::kv_encode_bulk (graph_launch.rs:980-1028): `rows` positions of a
+ * position-major [.][n_kv*head_dim] f32 buffer; source row src0+r lands at position start+r. */
+int hipml_kv_encode_bulk(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
+                         void *k_cache, void *v_cache, int n_kv, int head_dim, int stride,
+                         int start, int src0, int rows);
+
+/* Launcher::kv_encode_rows_ptr / kv_encode_batch
+ * (crates/hipml-kernels/src/launch/device/batch_launch.rs:22-105): one row per slot, slot s
+ * appends at pos[2*s] into the cache at byte s*slot_bytes. pos is i32 [slots][2] = (pos, pos+1). */
+int hipml_kv_encode_rows(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
+                         void *k_cache, void *v_cache, int n_kv, int head_dim, int stride,
+                         const int *pos, int slot_bytes, int slots);
+
+/* AttnLayer::append_at (crates/hipml-kernels/src/attn_gpu.rs:885-912; kernel
+ * kv_append_f32.hip:10-26): copy one K and one V row into the f32 caches at step[0]. */
+int hipml_kv_append_f32(hipml_stream_t stream, const int *step, float *k_cache, float *v_cache,
+                        const float *k_row, const float *v_row, int width);
+
+/* kv_append_chunk_f32 (crates/hipml-kernels/kernels/attn_chunk_f32.hip:100-119): rows
+ * t < tokens of k/v land at cache row pos0+t. */
+int hipml_kv_append_chunk_f32(hipml_stream_t stream, float *k_cache, float *v_cache,
+                              const float *k, const float *v, int pos0, int width, int tokens);
+
+/* launch_kv::launch_ptrs (crates/hipml-kernels/src/launch_kv.rs:110-280): split-K decode over
+ * the q8_0 cache, then the split reduce. `selector` is the reference's kernel id: 0 and 4
+ * select the tensor-core kernel (head_dim 256 only), 6 the scalar kernel (any head_dim in
+ * 32..256 step 32); other ids are rejected. `stride` is the cache's rows per KV head; the
+ * live length is step[1]. Split s covers positions [s*per, min((s+1)*per, seq)),
+ * per = ceil(seq/splits). part_acc is f32 [n_heads][splits][head_dim], part_ml f32
+ * [n_heads][splits][2] = (max in log2 units, sum). k_off/v_off are byte offsets (multiples
+ * of 16) added to k/v. out is f32 [n_heads][head_dim]. */
+int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
+                         const void *k, const void *v, float *part_acc, float *part_ml,
+                         float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
+                         int splits, size_t k_off, size_t v_off);
+
+/* Launcher::attn_decode_rows_ptr (batch_launch.rs:213-316): multi-slot decode. Slot s reads
+ * q + s*q_slot, caches + s*kv_slot_bytes, pos[2*s+1] as its live length, and writes
+ * part_acc + s*acc_slot, part_ml + s*ml_slot, out + s*q_slot. The key axis is cut into
+ * `splits` runs of ceil(stride/splits) rows fixed in cache positions; runs that start at or
+ * beyond the live length write an empty partial (max = -inf, sum = 0). */
+int hipml_attn_decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,
+                           const void *k_cache, const void *v_cache, float *part_acc,
+                           float *part_ml, float *out, int n_heads, int n_kv, int head_dim,
+                           int stride, float scale, int splits, int kv_slot_bytes, int acc_slot,
+                           int ml_slot, int q_slot, int slots);
+
+/* Launcher::attn_decode_batch (batch_launch.rs:109-209): as above, except that one live slot
+ * (slots == 1, live_seq > 0, head_dim 256) partitions over the live length with
+ * min(clamp(live_seq/32, 1, 256), splits) splits, as the reference's lone-slot route does. */
+int hipml_attn_decode_batch(hipml_stream_t stream, int dtype, const int *pos, const float *q,
+                            const void *k_cache, const void *v_cache, float *part_acc,
+                            float *part_ml, float *out, int n_heads, int n_kv, int head_dim,
+                            int stride, float scale, int splits, int kv_slot_bytes, int acc_slot,
+                            int ml_slot, int q_slot, int slots, int live_seq);
+
+/* Bytes of device workspace hipml_attn_chunk needs for a call with these shapes (the staged
+ * half-precision image of the visible cache rows). Monotonic in pos0 + tokens. */
+size_t hipml_attn_chunk_workspace_bytes(int n_kv, int head_dim, int pos0, int tokens);
+
+/* AttnLayer::chunk_attention_kv (crates/hipml-kernels/src/attn_gpu/imp/attn_chunk_kv.rs:129-305):
+ * causal GQA attention of `tokens` query rows at positions pos0..pos0+tokens-1 over cache rows
+ * [0, pos0+tokens); row t sees cache rows 0..pos0+t. q and out are f32 [tokens][n_heads*head_dim].
+ * kv_dtype: 0 = f32 position-major cache [n_ctx][n_kv*head_dim] (stride unused), 1 = q8_0
+ * head-major cache with `stride` rows per KV head (2 = q4_0 is rejected: not built).
+ * scale is 1/sqrt(head_dim), computed here as the reference does.
+ * splits < 2: one pass. splits >= 2: the key axis of every query tile is cut into `splits`
+ * slices, partials go to part_acc f32 [splits][qslots][n_heads][head_dim] and part_ml f32
+ * [splits][qslots][n_heads][2] with qslots = tokens rounded up to 32, and a combine pass
+ * writes out (attn_chunk_split.hip:343-376).
+ * mode: 0 = tensor-core kernel with error-compensated half-precision operands (meets the f32
+ * tolerance), 1 = tensor-core kernel, single half-precision pass (the reference kernel's own
+ * precision), 2 = scalar f32 kernel (any head_dim multiple of 32 up to 256; no workspace).
+ * workspace: device memory of at least hipml_attn_chunk_workspace_bytes(...) for modes 0/1. */
+int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
+                     const void *v_cache, float *out, int n_heads, int n_kv, int head_dim,
+                     int pos0, int tokens, int kv_dtype, int stride, float *part_acc,
+                     float *part_ml, int splits, int mode, void *workspace,
+                     size_t workspace_bytes);
+
+/* Reads and clears the device status word that kernels with bounded waits set when a wait
+ * ran out (0 = none). Synchronises `stream`. Returns HIPML_ERR_DEVICE_STATUS if it was set. */
+int hipml_check_device_status(hipml_stream_t stream, int *status);
+
+/* Library build identification: "hipml_cuda <version> sm_100a". */
+const char *hipml_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
