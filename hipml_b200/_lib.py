@@ -75,6 +75,9 @@ SIGNATURES = {
     "hipml_attn_chunk_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "hipml_attn_chunk": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i,
                               _i, _vp, _sz]),
+    "hipml_attn_chunk_stage": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz]),
+    "hipml_attn_chunk_staged": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp,
+                                     _sz]),
     "hipml_check_device_status": (_i, [_vp, C.POINTER(_i)]),
     "hipml_version": (C.c_char_p, []),
 }

@@ -100,6 +100,23 @@ def attn_chunk(q, k_cache, v_cache, out, n_heads, n_kv, head_dim, pos0, tokens, 
         ws_bytes))
 
 
+def attn_chunk_stage(k_cache, v_cache, n_kv, head_dim, kv_dtype, stride, key_from, key_to,
+                     key_capacity, workspace):
+    """Convert cache rows [key_from, key_to) into the tensor-core operand image."""
+    _lib.check("chunk_attention stage", _lib.load().hipml_attn_chunk_stage(
+        _stream(), _p(k_cache), _p(v_cache), n_kv, head_dim, kv_dtype, stride, key_from, key_to,
+        key_capacity, _p(workspace), workspace.numel() * workspace.element_size()))
+
+
+def attn_chunk_staged(q, out, n_heads, n_kv, head_dim, pos0, tokens, key_capacity, workspace,
+                      part_acc=None, part_ml=None, splits=1, mode=0):
+    """Chunk attention over rows already staged by attn_chunk_stage."""
+    _lib.check("chunk_attention", _lib.load().hipml_attn_chunk_staged(
+        _stream(), _p(q), _p(out), n_heads, n_kv, head_dim, pos0, tokens, _p(part_acc),
+        _p(part_ml), splits, mode, key_capacity, _p(workspace),
+        workspace.numel() * workspace.element_size()))
+
+
 def check_device_status() -> int:
     """Synchronises the current stream; raises if a kernel's bounded wait ran out."""
     st = C.c_int(0)

@@ -223,6 +223,7 @@ struct StageParams {
     __half *k_hi, *k_lo;    // [n_kv][lpad][256]
     __half *vt_hi, *vt_lo;  // [n_kv][256][lpad]
     int n_kv, n_keys, lpad, kv_dtype, stride;
+    int tile0;              // first 64-key tile this launch writes
 };
 
 __device__ __forceinline__ void split_half(float x, __half &hi, __half &lo) {
@@ -269,10 +270,10 @@ __device__ __forceinline__ void stage_store8(__half *hi, __half *lo, size_t at, 
         make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
 }
 
-// grid (lpad/64, n_kv), block 256: one CTA stages 64 keys of one KV head.
+// grid (tiles, n_kv), block 256: one CTA stages 64 keys of one KV head.
 __global__ void __launch_bounds__(256) attn_chunk_stage(StageParams p) {
     __shared__ float vs[64][129];
-    const int kvh = blockIdx.y, key0 = blockIdx.x * 64;
+    const int kvh = blockIdx.y, key0 = (p.tile0 + blockIdx.x) * 64;
     const int tid = threadIdx.x;
     // K: row-major copy. Thread -> dims [8*(tid%32), +8) of keys tid/32 + 8*i.
     for (int i = 0; i < 8; i++) {
@@ -663,16 +664,14 @@ size_t chunk_tc_workspace_bytes(int n_kv, int n_keys) {
     return 4 * (size_t)n_kv * lpad * kD * sizeof(__half);
 }
 
-// Stages the cache and launches the tensor-core kernel. Shapes are validated by the caller.
-int launch_chunk_tc(cudaStream_t stream, const float *q, const void *k_cache, const void *v_cache,
-                    float *out, float *part_acc, float *part_ml, int n_heads, int n_kv, int pos0,
-                    int tokens, int kv_dtype, int stride, int splits, int single_pass,
-                    void *workspace, int *status) {
-    const int n_keys = pos0 + tokens;
-    const int lpad = (n_keys + kKeyTile - 1) / kKeyTile * kKeyTile;
-    const size_t plane = (size_t)n_kv * lpad * kD;
+// Stages cache rows [key_from, key_to) into a workspace laid out for `cap` keys per head
+// (cap a multiple of 128, >= key_to): whole 64-key tiles are rewritten, and rows from key_to
+// up to the next multiple of 128 are zero-filled so the last key tile is finite.
+int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_cache, int n_kv,
+                       int kv_dtype, int stride, int key_from, int key_to, int cap,
+                       void *workspace) {
+    const size_t plane = (size_t)n_kv * cap * kD;
     __half *ws = reinterpret_cast<__half *>(workspace);
-
     StageParams sp;
     sp.k = k_cache;
     sp.v = v_cache;
@@ -681,19 +680,30 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, const void *k_cache, co
     sp.vt_hi = ws + 2 * plane;
     sp.vt_lo = ws + 3 * plane;
     sp.n_kv = n_kv;
-    sp.n_keys = n_keys;
-    sp.lpad = lpad;
+    sp.n_keys = key_to;
+    sp.lpad = cap;
     sp.kv_dtype = kv_dtype;
     sp.stride = stride;
-    attn_chunk_stage<<<dim3(lpad / 64, n_kv), 256, 0, stream>>>(sp);
-    int rc = launch_status();
-    if (rc) return rc;
+    sp.tile0 = key_from / 64;
+    const int tile_end = (key_to + kKeyTile - 1) / kKeyTile * kKeyTile / 64;
+    if (tile_end <= sp.tile0) return 0;
+    attn_chunk_stage<<<dim3(tile_end - sp.tile0, n_kv), 256, 0, stream>>>(sp);
+    return launch_status();
+}
 
+// Launches the tensor-core kernel over a workspace staged for `cap` keys per head.
+// Shapes are validated by the caller.
+int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part_acc,
+                    float *part_ml, int n_heads, int n_kv, int pos0, int tokens, int cap,
+                    int splits, int single_pass, void *workspace, int *status) {
+    const size_t plane = (size_t)n_kv * cap * kD;
+    __half *ws = reinterpret_cast<__half *>(workspace);
+    int rc;
     CUtensorMap mk_hi, mk_lo, mv_hi, mv_lo;
-    if ((rc = make_map(&mk_hi, sp.k_hi, kD, (uint64_t)n_kv * lpad))) return rc;
-    if ((rc = make_map(&mk_lo, sp.k_lo, kD, (uint64_t)n_kv * lpad))) return rc;
-    if ((rc = make_map(&mv_hi, sp.vt_hi, lpad, (uint64_t)n_kv * kD))) return rc;
-    if ((rc = make_map(&mv_lo, sp.vt_lo, lpad, (uint64_t)n_kv * kD))) return rc;
+    if ((rc = make_map(&mk_hi, ws, kD, (uint64_t)n_kv * cap))) return rc;
+    if ((rc = make_map(&mk_lo, ws + plane, kD, (uint64_t)n_kv * cap))) return rc;
+    if ((rc = make_map(&mv_hi, ws + 2 * plane, cap, (uint64_t)n_kv * kD))) return rc;
+    if ((rc = make_map(&mv_lo, ws + 3 * plane, cap, (uint64_t)n_kv * kD))) return rc;
 
     static bool configured[64] = {};
     int dev = 0;
@@ -716,7 +726,7 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, const void *k_cache, co
     p.group = n_heads / n_kv;
     p.pos0 = pos0;
     p.tokens = tokens;
-    p.lpad = lpad;
+    p.lpad = cap;
     p.qtile = 128 / p.group;
     p.scale_log2 = (1.0f / sqrtf((float)kD)) * 1.4426950408889634f;
     p.splits = splits;

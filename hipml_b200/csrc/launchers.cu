@@ -286,25 +286,80 @@ int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
         if (head_dim != 256 || group > 8)
             return fail(HIPML_ERR_INVALID_ARGUMENT,
                         "tensor-core chunk attention: only head_dim 256 with a GQA group <= 8");
-        const size_t need = chunk_tc_workspace_bytes(n_kv, pos0 + tokens);
-        if (!workspace || workspace_bytes < need)
-            return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace: %zu bytes given, %zu needed",
-                        workspace_bytes, need);
-        if ((reinterpret_cast<size_t>(workspace) & 255) != 0)
-            return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace must be 256-byte aligned");
-        if (((reinterpret_cast<size_t>(q) | reinterpret_cast<size_t>(out) |
-              reinterpret_cast<size_t>(k_cache) | reinterpret_cast<size_t>(v_cache)) & 15) != 0)
-            return fail(HIPML_ERR_INVALID_ARGUMENT, "q, out and the caches must be 16-byte aligned");
-        int *status = device_status_word();
-        if (!status) return launch_status();
-        if (int e = launch_chunk_tc(as_stream(stream), q, k_cache, v_cache, out, part_acc, part_ml,
-                                    n_heads, n_kv, pos0, tokens, kv_dtype, stride, splits,
-                                    mode == 1, workspace, status))
+        const int cap = (pos0 + tokens + 127) / 128 * 128;
+        if (int e = hipml_attn_chunk_stage(stream, k_cache, v_cache, n_kv, head_dim, kv_dtype,
+                                           stride, 0, pos0 + tokens, cap, workspace,
+                                           workspace_bytes))
             return e;
+        return hipml_attn_chunk_staged(stream, q, out, n_heads, n_kv, head_dim, pos0, tokens,
+                                       part_acc, part_ml, splits, mode, cap, workspace,
+                                       workspace_bytes);
     }
     if (splits >= 2)
         return launch_chunk_combine(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
                                     tokens, qslots, splits);
+    return 0;
+}
+
+int hipml_attn_chunk_stage(hipml_stream_t stream, const void *k_cache, const void *v_cache,
+                           int n_kv, int head_dim, int kv_dtype, int stride, int key_from,
+                           int key_to, int key_capacity, void *workspace,
+                           size_t workspace_bytes) {
+    if (head_dim != 256 || n_kv <= 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT,
+                    "tensor-core chunk attention: only head_dim 256 with a GQA group <= 8");
+    if (kv_dtype != 0 && kv_dtype != 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", kv_dtype);
+    if (key_from < 0 || key_to < key_from || key_capacity % 128 != 0 || key_to > key_capacity)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "stage rows [%d, %d) with capacity %d", key_from,
+                    key_to, key_capacity);
+    if (kv_dtype == 1 && key_to > stride)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "position %d beyond KV cache %d", key_to, stride);
+    const size_t need = chunk_tc_workspace_bytes(n_kv, key_capacity);
+    if (!workspace || workspace_bytes < need)
+        return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace: %zu bytes given, %zu needed",
+                    workspace_bytes, need);
+    if ((reinterpret_cast<size_t>(workspace) & 255) != 0)
+        return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace must be 256-byte aligned");
+    if (((reinterpret_cast<size_t>(k_cache) | reinterpret_cast<size_t>(v_cache)) & 15) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "q, out and the caches must be 16-byte aligned");
+    return launch_chunk_stage(as_stream(stream), k_cache, v_cache, n_kv, kv_dtype, stride, key_from,
+                              key_to, key_capacity, workspace);
+}
+
+int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, int n_heads,
+                            int n_kv, int head_dim, int pos0, int tokens, float *part_acc,
+                            float *part_ml, int splits, int mode, int key_capacity,
+                            void *workspace, size_t workspace_bytes) {
+    if (n_kv <= 0 || n_heads % n_kv != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "n_heads %d is not a multiple of n_kv %d", n_heads,
+                    n_kv);
+    if (head_dim != 256 || n_heads / n_kv > 8)
+        return fail(HIPML_ERR_INVALID_ARGUMENT,
+                    "tensor-core chunk attention: only head_dim 256 with a GQA group <= 8");
+    if (mode != 0 && mode != 1) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown mode %d", mode);
+    if (pos0 < 0 || tokens < 0 || key_capacity % 128 != 0 || pos0 + tokens > key_capacity)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "rows [%d, %d) with capacity %d", pos0,
+                    pos0 + tokens, key_capacity);
+    if (tokens == 0) return 0;
+    if (splits >= 2 && (!part_acc || !part_ml))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "split attention needs part_acc and part_ml");
+    const size_t need = chunk_tc_workspace_bytes(n_kv, key_capacity);
+    if (!workspace || workspace_bytes < need)
+        return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace: %zu bytes given, %zu needed",
+                    workspace_bytes, need);
+    if ((reinterpret_cast<size_t>(workspace) & 255) != 0)
+        return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace must be 256-byte aligned");
+    if (((reinterpret_cast<size_t>(q) | reinterpret_cast<size_t>(out)) & 15) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "q, out and the caches must be 16-byte aligned");
+    int *status = device_status_word();
+    if (!status) return launch_status();
+    if (int e = launch_chunk_tc(as_stream(stream), q, out, part_acc, part_ml, n_heads, n_kv, pos0,
+                                tokens, key_capacity, splits, mode == 1, workspace, status))
+        return e;
+    if (splits >= 2)
+        return launch_chunk_combine(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
+                                    tokens, (tokens + 31) / 32 * 32, splits);
     return 0;
 }
 

@@ -46,9 +46,11 @@ int launch_chunk_combine(cudaStream_t stream, const float *part_acc, const float
 
 // Tensor-core chunk attention (attn_chunk_tc.cu).
 size_t chunk_tc_workspace_bytes(int n_kv, int n_keys);
-int launch_chunk_tc(cudaStream_t stream, const float *q, const void *k_cache, const void *v_cache,
-                    float *out, float *part_acc, float *part_ml, int n_heads, int n_kv, int pos0,
-                    int tokens, int kv_dtype, int stride, int splits, int single_pass,
-                    void *workspace, int *status);
+int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_cache, int n_kv,
+                       int kv_dtype, int stride, int key_from, int key_to, int cap,
+                       void *workspace);
+int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part_acc,
+                    float *part_ml, int n_heads, int n_kv, int pos0, int tokens, int cap,
+                    int splits, int single_pass, void *workspace, int *status);
 
 }  // namespace hipml

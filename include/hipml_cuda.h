@@ -218,6 +218,25 @@ int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
                      float *part_ml, int splits, int mode, void *workspace,
                      size_t workspace_bytes);
 
+/* The two halves of hipml_attn_chunk's tensor-core modes, for callers that keep the staged
+ * image across chunks (no counterpart in the reference, whose kernel converts each K/V tile
+ * inside the attention kernel, attn_chunk_wmma.hip:123-154). The workspace is laid out for
+ * key_capacity keys per KV head (a multiple of 128; size it with
+ * hipml_attn_chunk_workspace_bytes(n_kv, head_dim, 0, key_capacity)) and that capacity must be
+ * the same in every call that shares the workspace.
+ * hipml_attn_chunk_stage converts cache rows [key_from, key_to) (whole 64-row tiles are
+ * rewritten; rows from key_to to the next multiple of 128 are zero-filled).
+ * hipml_attn_chunk_staged runs the attention of rows pos0..pos0+tokens-1 over staged rows
+ * [0, pos0+tokens); mode 0 or 1 as in hipml_attn_chunk. */
+int hipml_attn_chunk_stage(hipml_stream_t stream, const void *k_cache, const void *v_cache,
+                           int n_kv, int head_dim, int kv_dtype, int stride, int key_from,
+                           int key_to, int key_capacity, void *workspace,
+                           size_t workspace_bytes);
+int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, int n_heads,
+                            int n_kv, int head_dim, int pos0, int tokens, float *part_acc,
+                            float *part_ml, int splits, int mode, int key_capacity,
+                            void *workspace, size_t workspace_bytes);
+
 /* Reads and clears the device status word that kernels with bounded waits set when a wait
  * ran out (0 = none). Synchronises `stream`. Returns HIPML_ERR_DEVICE_STATUS if it was set. */
 int hipml_check_device_status(hipml_stream_t stream, int *status);
