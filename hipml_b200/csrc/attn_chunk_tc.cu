@@ -315,7 +315,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     unsigned char *q_smem = smem;                       // 8 tiles: hi chunks 0..3, lo chunks 0..3
     unsigned char *ring = smem + kQBytes;               // kStages x (hi tile, lo tile)
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kStages * kStageBytes);
-    // bars: full[3], empty[3], s_ready[2], p_ready[2], o_done
+    // bars: full[3], empty[3], s_ready[2], p_ready[2], o_done[2]
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 12);
     unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 13);
 
@@ -345,6 +345,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         mbar_init(bar_p, 128);
         mbar_init(bar_p + 8, 128);
         mbar_init(bar_o, 1);
+        mbar_init(bar_o + 8, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -476,7 +477,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                         tc_commit(bar_empty + 8 * stage);
                         n++;
                     }
-                if (ok) tc_commit(bar_o);
+                if (ok) tc_commit(bar_o + 8 * (i & 1));
             };
             qk(0);
             for (int i = 0; i < n_tiles && ok; i++) {
@@ -519,7 +520,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                                           (m_used == -INFINITY && m_new > -INFINITY));
             if (i == 0) m_used = m_new;
             if (__any_sync(0xffffffffu, want)) {
-                ok = mbar_wait(bar_o, (i - 1) & 1, abort_flag, p.status, 6);
+                ok = mbar_wait(bar_o + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, p.status, 6);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                 tc_fence_after();
                 const float corr = (m_used == -INFINITY) ? 0.0f : exp2f(m_used - m_new);
@@ -563,7 +564,8 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         }
         // epilogue: O / l (or the raw partial)
         if (ok && n_tiles > 0) {
-            ok = mbar_wait(bar_o, (n_tiles - 1) & 1, abort_flag, p.status, 7);
+            ok = mbar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag,
+                           p.status, 7);
         }
         ok = __all_sync(0xffffffffu, ok);
         const bool live = r < rows_live;
