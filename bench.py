@@ -354,6 +354,96 @@ def decode_bench(torch, api, depths, steps, layers, hbm_gbs, reps=3):
     return results
 
 
+def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs, reps=3):
+    """Decode at `depth` with the cache rows split across the ranks by sequence: per layer the
+    owner of the new position appends its row, every rank folds its rows to one
+    (acc, max, sum) triple per head, the triples are all-gathered over NCCL and folded again
+    on every rank. One CUDA graph per rank holds all steps (NCCL calls included)."""
+    from hipml_b200 import sharding
+    dev = "cuda"
+    capacity = depth + steps + 8
+    lo, hi = sharding.decode_shard_range(capacity, world, rank)
+    stride = max(hi - lo, 1)
+    g = torch.Generator(device=dev).manual_seed(4 + 17 * rank)
+    kc = [torch.zeros(KV * stride * ROW, dtype=torch.uint8, device=dev) for _ in range(layers)]
+    vc = [torch.zeros(KV * stride * ROW, dtype=torch.uint8, device=dev) for _ in range(layers)]
+    n0 = sharding.local_length(depth, lo, hi)
+    for l in range(layers):
+        for p0 in range(0, n0, 8192):
+            n = min(8192, n0 - p0)
+            api.kv_encode_bulk(torch.randn(n, W, device=dev, generator=g),
+                               torch.randn(n, W, device=dev, generator=g), kc[l], vc[l], KV, D,
+                               stride, p0, 0, n)
+    gs = torch.Generator(device=dev).manual_seed(4)  # same query / new rows on every rank
+    q = torch.randn(steps, layers, QW, device=dev, generator=gs)
+    kn = torch.randn(steps, layers, W, device=dev, generator=gs)
+    vn = torch.randn(steps, layers, W, device=dev, generator=gs)
+    step_host = []
+    for i in range(steps):
+        pos = depth + i
+        step_host.append([max(pos - lo, 0), sharding.local_length(pos + 1, lo, hi), 0, 0, 0, 0, 0, 0])
+    step_buf = torch.tensor(step_host, dtype=torch.int32, device=dev)
+    owners = [sharding.decode_owner(depth + i, capacity, world) for i in range(steps)]
+    out = torch.empty(steps, layers, QW, device=dev)
+    acc = torch.empty(H * 256 * D, device=dev)
+    ml = torch.empty(H * 256 * 2, device=dev)
+    shard = torch.empty(H, D + 2, device=dev)
+    gathered = torch.empty(world, H, D + 2, device=dev)
+
+    def token(i):
+        splits = api.decode_splits(max(step_host[i][1], 1))
+        for l in range(layers):
+            if owners[i] == rank:
+                api.kv_encode(step_buf[i], kn[i, l], vn[i, l], kc[l], vc[l], KV, D, stride)
+            api.attn_decode_kv_shard(step_buf[i], q[i, l], kc[l], vc[l], acc, ml, shard, H, KV, D,
+                                     stride, SCALE, splits)
+            dist.all_gather_into_tensor(gathered, shard)
+            api.attn_decode_combine(gathered, out[i, l], H, D, world)
+
+    token(0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    mode = "cuda graph"
+    try:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(steps):
+                    token(i)
+        torch.cuda.current_stream().wait_stream(side)
+        run = graph.replay
+    except Exception as e:  # capture of the collective refused: time the eager loop instead
+        mode = f"eager ({type(e).__name__})"
+
+        def run():
+            for i in range(steps):
+                token(i)
+    run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times.append(float(t.item()))
+    ms_step = min(times) / steps
+    kv_bytes = sum(layers * 2 * KV * (depth + i + 1) * ROW for i in range(steps)) / steps
+    gbs = kv_bytes / (ms_step * 1e-3) / 1e9
+    return {"depth": depth, "ranks": world, "partition": "sequence", "launch": mode,
+            "ms_per_step": ms_step, "tok_s": 1e3 / ms_step, "kv_bytes_per_step": kv_bytes,
+            "kv_gbs": gbs, "frac_hbm_of_all_gpus": gbs / (hbm_gbs * world),
+            "exchange_bytes_per_layer_step": world * H * (D + 2) * 4,
+            "finite": bool(torch.isfinite(out).all().item())}
+
+
 def gpu_main(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -372,22 +462,15 @@ def gpu_main(args):
 
     # KV-head sharding: each rank owns n_kv/world KV heads and their query heads; no data-path
     # collective inside the attention. Beyond 4 ranks the query tiles are interleaved too.
-    kv_shards = min(world, KV)
-    q_shards = world // kv_shards
-    n_kv_local, heads_local = KV // kv_shards, H // kv_shards
-    tokens_local = T_PREFILL  # keys are never split; queries are when world > 4
+    from hipml_b200 import sharding
+    kv_shards, q_shards, kv_index, q_index, n_kv_local, heads_local = sharding.kv_head_shard(
+        H, KV, world, rank)
     pf = Prefill(torch, api, heads_local, n_kv_local, T_PREFILL, CHUNK, LAYERS,
-                 seed=1 + 1000 * (rank % kv_shards), stride=T_PREFILL + 8)
+                 seed=1 + 1000 * kv_index, stride=T_PREFILL + 8)
     if q_shards > 1:
-        # rank r of a pair runs every q_shards-th 2048-token chunk's second/first half:
-        # halves alternate so both see the same causal work.
-        qi = rank // kv_shards
-        chunks = []
-        for ci, (p, n) in enumerate(pf.chunks):
-            half = n // q_shards
-            part = (qi + ci) % q_shards
-            chunks.append((p, n, part * half, half))
-        pf.q_parts = chunks
+        # the ranks that share a KV head take rotating parts of every chunk's query rows
+        pf.q_parts = [(p, n) + sharding.query_part(ci, n, q_shards, q_index)
+                      for ci, (p, n) in enumerate(pf.chunks)]
 
         def layer(l, q, k, v, out, kc, vc, ws, mode=0, timed=None):
             for ci, (pos0, n, qoff, qn) in enumerate(pf.q_parts):
@@ -458,6 +541,12 @@ def gpu_main(args):
             line["decode"] = decode_bench(torch, api, DECODE_DEPTHS, DECODE_STEPS, LAYERS,
                                           pk["hbm_gbs"])
             line["decode_peak_hbm_gbs"] = pk["hbm_gbs"]
+    if world > 1 and not args.no_decode:
+        del pf
+        torch.cuda.empty_cache()
+        line["decode"] = [decode_sharded(torch, dist, api, 100000, DECODE_STEPS, LAYERS, world, rank,
+                                         pk["hbm_gbs"])]
+        line["decode_peak_hbm_gbs"] = pk["hbm_gbs"]
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:
@@ -519,15 +608,97 @@ def reference_main(args):
     }))
 
 
+def profile_case(args):
+    """Small single-kernel cases for `ncu` captures (a few launches, a few hundred MB held):
+    chunk  -- one 2048-token chunk at position 6144 of one layer (the largest chunk of the
+              headline workload): kv_encode_bulk, stage, attn_chunk_tc, `--reps` times;
+    decode -- one layer's decode at depth 100000 (217.6 MB of q8 K/V, larger than L2):
+              kv_encode_q8, attn_decode_kv_tc, attn_decode_kv_reduce, `--reps` times.
+    Prints the CUDA-event time per repetition so the capture has an un-profiled number."""
+    import torch
+
+    import __graft_entry__ as entry
+    entry.build()
+    from hipml_b200 import api
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(7)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.reps)]
+    if args.case == "chunk":
+        pos0, n, stride = 6144, 2048, 8200
+        q = torch.randn(n, QW, device=dev, generator=g)
+        kf = torch.randn(pos0 + n, W, device=dev, generator=g)
+        vf = torch.randn(pos0 + n, W, device=dev, generator=g)
+        kc = torch.zeros(KV * stride * ROW, dtype=torch.uint8, device=dev)
+        vc = torch.zeros_like(kc)
+        out = torch.empty(n, QW, device=dev)
+        cap = 8192
+        ws = torch.empty(api.attn_chunk_workspace_bytes(KV, D, 0, cap), dtype=torch.uint8, device=dev)
+        api.kv_encode_bulk(kf, vf, kc, vc, KV, D, stride, 0, 0, pos0)
+        api.attn_chunk_stage(kc, vc, KV, D, 1, stride, 0, pos0, cap, ws)
+        for r in range(args.reps):
+            api.kv_encode_bulk(kf[pos0:], vf[pos0:], kc, vc, KV, D, stride, pos0, 0, n)
+            api.attn_chunk_stage(kc, vc, KV, D, 1, stride, pos0, pos0 + n, cap, ws)
+            ev[2 * r].record()
+            api.attn_chunk_staged(q, out, H, KV, D, pos0, n, cap, ws, mode=args.mode)
+            ev[2 * r + 1].record()
+        torch.cuda.synchronize()
+        flops = attn_flops(chunk_pairs(pos0, n))
+        for r in range(args.reps):
+            ms = ev[2 * r].elapsed_time(ev[2 * r + 1])
+            print(json.dumps({"case": "chunk 2048@6144", "mode": args.mode, "ms": ms,
+                              "algorithmic_tflops": flops / ms / 1e9}))
+    else:
+        depth = args.depth
+        stride = depth + 136
+        kc = torch.zeros(KV * stride * ROW, dtype=torch.uint8, device=dev)
+        vc = torch.zeros_like(kc)
+        for p0 in range(0, depth, 8192):
+            n = min(8192, depth - p0)
+            api.kv_encode_bulk(torch.randn(n, W, device=dev, generator=g),
+                               torch.randn(n, W, device=dev, generator=g), kc, vc, KV, D, stride,
+                               p0, 0, n)
+        q = torch.randn(args.reps, QW, device=dev, generator=g)
+        kn = torch.randn(args.reps, W, device=dev, generator=g)
+        vn = torch.randn(args.reps, W, device=dev, generator=g)
+        out = torch.empty(args.reps, QW, device=dev)
+        acc = torch.empty(H * 256 * D, device=dev)
+        ml = torch.empty(H * 256 * 2, device=dev)
+        steps = torch.zeros(args.reps, 8, dtype=torch.int32, device=dev)
+        steps[:, 0] = torch.arange(depth, depth + args.reps, dtype=torch.int32, device=dev)
+        steps[:, 1] = steps[:, 0] + 1
+        torch.cuda.synchronize()
+        for r in range(args.reps):
+            api.kv_encode(steps[r], kn[r], vn[r], kc, vc, KV, D, stride)
+            ev[2 * r].record()
+            api.attn_decode_kv(steps[r], q[r], kc, vc, acc, ml, out[r], H, KV, D, stride, SCALE,
+                               api.decode_splits(depth + r + 1), selector=args.selector)
+            ev[2 * r + 1].record()
+        torch.cuda.synchronize()
+        for r in range(args.reps):
+            ms = ev[2 * r].elapsed_time(ev[2 * r + 1])
+            nbytes = 2 * KV * (depth + r + 1) * ROW
+            print(json.dumps({"case": f"decode depth {depth}", "selector": args.selector, "ms": ms,
+                              "kv_gbs": nbytes / ms / 1e6}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", choices=["chunk", "decode"], default=None,
+                    help="run one small profiling case instead of the benchmark")
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--mode", type=int, default=0)
+    ap.add_argument("--selector", type=int, default=0)
+    ap.add_argument("--depth", type=int, default=100000)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="hipml_b200")
     ap.add_argument("--no-decode", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        profile_case(args)
+    elif args.impl == "reference":
         reference_main(args)
     else:
         gpu_main(args)

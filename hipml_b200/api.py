@@ -66,6 +66,21 @@ def attn_decode_kv(step, q, k, v, part_acc, part_ml, out, n_heads, n_kv, head_di
         n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
 
 
+def attn_decode_kv_shard(step, q, k, v, part_acc, part_ml, shard_out, n_heads, n_kv, head_dim,
+                         stride, scale, splits, selector=0, k_off=0, v_off=0):
+    """One GPU's part of a sequence-split decode: writes [n_heads][head_dim+2] =
+    (unnormalised acc, max_log2, sum) of the local cache rows."""
+    _lib.check("attn_decode_kv_shard", _lib.load().hipml_attn_decode_kv_shard(
+        _stream(), _p(step), selector, _p(q), _p(k), _p(v), _p(part_acc), _p(part_ml),
+        _p(shard_out), n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
+
+
+def attn_decode_combine(gathered, out, n_heads, head_dim, shards):
+    """Fold the all-gathered shard triples [shards][n_heads][head_dim+2] into out."""
+    _lib.check("attn_decode_combine", _lib.load().hipml_attn_decode_combine(
+        _stream(), _p(gathered), _p(out), n_heads, head_dim, shards))
+
+
 def attn_decode_rows(pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads, n_kv, head_dim,
                      stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot, q_slot, slots,
                      dtype=0):

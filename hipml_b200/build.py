@@ -14,6 +14,7 @@ SOURCES = [
     "device_api.cu",
     "kv_encode.cu",
     "attn_decode.cu",
+    "attn_decode_tc.cu",
     "attn_chunk_scalar.cu",
     "attn_chunk_tc.cu",
     "launchers.cu",

@@ -112,304 +112,55 @@ __global__ void __launch_bounds__(128) attn_decode_kv_scalar(DecodeParams p) {
     }
 }
 
-// -------------------------------------------------------- tensor-core body
-
-constexpr int kTcTile = 64;                        // keys per shared-memory tile
-constexpr int kTcRowBytes = 8 * kQ8BlockBytes;     // 272
-constexpr int kTcTileBytes = kTcTile * kTcRowBytes;
-constexpr int kTcThreads = 128;
-constexpr float kPScale = 1024.0f;                 // keeps p*scale in f16's normal range
-
-// Dynamic shared memory: K[2] | V[2] tiles, then the query and the score tile.
-constexpr int kTcSmemBytes = 4 * kTcTileBytes + 8 * 256 * 4 + 8 * kTcTile * 4;
-
-__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-
-__device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0,
-                                          unsigned b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
-        "{%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// The eight "logical words" of a block: four codes each, 4-byte aligned in the row.
-// Odd blocks start 2 bytes past a word boundary, so their codes are aligned:
-// word j holds codes 4j..4j+3. Even blocks start on a word boundary, so the scale
-// shares a word with codes 0,1: words 0..6 hold codes 4j+2..4j+5 and word 7 is
-// stitched from codes 0,1 and 30,31. Element order inside the contraction is
-// free as long as both operands use the same one.
-__device__ __forceinline__ unsigned block_word(const unsigned *row, int blk, int j) {
-    const int m = blk >> 1;
-    if (blk & 1) return row[17 * m + 9 + j];
-    if (j < 7) return row[17 * m + 1 + j];
-    return __byte_perm(row[17 * m], row[17 * m + 8], 0x5432);
-}
-
-// head_dim index of byte i of logical word j of block blk.
-__device__ __forceinline__ int block_word_dim(int blk, int j, int i) {
-    if (blk & 1) return blk * 32 + 4 * j + i;
-    if (j < 7) return blk * 32 + 4 * j + 2 + i;
-    return blk * 32 + (i < 2 ? i : 28 + i);
-}
-
-__device__ __forceinline__ float block_scale(const unsigned char *row, int blk) {
-    return half_bits_to_float(*reinterpret_cast<const unsigned short *>(row + blk * kQ8BlockBytes));
-}
-
-// Two int8 codes (bytes lo_sel of x) as an exact half2: 0x64xx is 1024 + xx, and x was
-// biased by 128, so subtracting 1152 gives the signed code.
-__device__ __forceinline__ unsigned codes_to_half2(unsigned biased, unsigned selector) {
-    const unsigned h = __byte_perm(biased, 0x64646464u, selector);
-    const __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half(0x6480)));
-    return *reinterpret_cast<const unsigned *>(&r);
-}
-
-__device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
-    const __half2 r = __halves2half2(lo, hi);
-    return *reinterpret_cast<const unsigned *>(&r);
-}
-
-__global__ void __launch_bounds__(kTcThreads) attn_decode_kv_tc(DecodeParams p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char *ktile[2] = {smem, smem + kTcTileBytes};
-    unsigned char *vtile[2] = {smem + 2 * kTcTileBytes, smem + 3 * kTcTileBytes};
-    float *qs = reinterpret_cast<float *>(smem + 4 * kTcTileBytes);  // [8][256], pre-scaled
-    float *ss = qs + 8 * 256;                                        // [8][kTcTile] scores
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
+// ------------------------------------------------------------ fast reduce
+//
+// The fold of the split partials used by the launchers. The kernels that keep the
+// reference's names below do the same arithmetic with one thread per output element and a
+// serial walk over the splits, which costs tens of microseconds at 256 splits; here a CTA
+// of 8 warps owns 32 output dims of one head and each warp folds every 8th split.
+__global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
+    __shared__ float s_max[8];
+    __shared__ float s_num[8][32];
+    __shared__ float s_den[8];
+    const int chunks = p.head_dim >> 5;
+    const int h = blockIdx.x / chunks, chunk = blockIdx.x - h * chunks;
     const int slot = blockIdx.y;
-    const int kvh = blockIdx.x / p.splits, split = blockIdx.x - kvh * p.splits;
-    const int group = p.n_heads / p.n_kv;
-
-    int lo, hi;
-    split_range(p, slot, split, lo, hi);
-
-    // Query rows of this KV head's group, scaled into log2 units; absent rows are zero.
-    const float *q = p.q + (size_t)slot * p.q_slot + (size_t)kvh * group * 256;
-    for (int i = tid; i < 8 * 256; i += kTcThreads)
-        qs[i] = (i >> 8) < group ? q[i] * p.scale_log2 : 0.0f;
-
-    const size_t head_byte = (size_t)slot * p.kv_slot_bytes + q8_row_offset(kvh, p.stride, 0, 256);
-    const unsigned char *kbase = p.k + head_byte;
-    const unsigned char *vbase = p.v + head_byte;
-
-    auto prefetch = [&](int tile, int buf) {
-        const int r0 = lo + tile * kTcTile;
-        const int nrows = min(kTcTile, hi - r0);
-        if (nrows > 0) {
-            const size_t off = (size_t)r0 * kTcRowBytes;
-            const int chunks = nrows * (kTcRowBytes / 16);
-            for (int i = tid; i < chunks; i += kTcThreads) {
-                cp_async_16(ktile[buf] + i * 16, kbase + off + (size_t)i * 16);
-                cp_async_16(vtile[buf] + i * 16, vbase + off + (size_t)i * 16);
-            }
-        }
-        cp_async_commit();
-    };
-
-    const int ntiles = (hi - lo + kTcTile - 1) / kTcTile;
-    if (ntiles > 0) prefetch(0, 0);
-    __syncthreads();  // qs visible
-
-    // A fragments of the query for all 16 k-steps: rows 0..7 = f16 high part of head g,
-    // rows 8..15 = f16 low part, contraction slots in block_word order.
-    unsigned qa[16][4];
+    const int dl = threadIdx.x & 31, sg = threadIdx.x >> 5;
+    const float *pa = p.acc + (size_t)slot * p.acc_slot + (size_t)h * p.acc_head_stride + chunk * 32 + dl;
+    const float *ml = p.ml + (size_t)slot * p.ml_slot + (size_t)h * p.ml_head_stride;
+    float big = -INFINITY;
+    for (int s = sg; s < p.splits; s += 8) big = fmaxf(big, ml[(size_t)s * p.ml_split_stride]);
+    if (dl == 0) s_max[sg] = big;
+    __syncthreads();
 #pragma unroll
-    for (int ks = 0; ks < 16; ks++) {
-        const int blk = ks >> 1, j = (ks & 1) * 4 + t;
-        float x[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) x[i] = qs[g * 256 + block_word_dim(blk, j, i)];
-        __half xh[4], xl[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            xh[i] = __float2half_rn(x[i]);
-            xl[i] = __float2half_rn(x[i] - __half2float(xh[i]));
-        }
-        qa[ks][0] = pack_half2(xh[0], xh[1]);
-        qa[ks][1] = pack_half2(xl[0], xl[1]);
-        qa[ks][2] = pack_half2(xh[2], xh[3]);
-        qa[ks][3] = pack_half2(xl[2], xl[3]);
+    for (int i = 0; i < 8; i++) big = fmaxf(big, s_max[i]);
+    float num = 0.0f, den = 0.0f;
+    for (int s = sg; s < p.splits; s += 8) {
+        const float m = ml[(size_t)s * p.ml_split_stride];
+        const float w = (m == -INFINITY) ? 0.0f : exp2f(m - big);
+        num += pa[(size_t)s * p.acc_split_stride] * w;
+        den += ml[(size_t)s * p.ml_split_stride + 1] * w;
     }
-
-    float acc[2][4][4];  // [block of this warp][byte i][c0..c3]
+    s_num[sg][dl] = num;
+    if (dl == 0) s_den[sg] = den;
+    __syncthreads();
+    if (sg == 0) {
+        float n = 0.0f, d = 0.0f;
 #pragma unroll
-    for (int a = 0; a < 2; a++)
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-#pragma unroll
-            for (int c = 0; c < 4; c++) acc[a][i][c] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
-
-    for (int tile = 0; tile < ntiles; tile++) {
-        const int buf = tile & 1;
-        if (tile + 1 < ntiles) {
-            prefetch(tile + 1, buf ^ 1);
-            cp_async_wait<1>();
+        for (int i = 0; i < 8; i++) {
+            n += s_num[i][dl];
+            d += s_den[i];
+        }
+        float *o = p.out + (size_t)slot * p.out_slot + (size_t)h * p.out_head_stride;
+        if (p.normalize) {
+            o[chunk * 32 + dl] = d > 0.0f ? n / d : 0.0f;
         } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const int r0 = lo + tile * kTcTile;
-        const int nvalid = min(kTcTile, hi - r0);
-
-        // ---- scores: warp w owns keys [16w, 16w+16) of the tile, all 256 dims.
-        {
-            float s[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
-#pragma unroll
-            for (int blk = 0; blk < 8; blk++) {
-                float c[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-#pragma unroll
-                for (int kk = 0; kk < 2; kk++) {
-#pragma unroll
-                    for (int nt = 0; nt < 2; nt++) {
-                        const int key = warp * 16 + nt * 8 + g;
-                        const unsigned *row =
-                            reinterpret_cast<const unsigned *>(ktile[buf] + key * kTcRowBytes);
-                        const unsigned w = block_word(row, blk, kk * 4 + t) ^ 0x80808080u;
-                        mma_16816(c[nt], qa[blk * 2 + kk], codes_to_half2(w, 0x4140),
-                                  codes_to_half2(w, 0x4342));
-                    }
-                }
-#pragma unroll
-                for (int nt = 0; nt < 2; nt++) {
-                    const int key = warp * 16 + nt * 8 + 2 * t;
-                    const float d0 = block_scale(ktile[buf] + key * kTcRowBytes, blk);
-                    const float d1 = block_scale(ktile[buf] + (key + 1) * kTcRowBytes, blk);
-                    s[nt][0] += d0 * (c[nt][0] + c[nt][2]);
-                    s[nt][1] += d1 * (c[nt][1] + c[nt][3]);
-                }
+            // the folded triple of this shard: acc (unnormalised), then max (log2 units), sum
+            o[chunk * 32 + dl] = n;
+            if (chunk == 0 && dl == 0) {
+                o[p.head_dim] = big;
+                o[p.head_dim + 1] = d;
             }
-#pragma unroll
-            for (int nt = 0; nt < 2; nt++) {
-                const int key = warp * 16 + nt * 8 + 2 * t;
-                ss[g * kTcTile + key] = key < nvalid ? s[nt][0] : -INFINITY;
-                ss[g * kTcTile + key + 1] = key + 1 < nvalid ? s[nt][1] : -INFINITY;
-            }
-        }
-        __syncthreads();
-
-        // ---- online softmax for head g over the 64 keys (every warp computes the same).
-        float pv[4][4];  // [k-step][slot pair element]: keys 16*ks + {2t, 2t+1, 2t+8, 2t+9}
-        float tmax = -INFINITY;
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-            const float2 a = *reinterpret_cast<const float2 *>(&ss[g * kTcTile + ks * 16 + 2 * t]);
-            const float2 b =
-                *reinterpret_cast<const float2 *>(&ss[g * kTcTile + ks * 16 + 2 * t + 8]);
-            pv[ks][0] = a.x; pv[ks][1] = a.y; pv[ks][2] = b.x; pv[ks][3] = b.y;
-            tmax = fmaxf(tmax, fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)));
-        }
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-        const float m_new = fmaxf(m_run, tmax);
-        // m_new is -inf only while every key so far was masked: nothing to scale then.
-        const float corr = (m_new == -INFINITY) ? 1.0f : exp2f(m_run - m_new);
-        float psum = 0.0f;
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float w = (pv[ks][e] == -INFINITY) ? 0.0f : exp2f(pv[ks][e] - m_new);
-                pv[ks][e] = w;
-                psum += w;
-            }
-        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-        l_run = l_run * corr + psum;
-        m_run = m_new;
-#pragma unroll
-        for (int a = 0; a < 2; a++)
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int c = 0; c < 4; c++) acc[a][i][c] *= corr;
-
-        // ---- values: warp w owns blocks 2w, 2w+1 (64 dims) for all 64 keys.
-#pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-            const int k0 = ks * 16 + 2 * t;  // keys k0, k0+1, k0+8, k0+9
-            const unsigned char *r[4] = {vtile[buf] + (k0)*kTcRowBytes,
-                                         vtile[buf] + (k0 + 1) * kTcRowBytes,
-                                         vtile[buf] + (k0 + 8) * kTcRowBytes,
-                                         vtile[buf] + (k0 + 9) * kTcRowBytes};
-            const bool ok[4] = {k0 < nvalid, k0 + 1 < nvalid, k0 + 8 < nvalid, k0 + 9 < nvalid};
-            // weights scaled by 2^10 and split into f16 high + low
-            __half ph[4], pl[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float w = pv[ks][e] * kPScale;
-                ph[e] = __float2half_rn(w);
-                pl[e] = __float2half_rn(w - __half2float(ph[e]));
-            }
-            const __half2 ph01 = __halves2half2(ph[0], ph[1]), ph23 = __halves2half2(ph[2], ph[3]);
-            const __half2 pl01 = __halves2half2(pl[0], pl[1]), pl23 = __halves2half2(pl[2], pl[3]);
-#pragma unroll
-            for (int a = 0; a < 2; a++) {
-                const int blk = warp * 2 + a;
-                // A = weight * block scale (exact product kept as high + low halves)
-                __half dv[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const unsigned short raw =
-                        *reinterpret_cast<const unsigned short *>(r[e] + blk * kQ8BlockBytes);
-                    dv[e] = ok[e] ? __ushort_as_half(raw) : __ushort_as_half(0);
-                }
-                const __half2 d01 = __halves2half2(dv[0], dv[1]), d23 = __halves2half2(dv[2], dv[3]);
-                const __half2 h01 = __hmul2(ph01, d01), h23 = __hmul2(ph23, d23);
-                const __half2 l01 = __hfma2(pl01, d01, __hfma2(ph01, d01, __hneg2(h01)));
-                const __half2 l23 = __hfma2(pl23, d23, __hfma2(ph23, d23, __hneg2(h23)));
-                unsigned afrag[4];
-                afrag[0] = *reinterpret_cast<const unsigned *>(&h01);
-                afrag[1] = *reinterpret_cast<const unsigned *>(&l01);
-                afrag[2] = *reinterpret_cast<const unsigned *>(&h23);
-                afrag[3] = *reinterpret_cast<const unsigned *>(&l23);
-                // B: logical word g of the block from each of the four keys
-                unsigned w[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    w[e] = block_word(reinterpret_cast<const unsigned *>(r[e]), blk, g) ^ 0x80808080u;
-                const unsigned ab01 = __byte_perm(w[0], w[1], 0x5140);  // [a0 b0 a1 b1]
-                const unsigned ab23 = __byte_perm(w[0], w[1], 0x7362);  // [a2 b2 a3 b3]
-                const unsigned cd01 = __byte_perm(w[2], w[3], 0x5140);
-                const unsigned cd23 = __byte_perm(w[2], w[3], 0x7362);
-                mma_16816(acc[a][0], afrag, codes_to_half2(ab01, 0x4140), codes_to_half2(cd01, 0x4140));
-                mma_16816(acc[a][1], afrag, codes_to_half2(ab01, 0x4342), codes_to_half2(cd01, 0x4342));
-                mma_16816(acc[a][2], afrag, codes_to_half2(ab23, 0x4140), codes_to_half2(cd23, 0x4140));
-                mma_16816(acc[a][3], afrag, codes_to_half2(ab23, 0x4342), codes_to_half2(cd23, 0x4342));
-            }
-        }
-        __syncthreads();  // tile buffers and ss are reused by the next iteration
-    }
-
-    // ---- partials: head g's row is c0/c1 (high part) + c2/c3 (low part).
-    if (g < group) {
-        const int h = kvh * group + g;
-        float *pa = p.part_acc + (size_t)slot * p.acc_slot + ((size_t)h * p.splits + split) * 256;
-        const float inv = 1.0f / kPScale;
-#pragma unroll
-        for (int a = 0; a < 2; a++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int blk = warp * 2 + a;
-                pa[block_word_dim(blk, 2 * t, i)] = (acc[a][i][0] + acc[a][i][2]) * inv;
-                pa[block_word_dim(blk, 2 * t + 1, i)] = (acc[a][i][1] + acc[a][i][3]) * inv;
-            }
-        if (warp == 0 && t == 0) {
-            float *pm = p.part_ml + (size_t)slot * p.ml_slot + ((size_t)h * p.splits + split) * 2;
-            pm[0] = m_run;
-            pm[1] = l_run;
         }
     }
 }
@@ -459,27 +210,42 @@ extern "C" __global__ void attn_decode_kv_reduce_b(const float *__restrict__ par
     out[(size_t)slot * out_slot + (size_t)h * head_dim + d] = den > 0.0f ? num / den : 0.0f;
 }
 
-// Host-side launch of the split pass; the reduce is launched by the caller.
+// Host-side launch of the split pass.
 int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, bool tensor_core) {
-    if (tensor_core) {
-        static bool configured[64] = {};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && !configured[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(attn_decode_kv_tc,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 kTcSmemBytes);
-            if (e != cudaSuccess) return (int)e;
-            configured[dev] = true;
-        }
-        dim3 grid(p.n_kv * p.splits, slots);
-        attn_decode_kv_tc<<<grid, kTcThreads, kTcSmemBytes, stream>>>(p);
-    } else {
-        const int warps = p.n_heads * p.splits;
-        dim3 grid((warps + 3) / 4, slots);
-        attn_decode_kv_scalar<<<grid, 128, 0, stream>>>(p);
-    }
+    if (tensor_core) return launch_decode_tc(stream, p, slots);
+    const int warps = p.n_heads * p.splits;
+    dim3 grid((warps + 3) / 4, slots);
+    attn_decode_kv_scalar<<<grid, 128, 0, stream>>>(p);
     return launch_status();
+}
+
+// Host-side launch of the fold.
+int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots) {
+    dim3 grid(n_heads * (p.head_dim >> 5), slots);
+    attn_decode_fold<<<grid, 256, 0, stream>>>(p);
+    return launch_status();
+}
+
+// The usual case: partials [n_heads][splits][head_dim] / [n_heads][splits][2] -> out[slot][h][d].
+int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
+                         float *out, int n_heads, int head_dim, int splits, int slots,
+                         long long acc_slot, long long ml_slot, long long out_slot) {
+    FoldParams p;
+    p.acc = part_acc;
+    p.ml = part_ml;
+    p.out = out;
+    p.head_dim = head_dim;
+    p.splits = splits;
+    p.acc_head_stride = (long long)splits * head_dim;
+    p.acc_split_stride = head_dim;
+    p.ml_head_stride = (long long)splits * 2;
+    p.ml_split_stride = 2;
+    p.acc_slot = acc_slot;
+    p.ml_slot = ml_slot;
+    p.out_slot = out_slot;
+    p.out_head_stride = head_dim;
+    p.normalize = 1;
+    return launch_decode_fold(stream, p, n_heads, slots);
 }
 
 const void *lookup_decode_kernel(const char *name) {

@@ -1,0 +1,364 @@
+// Split-K flash-decode over the q8_0 cache, tensor-core body (head_dim 256).
+//
+// A CTA of 8 warps owns one (KV head, split[, slot]) and streams its rows through a
+// double-buffered shared-memory ring with 16-byte asynchronous copies: rows are 272 B,
+// 16-byte aligned, and consecutive positions of one head are contiguous, so a 64-key tile
+// of K (or V) is one linear 17 KB run. Both contractions run on the tensor cores
+// (mma.sync m16n8k16, f16 operands, f32 accumulate) with operands built in registers:
+//   * int8 codes are exact in f16 (0x6400 | (code ^ 0x80) is 1152 + code);
+//   * the query and the softmax weights are split into f16 high + low parts stacked along
+//     M (rows 0..7 high, rows 8..15 low of the same head), so one MMA carries both;
+//   * the per-block f16 scales are applied in f32: on the K side to the 32-wide partial dot
+//     products, on the V side folded into the weight operand (weight * scale kept as an
+//     exact f16 high + low pair).
+// Results agree with the f32 definition to ~1e-6. The CUDA cores only unpack bytes: at 12
+// f32 FMA per cache byte a scalar kernel cannot keep up with HBM3e.
+//
+// Per tile: (1) scores -- warp (kg, dh) computes the partial scores of keys [16kg, 16kg+16)
+// over blocks [4dh, 4dh+4); (2) softmax -- warp g owns query head g of the group: running
+// max / sum, weights written once to shared memory as f16 high/low; (3) values -- warp w
+// owns block w (32 dims) for all 64 keys. CPU definition: crates/hipml-core/src/ops.rs:
+// 449-518; kernel replaced: crates/hipml-kernels/kernels/attn_decode_kv_w.hip:92-285 and
+// attn_decode_kv.hip:251-374,427-484.
+#include "params.cuh"
+
+namespace hipml {
+
+namespace {
+
+constexpr int kTile = 64;                        // keys per shared-memory tile
+constexpr int kRowBytes = 8 * kQ8BlockBytes;     // 272
+constexpr int kTileBytes = kTile * kRowBytes;    // 17408
+constexpr int kThreads = 256;
+constexpr int kSsStride = 72;                    // padded row of the score tile (floats)
+constexpr int kPStride = 72;                     // padded row of the weight tile (halves)
+constexpr float kPScale = 1024.0f;               // keeps weight*scale in f16's normal range
+
+// Dynamic shared memory: K[2] | V[2] | scores [2][8][72] f32 | weights hi, lo [8][72] f16 |
+// corr[8] f32. The query staging area [8][256] f32 aliases V[1] during set-up.
+constexpr int kOffSs = 4 * kTileBytes;
+constexpr int kOffPh = kOffSs + 2 * 8 * kSsStride * 4;
+constexpr int kOffPl = kOffPh + 8 * kPStride * 2;
+constexpr int kOffCorr = kOffPl + 8 * kPStride * 2;
+constexpr int kSmemBytes = kOffCorr + 8 * 4;
+
+__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0,
+                                          unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// K side: the eight "logical words" (four codes each) of block blk, all 4-byte aligned loads.
+// Odd blocks start 2 bytes past a word boundary, so word j holds codes 4j..4j+3. Even blocks
+// start on a word boundary (the scale shares a word with codes 0,1): words 0..6 hold codes
+// 4j+2..4j+5 and word 7 is stitched from codes 0,1 and 30,31. The order of elements inside
+// the contraction is free as long as the query operand uses the same one.
+template <int BLK, int KK>
+__device__ __forceinline__ unsigned k_word(const unsigned *row, int t) {
+    constexpr int m = BLK >> 1;
+    if constexpr (BLK & 1) {
+        return row[17 * m + 9 + KK * 4 + t];
+    } else if constexpr (KK == 0) {
+        return row[17 * m + 1 + t];
+    } else {
+        // j = 4 + t; j == 7 is the stitched word. Branch-free: two loads and a permute.
+        const bool last = t == 3;
+        const unsigned a = row[last ? 17 * m : 17 * m + 5 + t];
+        const unsigned b = row[last ? 17 * m + 8 : 17 * m + 5 + t];
+        return __byte_perm(a, b, last ? 0x5432 : 0x3210);
+    }
+}
+
+// head_dim index of byte i of logical word j of block blk, in k_word's order.
+__device__ __forceinline__ int k_word_dim(int blk, int j, int i) {
+    if (blk & 1) return blk * 32 + 4 * j + i;
+    if (j < 7) return blk * 32 + 4 * j + 2 + i;
+    return blk * 32 + (i < 2 ? i : 28 + i);
+}
+
+// V side: codes 4j..4j+3 of block blk in natural order (two loads and a permute for even
+// blocks, whose codes straddle word boundaries).
+__device__ __forceinline__ unsigned v_word(const unsigned *row, int blk, int j) {
+    const int m = blk >> 1;
+    if (blk & 1) return row[17 * m + 9 + j];
+    return __byte_perm(row[17 * m + j], row[17 * m + j + 1], 0x5432);
+}
+
+// Bytes lo/hi of `biased` (code ^ 0x80) as an exact half2: 0x64xx is 1024 + xx, minus 1152.
+__device__ __forceinline__ unsigned codes_to_half2(unsigned biased, unsigned selector) {
+    const unsigned h = __byte_perm(biased, 0x64646464u, selector);
+    const __half2 r =
+        __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half(0x6480)));
+    return *reinterpret_cast<const unsigned *>(&r);
+}
+
+__device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
+    const __half2 r = __halves2half2(lo, hi);
+    return *reinterpret_cast<const unsigned *>(&r);
+}
+
+__device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int &lo,
+                                            int &hi) {
+    const int len = p.len[slot * p.len_stride + p.len_offset];
+    const int span = p.by_stride ? p.stride : len;
+    const int per = (span + p.splits - 1) / p.splits;
+    lo = min(split * per, len);
+    hi = min(lo + per, len);
+}
+
+// Scores of one block for this warp's 16 keys (two n-tiles), added into s.
+template <int BLK>
+__device__ __forceinline__ void score_block(const unsigned char *ktile, int key_base, int g, int t,
+                                            const unsigned (&qa0)[4], const unsigned (&qa1)[4],
+                                            float (&s)[2][2]) {
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+        const unsigned *row =
+            reinterpret_cast<const unsigned *>(ktile + (key_base + nt * 8 + g) * kRowBytes);
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const unsigned w0 = k_word<BLK, 0>(row, t) ^ 0x80808080u;
+        mma_16816(c, qa0, codes_to_half2(w0, 0x4140), codes_to_half2(w0, 0x4342));
+        const unsigned w1 = k_word<BLK, 1>(row, t) ^ 0x80808080u;
+        mma_16816(c, qa1, codes_to_half2(w1, 0x4140), codes_to_half2(w1, 0x4342));
+        const unsigned char *r0 = ktile + (key_base + nt * 8 + 2 * t) * kRowBytes + BLK * kQ8BlockBytes;
+        const float d0 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(r0));
+        const float d1 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(r0 + kRowBytes));
+        s[nt][0] += d0 * (c[0] + c[2]);
+        s[nt][1] += d1 * (c[1] + c[3]);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    unsigned char *ktile[2] = {smem, smem + kTileBytes};
+    unsigned char *vtile[2] = {smem + 2 * kTileBytes, smem + 3 * kTileBytes};
+    float *qs = reinterpret_cast<float *>(vtile[1]);                 // set-up only
+    float *ss = reinterpret_cast<float *>(smem + kOffSs);            // [2][8][kSsStride]
+    __half *ph = reinterpret_cast<__half *>(smem + kOffPh);          // [8][kPStride]
+    __half *pl = reinterpret_cast<__half *>(smem + kOffPl);
+    float *corr_s = reinterpret_cast<float *>(smem + kOffCorr);      // [8]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int slot = blockIdx.y;
+    const int kvh = blockIdx.x / p.splits, split = blockIdx.x - kvh * p.splits;
+    const int group = p.n_heads / p.n_kv;
+    const int kg = warp & 3, dh = warp >> 2;
+
+    int lo, hi;
+    split_range(p, slot, split, lo, hi);
+    const int ntiles = (hi - lo + kTile - 1) / kTile;
+
+    const size_t head_byte = (size_t)slot * p.kv_slot_bytes + q8_row_offset(kvh, p.stride, 0, 256);
+    const unsigned char *kbase = p.k + head_byte;
+    const unsigned char *vbase = p.v + head_byte;
+
+    auto prefetch = [&](int tile, int buf) {
+        const int r0 = lo + tile * kTile;
+        const int nrows = min(kTile, hi - r0);
+        const size_t off = (size_t)r0 * kRowBytes;
+        const int chunks = nrows * (kRowBytes / 16);
+        for (int i = tid; i < chunks; i += kThreads) {
+            cp_async_16(ktile[buf] + i * 16, kbase + off + (size_t)i * 16);
+            cp_async_16(vtile[buf] + i * 16, vbase + off + (size_t)i * 16);
+        }
+        cp_async_commit();
+    };
+    if (ntiles > 0) prefetch(0, 0);
+
+    // Query rows of this KV head's group in log2 units; rows past the group are zero.
+    const float *q = p.q + (size_t)slot * p.q_slot + (size_t)kvh * group * 256;
+    for (int i = tid; i < 8 * 256; i += kThreads)
+        qs[i] = (i >> 8) < group ? q[i] * p.scale_log2 : 0.0f;
+    __syncthreads();
+
+    // A fragments of the query for this warp's four blocks: rows 0..7 carry the f16 high
+    // part of head g, rows 8..15 the low part; contraction slots follow k_word's order.
+    unsigned qa[8][4];
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+        const int blk = dh * 4 + (ks >> 1), j = (ks & 1) * 4 + t;
+        __half xh[4], xl[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float x = qs[g * 256 + k_word_dim(blk, j, i)];
+            xh[i] = __float2half_rn(x);
+            xl[i] = __float2half_rn(x - __half2float(xh[i]));
+        }
+        qa[ks][0] = pack_half2(xh[0], xh[1]);
+        qa[ks][1] = pack_half2(xl[0], xl[1]);
+        qa[ks][2] = pack_half2(xh[2], xh[3]);
+        qa[ks][3] = pack_half2(xl[2], xl[3]);
+    }
+    __syncthreads();  // qs aliases V[1]: every warp is done with it before tile 1 is fetched
+
+    float acc[4][4];  // block `warp`: [byte i of the code word][c0..c3]
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[i][c] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;  // meaningful in warp g' = head of the group
+
+    for (int tile = 0; tile < ntiles; tile++) {
+        const int buf = tile & 1;
+        if (tile + 1 < ntiles) {
+            prefetch(tile + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        const int nvalid = min(kTile, hi - (lo + tile * kTile));
+        __syncthreads();
+        if (nvalid < kTile) {
+            // Rows past the split's end hold stale bytes; their V scales must read as zero.
+            for (int i = tid; i < (kTile - nvalid) * (kRowBytes / 16); i += kThreads)
+                reinterpret_cast<uint4 *>(vtile[buf] + nvalid * kRowBytes)[i] = make_uint4(0, 0, 0, 0);
+        }
+
+        // ---- (1) scores
+        {
+            float s[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+            if (dh == 0) {
+                score_block<0>(ktile[buf], kg * 16, g, t, qa[0], qa[1], s);
+                score_block<1>(ktile[buf], kg * 16, g, t, qa[2], qa[3], s);
+                score_block<2>(ktile[buf], kg * 16, g, t, qa[4], qa[5], s);
+                score_block<3>(ktile[buf], kg * 16, g, t, qa[6], qa[7], s);
+            } else {
+                score_block<4>(ktile[buf], kg * 16, g, t, qa[0], qa[1], s);
+                score_block<5>(ktile[buf], kg * 16, g, t, qa[2], qa[3], s);
+                score_block<6>(ktile[buf], kg * 16, g, t, qa[4], qa[5], s);
+                score_block<7>(ktile[buf], kg * 16, g, t, qa[6], qa[7], s);
+            }
+            float *dst = ss + (dh * 8 + g) * kSsStride + kg * 16 + 2 * t;
+            *reinterpret_cast<float2 *>(dst) = make_float2(s[0][0], s[0][1]);
+            *reinterpret_cast<float2 *>(dst + 8) = make_float2(s[1][0], s[1][1]);
+        }
+        __syncthreads();
+
+        // ---- (2) softmax: warp = head of the group, lane = keys 2*lane, 2*lane+1
+        {
+            const float2 a = *reinterpret_cast<const float2 *>(ss + warp * kSsStride + 2 * lane);
+            const float2 b = *reinterpret_cast<const float2 *>(ss + (8 + warp) * kSsStride + 2 * lane);
+            const float s0 = 2 * lane < nvalid ? a.x + b.x : -INFINITY;
+            const float s1 = 2 * lane + 1 < nvalid ? a.y + b.y : -INFINITY;
+            const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
+            // m_new is -inf only while every key so far was masked: nothing to scale then.
+            const float corr = (m_new == -INFINITY) ? 1.0f : exp2f(m_run - m_new);
+            const float p0 = (s0 == -INFINITY) ? 0.0f : exp2f(s0 - m_new);
+            const float p1 = (s1 == -INFINITY) ? 0.0f : exp2f(s1 - m_new);
+            l_run = l_run * corr + warp_sum(p0 + p1);
+            m_run = m_new;
+            const float w0 = p0 * kPScale, w1 = p1 * kPScale;
+            const __half h0 = __float2half_rn(w0), h1 = __float2half_rn(w1);
+            const __half l0 = __float2half_rn(w0 - __half2float(h0));
+            const __half l1 = __float2half_rn(w1 - __half2float(h1));
+            *reinterpret_cast<unsigned *>(ph + warp * kPStride + 2 * lane) = pack_half2(h0, h1);
+            *reinterpret_cast<unsigned *>(pl + warp * kPStride + 2 * lane) = pack_half2(l0, l1);
+            if (lane == 0) corr_s[warp] = corr;
+        }
+        __syncthreads();
+
+        // ---- (3) values: warp = block (32 dims), all 64 keys
+        {
+            const float corr = corr_s[g];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) acc[i][c] *= corr;
+            const int blk = warp;
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                const int k0 = ks * 16 + 2 * t;  // keys k0, k0+1, k0+8, k0+9
+                const unsigned char *r0 = vtile[buf] + k0 * kRowBytes;
+                const unsigned char *r[4] = {r0, r0 + kRowBytes, r0 + 8 * kRowBytes, r0 + 9 * kRowBytes};
+                // A = weight * block scale, kept as an exact f16 high + low pair
+                __half dv[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    dv[e] = __ushort_as_half(
+                        *reinterpret_cast<const unsigned short *>(r[e] + blk * kQ8BlockBytes));
+                const __half2 d01 = __halves2half2(dv[0], dv[1]), d23 = __halves2half2(dv[2], dv[3]);
+                const __half2 ph01 = *reinterpret_cast<const __half2 *>(ph + g * kPStride + k0);
+                const __half2 ph23 = *reinterpret_cast<const __half2 *>(ph + g * kPStride + k0 + 8);
+                const __half2 pl01 = *reinterpret_cast<const __half2 *>(pl + g * kPStride + k0);
+                const __half2 pl23 = *reinterpret_cast<const __half2 *>(pl + g * kPStride + k0 + 8);
+                const __half2 h01 = __hmul2(ph01, d01), h23 = __hmul2(ph23, d23);
+                const __half2 l01 = __hfma2(pl01, d01, __hfma2(ph01, d01, __hneg2(h01)));
+                const __half2 l23 = __hfma2(pl23, d23, __hfma2(ph23, d23, __hneg2(h23)));
+                unsigned afrag[4];
+                afrag[0] = *reinterpret_cast<const unsigned *>(&h01);
+                afrag[1] = *reinterpret_cast<const unsigned *>(&l01);
+                afrag[2] = *reinterpret_cast<const unsigned *>(&h23);
+                afrag[3] = *reinterpret_cast<const unsigned *>(&l23);
+                // B: code word g of the block (dims 32*blk + 4g .. +3) from each of the four keys
+                unsigned w[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    w[e] = v_word(reinterpret_cast<const unsigned *>(r[e]), blk, g) ^ 0x80808080u;
+                const unsigned ab01 = __byte_perm(w[0], w[1], 0x5140);  // [a0 b0 a1 b1]
+                const unsigned ab23 = __byte_perm(w[0], w[1], 0x7362);  // [a2 b2 a3 b3]
+                const unsigned cd01 = __byte_perm(w[2], w[3], 0x5140);
+                const unsigned cd23 = __byte_perm(w[2], w[3], 0x7362);
+                mma_16816(acc[0], afrag, codes_to_half2(ab01, 0x4140), codes_to_half2(cd01, 0x4140));
+                mma_16816(acc[1], afrag, codes_to_half2(ab01, 0x4342), codes_to_half2(cd01, 0x4342));
+                mma_16816(acc[2], afrag, codes_to_half2(ab23, 0x4140), codes_to_half2(cd23, 0x4140));
+                mma_16816(acc[3], afrag, codes_to_half2(ab23, 0x4342), codes_to_half2(cd23, 0x4342));
+            }
+        }
+        __syncthreads();  // tile buffers, ss and the weight tile are reused by the next tile
+    }
+
+    // ---- partials. Output column n of MMA i is dim 32*blk + 4n + i; this thread holds
+    // columns 2t, 2t+1, i.e. dims 32*blk + 8t + i and 32*blk + 8t + 4 + i of head g
+    // (c0/c1: high-part row, c2/c3: low-part row).
+    if (g < group) {
+        const int h = kvh * group + g;
+        float *pa = p.part_acc + (size_t)slot * p.acc_slot + ((size_t)h * p.splits + split) * 256 +
+                    warp * 32 + 8 * t;
+        const float inv = 1.0f / kPScale;
+        *reinterpret_cast<float4 *>(pa) =
+            make_float4((acc[0][0] + acc[0][2]) * inv, (acc[1][0] + acc[1][2]) * inv,
+                        (acc[2][0] + acc[2][2]) * inv, (acc[3][0] + acc[3][2]) * inv);
+        *reinterpret_cast<float4 *>(pa + 4) =
+            make_float4((acc[0][1] + acc[0][3]) * inv, (acc[1][1] + acc[1][3]) * inv,
+                        (acc[2][1] + acc[2][3]) * inv, (acc[3][1] + acc[3][3]) * inv);
+    }
+    if (warp < group && lane == 0) {
+        const int h = kvh * group + warp;
+        float *pm = p.part_ml + (size_t)slot * p.ml_slot + ((size_t)h * p.splits + split) * 2;
+        pm[0] = m_run;
+        pm[1] = l_run;
+    }
+}
+
+}  // namespace
+
+int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kv_tc,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+    dim3 grid(p.n_kv * p.splits, slots);
+    attn_decode_kv_tc<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    return launch_status();
+}
+
+}  // namespace hipml

@@ -101,10 +101,10 @@ int hipml_kv_append_chunk_f32(hipml_stream_t stream, float *k_cache, float *v_ca
                                  dim3(256), args, 0, as_stream(stream));
 }
 
-int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
-                         const void *k, const void *v, float *part_acc, float *part_ml,
-                         float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
-                         int splits, size_t k_off, size_t v_off) {
+static int decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
+                     const void *k, const void *v, float *part_acc, float *part_ml, float *out,
+                     int n_heads, int n_kv, int head_dim, int stride, float scale, int splits,
+                     size_t k_off, size_t v_off, bool shard) {
     if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
     // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
     // experimental variants have no counterpart here.
@@ -145,10 +145,59 @@ int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, c
     if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
     if (int e = launch_decode_split(as_stream(stream), p, 1, tensor_core)) return e;
-    const float *pa = part_acc, *pm = part_ml;
-    void *args[] = {&pa, &pm, &out, &head_dim, &splits};
-    return (int)cudaLaunchKernel(lookup_decode_kernel("attn_decode_kv_reduce"), dim3(n_heads),
-                                 dim3(head_dim), args, 0, as_stream(stream));
+    if (!shard)
+        return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
+                                    splits, 1, 0, 0, 0);
+    FoldParams f;
+    f.acc = part_acc;
+    f.ml = part_ml;
+    f.out = out;
+    f.head_dim = head_dim;
+    f.splits = splits;
+    f.acc_head_stride = (long long)splits * head_dim;
+    f.acc_split_stride = head_dim;
+    f.ml_head_stride = (long long)splits * 2;
+    f.ml_split_stride = 2;
+    f.acc_slot = f.ml_slot = f.out_slot = 0;
+    f.out_head_stride = head_dim + 2;
+    f.normalize = 0;
+    return launch_decode_fold(as_stream(stream), f, n_heads, 1);
+}
+
+int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
+                         const void *k, const void *v, float *part_acc, float *part_ml,
+                         float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
+                         int splits, size_t k_off, size_t v_off) {
+    return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
+                     head_dim, stride, scale, splits, k_off, v_off, false);
+}
+
+int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selector,
+                               const float *q, const void *k, const void *v, float *part_acc,
+                               float *part_ml, float *shard_out, int n_heads, int n_kv,
+                               int head_dim, int stride, float scale, int splits, size_t k_off,
+                               size_t v_off) {
+    return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, shard_out, n_heads, n_kv,
+                     head_dim, stride, scale, splits, k_off, v_off, true);
+}
+
+int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, float *out,
+                              int n_heads, int head_dim, int shards) {
+    if (n_heads <= 0 || shards <= 0 || head_dim % 32 != 0 || head_dim < 32 || head_dim > 256)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "combine: n_heads %d / head_dim %d / shards %d",
+                    n_heads, head_dim, shards);
+    FoldParams f;
+    f.acc = gathered;
+    f.ml = gathered + head_dim;
+    f.out = out;
+    f.head_dim = head_dim;
+    f.splits = shards;
+    f.acc_head_stride = f.ml_head_stride = head_dim + 2;
+    f.acc_split_stride = f.ml_split_stride = (long long)n_heads * (head_dim + 2);
+    f.acc_slot = f.ml_slot = f.out_slot = 0;
+    f.out_head_stride = head_dim;
+    f.normalize = 1;
+    return launch_decode_fold(as_stream(stream), f, n_heads, 1);
 }
 
 static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,
@@ -188,10 +237,8 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
          15) == 0;
     const bool tensor_core = head_dim == 256 && aligned;
     if (int e = launch_decode_split(as_stream(stream), p, slots, tensor_core)) return e;
-    const float *pa = part_acc, *pm = part_ml;
-    void *args[] = {&pa, &pm, &out, &head_dim, &splits, &acc_slot, &ml_slot, &q_slot};
-    return (int)cudaLaunchKernel(lookup_decode_kernel("attn_decode_kv_reduce_b"),
-                                 dim3(n_heads, slots), dim3(head_dim), args, 0, as_stream(stream));
+    return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim, splits,
+                                slots, acc_slot, ml_slot, q_slot);
 }
 
 int hipml_attn_decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,

@@ -24,6 +24,22 @@ struct DecodeParams {
 };
 // Launches the split pass (the caller launches the reduce).
 int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, bool tensor_core);
+int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots);
+// Fold of (acc, max, sum) triples over the split axis; all strides in floats.
+struct FoldParams {
+    const float *acc;
+    const float *ml;   // (max in log2 units, sum) pairs
+    float *out;
+    int head_dim, splits;
+    long long acc_head_stride, acc_split_stride, ml_head_stride, ml_split_stride;
+    long long acc_slot, ml_slot, out_slot, out_head_stride;
+    int normalize;     // 1: out = acc/sum; 0: out row = [acc (unnormalised) | max | sum]
+};
+int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots);
+// Folds the partials into out[slot][h][d] (slot strides in floats).
+int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
+                         float *out, int n_heads, int head_dim, int splits, int slots,
+                         long long acc_slot, long long ml_slot, long long out_slot);
 
 // Scalar chunk attention (attn_chunk_scalar.cu).
 struct ChunkScalarParams {

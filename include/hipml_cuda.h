@@ -174,6 +174,23 @@ int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, c
                          float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
                          int splits, size_t k_off, size_t v_off);
 
+/* Sequence-split decode across GPUs (no counterpart in the reference, which is single-GPU; the
+ * algebra is its split-K reduce, crates/hipml-kernels/kernels/attn_decode_kv.hip:491-532, lifted
+ * from thread blocks to devices). Each GPU holds a contiguous range of every KV head's positions
+ * in its own cache and runs hipml_attn_decode_kv_shard: same arguments as hipml_attn_decode_kv
+ * (step[1] = the live length of the LOCAL cache, 0 allowed), but instead of the normalised
+ * output it writes the folded triple of its shard: shard_out f32 [n_heads][head_dim + 2] =
+ * (unnormalised acc[head_dim], max in log2 units, sum). The shards' rows are exchanged with any
+ * all-gather (NCCL) into gathered f32 [shards][n_heads][head_dim + 2], and
+ * hipml_attn_decode_combine folds them into out f32 [n_heads][head_dim]. */
+int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selector,
+                               const float *q, const void *k, const void *v, float *part_acc,
+                               float *part_ml, float *shard_out, int n_heads, int n_kv,
+                               int head_dim, int stride, float scale, int splits, size_t k_off,
+                               size_t v_off);
+int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, float *out,
+                              int n_heads, int head_dim, int shards);
+
 /* Launcher::attn_decode_rows_ptr (batch_launch.rs:213-316): multi-slot decode. Slot s reads
  * q + s*q_slot, caches + s*kv_slot_bytes, pos[2*s+1] as its live length, and writes
  * part_acc + s*acc_slot, part_ml + s*ml_slot, out + s*q_slot. The key axis is cut into

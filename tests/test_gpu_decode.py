@@ -202,3 +202,38 @@ def test_decode_argument_errors():
         api.attn_decode_kv(step, z, c, c, z, z, z, 8, 2, 64, 8, 0.125, 1, selector=4)
     with pytest.raises(_lib.HipmlError, match="unknown KV dtype 9"):
         api.attn_decode_kv(step, z, c, c, z, z, z, 24, 4, 256, 8, 0.0625, 1, selector=9)
+
+
+@pytest.mark.parametrize("shards,seq", [(2, 700), (3, 100), (8, 5)])
+def test_sequence_split_shards_fold_to_the_whole_cache(shards, seq):
+    """The multi-GPU decode path on one GPU: every shard's rows live in their own cache, each
+    is folded to its (acc, max, sum) triple, and the combine of the triples must equal the
+    attention over the whole cache (shards with no live rows contribute nothing)."""
+    from hipml_b200 import api, sharding
+    heads, n_kv, hd, scale = 24, 4, 256, 0.0625
+    capacity = seq + 9
+    rng = O.Rng(0x5A4D + shards)
+    q = rng.normals(heads * hd)
+    kb = O.quantize_q8(rng.normals(n_kv * seq * hd)).reshape(n_kv, seq, 272)
+    vb = O.quantize_q8(rng.normals(n_kv * seq * hd)).reshape(n_kv, seq, 272)
+    expected = O.attn_decode_kv_q8(q, kb, vb, heads, n_kv, hd, seq, scale)
+    gathered = torch.full((shards, heads, hd + 2), float("nan"), device="cuda")
+    dq = _dev(q)
+    for r in range(shards):
+        lo, hi = sharding.decode_shard_range(capacity, shards, r)
+        n = sharding.local_length(seq, lo, hi)
+        stride = max(hi - lo, 1)
+        kc, vc = _canary_cache(n_kv, stride, 272), _canary_cache(n_kv, stride, 272)
+        kc[:, :n], vc[:, :n] = kb[:, lo:lo + n], vb[:, lo:lo + n]
+        splits = api.decode_splits(max(n, 1))
+        acc = torch.full((heads * splits * hd,), float("nan"), device="cuda")
+        ml = torch.full((heads * splits * 2,), float("nan"), device="cuda")
+        api.attn_decode_kv_shard(_step(max(n - 1, 0), n), dq, _dev(kc), _dev(vc), acc, ml,
+                                 gathered[r], heads, n_kv, hd, stride, scale, splits)
+    out = torch.full((heads * hd,), float("nan"), device="cuda")
+    api.attn_decode_combine(gathered, out, heads, hd, shards)
+    torch.cuda.synchronize()
+    _assert_close(expected, out.cpu().numpy())
+    # the numpy mirror used by the CPU (gloo) tests folds the same triples to the same result
+    mirror = sharding.fold_triples(gathered.cpu().numpy())
+    assert O.max_abs(mirror.ravel(), out.cpu().numpy()) < 1e-6

@@ -1,0 +1,122 @@
+"""The multi-GPU partition on CPU: two gloo ranks stand in for two GPUs.
+
+Each rank holds its range of cache rows, folds them to one (acc, max, sum) triple per head
+with a numpy stand-in for the shard kernel, the triples are all-gathered over gloo and folded
+with the numpy mirror of the combine kernel; the result must equal the oracle's attention
+over the whole cache. The GPU tests check the kernels against the same mirrors.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle as O
+from hipml_b200 import sharding
+
+HEADS, N_KV, HD, SEQ, SCALE = 12, 2, 64, 301, 0.125
+ROW = HD // 32 * 34
+
+
+def _inputs():
+    rng = O.Rng(0x5EA)
+    q = rng.normals(HEADS * HD)
+    kb = O.quantize_q8(rng.normals(N_KV * SEQ * HD, 0.3)).reshape(N_KV, SEQ, ROW)
+    vb = O.quantize_q8(rng.normals(N_KV * SEQ * HD)).reshape(N_KV, SEQ, ROW)
+    return q, kb, vb
+
+
+def shard_triple(q, kb, vb, lo, n):
+    """numpy stand-in for hipml_attn_decode_kv_shard over local rows [lo, lo+n)."""
+    out = np.zeros((HEADS, HD + 2), dtype=np.float32)
+    out[:, HD] = -np.inf
+    if n == 0:
+        return out
+    group = HEADS // N_KV
+    log2e = np.float32(1.4426950408889634)
+    for h in range(HEADS):
+        k = O.dequantize_q8(kb[h // group, lo:lo + n]).reshape(n, HD)
+        v = O.dequantize_q8(vb[h // group, lo:lo + n]).reshape(n, HD)
+        s = (k @ q[h * HD:(h + 1) * HD]) * np.float32(SCALE) * log2e
+        m = s.max()
+        p = np.exp2(s - m).astype(np.float32)
+        out[h, :HD] = p @ v
+        out[h, HD], out[h, HD + 1] = m, p.sum()
+    return out
+
+
+def _worker(rank, world, port, capacity, seq, result):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    q, kb, vb = _inputs()
+    lo, hi = sharding.decode_shard_range(capacity, world, rank)
+    n = sharding.local_length(seq, lo, hi)
+    mine = torch.from_numpy(shard_triple(q, kb, vb, lo, n))
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    out = sharding.fold_triples(torch.stack(gathered).numpy())
+    if rank == 0:
+        result.put(out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("capacity,seq", [(SEQ, SEQ), (SEQ, 140), (400, SEQ)])
+def test_two_rank_sequence_split_decode_matches_the_oracle(capacity, seq):
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, capacity, seq, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = result.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    q, kb, vb = _inputs()
+    want = O.attn_decode_kv_q8(q, kb, vb, HEADS, N_KV, HD, seq, SCALE, stride=SEQ)
+    assert O.max_abs(want, out.ravel()) < 2e-6
+
+
+def test_partition_arithmetic():
+    # decode ranges tile [0, capacity) in order; each position has exactly one owner
+    for cap, world in [(100000, 8), (100136, 4), (7, 8), (672, 2)]:
+        edges = [sharding.decode_shard_range(cap, world, r) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == cap
+        assert all(a[1] == b[0] for a, b in zip(edges, edges[1:]))
+        assert max(hi - lo for lo, hi in edges) - min(hi - lo for lo, hi in edges) <= 1
+        for pos in (0, cap // 2, cap - 1):
+            r = sharding.decode_owner(pos, cap, world)
+            assert edges[r][0] <= pos < edges[r][1]
+        assert sum(sharding.local_length(cap - 3, lo, hi) for lo, hi in edges) == cap - 3
+    # prefill: KV heads first, then query halves that rotate with the chunk index
+    assert sharding.kv_head_shard(24, 4, 1, 0) == (1, 1, 0, 0, 4, 24)
+    assert sharding.kv_head_shard(24, 4, 4, 3) == (4, 1, 3, 0, 1, 6)
+    assert sharding.kv_head_shard(24, 4, 8, 6) == (4, 2, 2, 1, 1, 6)
+    with pytest.raises(ValueError):
+        sharding.kv_head_shard(24, 4, 3, 0)
+    for ci in range(4):
+        parts = [sharding.query_part(ci, 2048, 2, qi) for qi in range(2)]
+        assert sorted(parts) == [(0, 1024), (1024, 1024)]
+    assert sharding.query_part(0, 2048, 2, 0) != sharding.query_part(1, 2048, 2, 0)
+    parts = sorted(sharding.query_part(0, 1697, 2, qi) for qi in range(2))
+    assert parts == [(0, 849), (849, 848)]
+
+
+def test_fold_handles_empty_shards():
+    g = np.zeros((3, 2, 6), dtype=np.float32)
+    g[:, :, 4] = -np.inf
+    assert np.all(sharding.fold_triples(g) == 0.0)
+    g[1, :, :4] = [2.0, 4.0, 6.0, 8.0]
+    g[1, :, 4], g[1, :, 5] = 0.5, 2.0
+    assert np.allclose(sharding.fold_triples(g), [[1.0, 2.0, 3.0, 4.0]] * 2)
