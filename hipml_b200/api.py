@@ -81,6 +81,15 @@ def attn_decode_combine(gathered, out, n_heads, head_dim, shards):
         _stream(), _p(gathered), _p(out), n_heads, head_dim, shards))
 
 
+def attn_decode_kv_static(step, q, k, v, out, n_heads, n_kv, head_dim, stride, scale, splits,
+                          selector=0, k_off=0, v_off=0):
+    """attn_decode_kv without caller scratch: for callers that cannot allocate device memory.
+    The partials live in a 6 MiB array inside the library; calls must not overlap on the GPU."""
+    _lib.check("attn_decode_kv_static", _lib.load().hipml_attn_decode_kv_static(
+        _stream(), _p(step), selector, _p(q), _p(k), _p(v), _p(out), n_heads, n_kv, head_dim,
+        stride, scale, splits, k_off, v_off))
+
+
 def attn_decode_rows(pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads, n_kv, head_dim,
                      stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot, q_slot, slots,
                      dtype=0):

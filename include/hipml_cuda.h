@@ -191,6 +191,22 @@ int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selec
 int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, float *out,
                               int n_heads, int head_dim, int shards);
 
+/* The same decode for callers that cannot allocate device memory (this entry has no
+ * counterpart in the reference): a host that serves from a fixed arena and may not call
+ * cudaMalloc, a binding without a device allocator, a loop that must stay clear of the
+ * allocator. The split partials live in a device array inside the library image (6.05 MiB,
+ * held by every GPU that loads the library until the process exits) instead of caller
+ * buffers; inputs and the output are still the caller's. Limit: n_heads * splits *
+ * (head_dim + 2) <= 24 * 256 * 258 floats, otherwise HIPML_ERR_WORKSPACE and nothing runs.
+ * The first call on a device looks up the array's device address; make it before any stream
+ * capture. All calls share the array (it keeps the previous call's partials; nothing needs
+ * clearing because every slot that is folded is written first), so calls that overlap on the
+ * GPU race: keep them ordered on one stream or with events. No allocation is made here. */
+int hipml_attn_decode_kv_static(hipml_stream_t stream, const int *step, int selector,
+                                const float *q, const void *k, const void *v, float *out,
+                                int n_heads, int n_kv, int head_dim, int stride, float scale,
+                                int splits, size_t k_off, size_t v_off);
+
 /* Launcher::attn_decode_rows_ptr (batch_launch.rs:213-316): multi-slot decode. Slot s reads
  * q + s*q_slot, caches + s*kv_slot_bytes, pos[2*s+1] as its live length, and writes
  * part_acc + s*acc_slot, part_ml + s*ml_slot, out + s*q_slot. The key axis is cut into
