@@ -73,6 +73,8 @@ SIGNATURES = {
     "hipml_attn_decode_combine": (_i, [_vp, _vp, _vp, _i, _i, _i]),
     "hipml_attn_decode_kv_static": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i,
                                          _sz, _sz]),
+    "hipml_attn_decode_cols_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i]),
+    "hipml_kv_append_cols_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "hipml_attn_decode_rows": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f,
                                     _i, _i, _i, _i, _i, _i]),
     "hipml_attn_decode_batch": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,

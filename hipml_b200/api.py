@@ -90,6 +90,25 @@ def attn_decode_kv_static(step, q, k, v, out, n_heads, n_kv, head_dim, stride, s
         stride, scale, splits, k_off, v_off))
 
 
+def attn_decode_cols_f32(q, k_cache, v_cache, part_acc, part_ml, out, n_heads, n_kv, head_dim,
+                         n_ctx, pos0, rows):
+    """AttnLayer::attention_cols: f32-cache decode of `rows` consecutive columns."""
+    _lib.check("attention_cols", _lib.load().hipml_attn_decode_cols_f32(
+        _stream(), _p(q), _p(k_cache), _p(v_cache), _p(part_acc), _p(part_ml), _p(out), n_heads,
+        n_kv, head_dim, n_ctx, pos0, rows))
+
+
+def kv_append_cols_f32(k_cache, v_cache, k, v, pos0, rows, width):
+    """AttnLayer::append_rows."""
+    _lib.check("kv_append_cols_f32", _lib.load().hipml_kv_append_cols_f32(
+        _stream(), _p(k_cache), _p(v_cache), _p(k), _p(v), pos0, rows, width))
+
+
+def cols_splits(n_ctx: int) -> int:
+    """split_geom (crates/hipml-kernels/src/attn_gpu/imp/attn_cols.rs:15-20)."""
+    return min(max((n_ctx + 31) // 32, 1), 64)
+
+
 def attn_decode_rows(pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads, n_kv, head_dim,
                      stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot, q_slot, slots,
                      dtype=0):

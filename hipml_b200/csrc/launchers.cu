@@ -410,4 +410,35 @@ int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, i
     return 0;
 }
 
+int hipml_kv_append_cols_f32(hipml_stream_t stream, float *k_cache, float *v_cache,
+                             const float *k, const float *v, int pos0, int rows, int width) {
+    if (width <= 0 || rows < 0 || pos0 < 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "width %d / rows %d / pos0 %d", width, rows, pos0);
+    if (rows == 0) return 0;
+    const long long n = 2LL * width * rows;
+    void *args[] = {&k_cache, &v_cache, &k, &v, &pos0, &rows, &width};
+    return (int)cudaLaunchKernel(lookup_cols_kernel("kv_append_cols_f32"),
+                                 dim3((unsigned)((n + 255) / 256)), dim3(256), args, 0,
+                                 as_stream(stream));
+}
+
+int hipml_attn_decode_cols_f32(hipml_stream_t stream, const float *q, const float *k_cache,
+                               const float *v_cache, float *part_acc, float *part_ml, float *out,
+                               int n_heads, int n_kv, int head_dim, int n_ctx, int pos0,
+                               int rows) {
+    if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
+    if (n_ctx <= 0 || pos0 < 0 || rows < 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "n_ctx %d / pos0 %d / rows %d", n_ctx, pos0, rows);
+    if (pos0 + rows > n_ctx)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "position %d beyond KV cache %d", pos0 + rows, n_ctx);
+    if (rows == 0) return 0;
+    if (!part_acc || !part_ml)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "attention scratch: missing for %d columns", rows);
+    // split_geom (attn_cols.rs:15-20): one run per 32 cache rows, at most 64 runs
+    int splits = (n_ctx + 31) / 32;
+    splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
+    return launch_decode_cols_f32(as_stream(stream), q, k_cache, v_cache, part_acc, part_ml, out,
+                                  n_heads, n_kv, head_dim, n_ctx, pos0, rows, splits);
+}
+
 }  // extern "C"

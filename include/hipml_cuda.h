@@ -174,6 +174,23 @@ int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, c
                          float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
                          int splits, size_t k_off, size_t v_off);
 
+/* AttnLayer::attention_cols (crates/hipml-kernels/src/attn_gpu/imp/attn_cols.rs:66-173): split-K
+ * decode over the f32 position-major cache [n_ctx][n_kv*head_dim] for `rows` consecutive
+ * columns; column c is the query at position pos0 + c and sees cache rows 0..pos0+c. q and out
+ * are f32 [rows][n_heads*head_dim]. The key axis is cut into splits = clamp(ceil(n_ctx/32), 1,
+ * 64) runs of ceil(n_ctx/splits) rows fixed in cache positions (split_geom, attn_cols.rs:15-20);
+ * part_acc is f32 [rows][n_heads][splits][head_dim], part_ml f32 [rows][n_heads][splits][2]
+ * (split_scratch, attn_cols.rs:24-31). scale is 1/sqrt(head_dim). */
+int hipml_attn_decode_cols_f32(hipml_stream_t stream, const float *q, const float *k_cache,
+                               const float *v_cache, float *part_acc, float *part_ml, float *out,
+                               int n_heads, int n_kv, int head_dim, int n_ctx, int pos0,
+                               int rows);
+
+/* AttnLayer::append_rows (attn_cols.rs:34-64; kernel kv_append_cols_f32.hip:11-31): row c of
+ * k/v ([rows][width] f32) lands at cache row pos0 + c. */
+int hipml_kv_append_cols_f32(hipml_stream_t stream, float *k_cache, float *v_cache,
+                             const float *k, const float *v, int pos0, int rows, int width);
+
 /* Sequence-split decode across GPUs (no counterpart in the reference, which is single-GPU; the
  * algebra is its split-K reduce, crates/hipml-kernels/kernels/attn_decode_kv.hip:491-532, lifted
  * from thread blocks to devices). Each GPU holds a contiguous range of every KV head's positions

@@ -237,3 +237,34 @@ def test_sequence_split_shards_fold_to_the_whole_cache(shards, seq):
     # the numpy mirror used by the CPU (gloo) tests folds the same triples to the same result
     mirror = sharding.fold_triples(gathered.cpu().numpy())
     assert O.max_abs(mirror.ravel(), out.cpu().numpy()) < 1e-6
+
+
+@pytest.mark.parametrize("rows,pos0,n_ctx", [(1, 36, 37), (1, 0, 8), (4, 29, 80), (3, 997, 1000)])
+def test_f32_cache_decode_columns(rows, pos0, n_ctx):
+    """AttnLayer::attention_cols over the f32 position-major cache: the reference's
+    attn_decode_pm_f32 / attn_decode_split_f32 shape (8/2/64, crates/hipml-core/src/
+    attn_parity.rs:101-161) and the shipped shape, 1..4 columns, append included."""
+    from hipml_b200 import api
+    for heads, n_kv, hd in ((8, 2, 64), (24, 4, 256)):
+        width, scale = n_kv * hd, 1.0 / np.sqrt(np.float32(hd))
+        rng = O.Rng(0x7777_8888_9999_AAAA + rows + pos0)
+        q = rng.normals(rows * heads * hd).reshape(rows, heads * hd)
+        k = rng.normals(n_ctx * width, 0.3).reshape(n_ctx, width)
+        v = rng.normals(n_ctx * width).reshape(n_ctx, width)
+        live = pos0 + rows
+        kc = np.full((n_ctx, width), np.nan, dtype=np.float32)  # rows past the live length: NaN
+        vc = np.full((n_ctx, width), np.nan, dtype=np.float32)
+        kc[:pos0], vc[:pos0] = k[:pos0], v[:pos0]
+        dkc, dvc = _dev(kc), _dev(vc)
+        api.kv_append_cols_f32(dkc, dvc, _dev(k[pos0:live]), _dev(v[pos0:live]), pos0, rows, width)
+        splits = api.cols_splits(n_ctx)
+        acc = torch.full((rows * heads * splits * hd,), float("nan"), device="cuda")
+        ml = torch.full((rows * heads * splits * 2,), float("nan"), device="cuda")
+        out = torch.full((rows, heads * hd), float("nan"), device="cuda")
+        api.attn_decode_cols_f32(_dev(q), dkc, dvc, acc, ml, out, heads, n_kv, hd, n_ctx, pos0, rows)
+        torch.cuda.synchronize()
+        assert np.array_equal(dkc.cpu().numpy()[:live], k[:live])
+        got = out.cpu().numpy()
+        for c in range(rows):
+            want = O.attn_causal_f32(q[c], k, v, heads, n_kv, hd, pos0 + c + 1, float(scale))
+            _assert_close(want, got[c])
