@@ -109,11 +109,20 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
     // experimental variants have no counterpart here.
     bool tensor_core;
+    bool tcgen05_body = false;
     if (selector == 0 || selector == 4) {
         tensor_core = head_dim == 256;
         if (selector == 4 && head_dim != 256)
             return fail(HIPML_ERR_INVALID_ARGUMENT,
                         "head_dim %d: the warp kernel is head_dim 256 only", head_dim);
+    } else if (selector == 5) {
+        // the tcgen05 body: head_dim 256 and a GQA group of at most 6
+        if (head_dim != 256 || n_heads / n_kv > 6)
+            return fail(HIPML_ERR_INVALID_ARGUMENT,
+                        "head_dim %d / group %d: the tcgen05 decode kernel needs head_dim 256 and a "
+                        "group <= 6", head_dim, n_heads / n_kv);
+        tensor_core = true;
+        tcgen05_body = true;
     } else if (selector == 6) {
         tensor_core = false;
     } else if (selector == 1) {
@@ -144,7 +153,13 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     p.kv_slot_bytes = p.acc_slot = p.ml_slot = p.q_slot = 0;
     if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
-    if (int e = launch_decode_split(as_stream(stream), p, 1, tensor_core)) return e;
+    if (tcgen05_body) {
+        int *status = device_status_word();
+        if (!status) return launch_status();
+        if (int e = launch_decode_t5(as_stream(stream), p, 1, status)) return e;
+    } else if (int e = launch_decode_split(as_stream(stream), p, 1, tensor_core)) {
+        return e;
+    }
     if (!shard)
         return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
                                     splits, 1, 0, 0, 0);

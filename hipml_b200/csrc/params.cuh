@@ -25,6 +25,7 @@ struct DecodeParams {
 // Launches the split pass (the caller launches the reduce).
 int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, bool tensor_core);
 int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots);
+int launch_decode_t5(cudaStream_t stream, const DecodeParams &p, int slots, int *status);
 // Fold of (acc, max, sum) triples over the split axis; all strides in floats.
 struct FoldParams {
     const float *acc;

@@ -55,9 +55,11 @@ def _assert_close(expected, got, tight=2e-5):
     assert ma <= tight and rl <= tight, (ma, rl)
 
 
-@pytest.mark.parametrize("selector", [0, 6], ids=["tensor_core", "scalar"])
+@pytest.mark.parametrize("selector", [0, 5, 6], ids=["tensor_core", "tcgen05", "scalar"])
 @pytest.mark.parametrize("case", cases.KV_CASES, ids=lambda c: c.name)
 def test_reference_kv_cases(case, selector):
+    if selector == 5 and case.dim != 256:
+        pytest.skip("the tcgen05 body is head_dim 256 only")
     q, kb, vb = cases.kv_case_inputs(case)
     expected = cases.kv_case_expected(case, q, kb, vb)
     got, acc, ml = _run_decode(q, kb, vb, case.heads, case.n_kv, case.dim, case.seq, case.seq,
@@ -67,7 +69,7 @@ def test_reference_kv_cases(case, selector):
     assert not np.isnan(acc).any() and not np.isnan(ml).any()
 
 
-@pytest.mark.parametrize("selector", [0, 6], ids=["tensor_core", "scalar"])
+@pytest.mark.parametrize("selector", [0, 5, 6], ids=["tensor_core", "tcgen05", "scalar"])
 def test_reference_deep_case_100000_tokens(selector):
     c = cases.DEEP_CASE
     q, kb, vb = cases.kv_case_inputs(c)
@@ -77,8 +79,9 @@ def test_reference_deep_case_100000_tokens(selector):
     _assert_close(expected, got)
 
 
-@pytest.mark.parametrize("selector", [0, 6], ids=["tensor_core", "scalar"])
-@pytest.mark.parametrize("seq,pad", [(1, 7), (63, 1), (64, 0), (65, 200), (672, 136), (2500, 600)])
+@pytest.mark.parametrize("selector", [0, 5, 6], ids=["tensor_core", "tcgen05", "scalar"])
+@pytest.mark.parametrize("seq,pad", [(1, 7), (63, 1), (64, 0), (65, 200), (127, 3), (129, 0), (672, 136),
+                                     (2500, 600)])
 def test_shipped_shape_with_stride_beyond_live_length(seq, pad, selector):
     """24/4/256, splits from the engine's policy, cache rows past the live length poisoned."""
     from hipml_b200 import api
@@ -94,6 +97,9 @@ def test_shipped_shape_with_stride_beyond_live_length(seq, pad, selector):
     splits = api.decode_splits(seq)
     got, _, _ = _run_decode(q, kc, vc, heads, n_kv, hd, seq, stride, scale, splits, selector)
     _assert_close(expected, got)
+    if selector == 5:
+        from hipml_b200 import api as _api
+        assert _api.check_device_status() == 0
 
 
 def test_more_splits_than_positions_leaves_empty_partials_neutral():
@@ -102,7 +108,7 @@ def test_more_splits_than_positions_leaves_empty_partials_neutral():
     q = rng.normals(heads * hd)
     kb, vb = O.quantize_q8(rng.normals(seq * hd)), O.quantize_q8(rng.normals(seq * hd))
     expected = O.attn_decode_kv_q8(q, kb, vb, heads, n_kv, hd, seq, 0.0625)
-    for selector in (0, 6):
+    for selector in (0, 5, 6):
         got, acc, ml = _run_decode(q, kb, vb, heads, n_kv, hd, seq, seq, 0.0625, splits, selector)
         _assert_close(expected, got)
         ml = ml.reshape(heads, splits, 2)
