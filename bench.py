@@ -354,6 +354,130 @@ def decode_bench(torch, api, depths, steps, layers, hbm_gbs, reps=3):
     return results
 
 
+def decode_batched(torch, api, slots_list, layers, hbm_gbs, steps=32, reps=3):
+    """BASELINE configs[3]: multi-slot decode, B = 8 and 16, per-slot depth uniform in
+    [512, 8192] from seed 3, one q8_0 region per slot in a contiguous cache (stride 8448).
+    One step = per layer kv_encode_rows + batched split pass + fold; `steps` steps are captured
+    in one CUDA graph. Every slot of the last step is checked against the oracle on layer 0."""
+    import numpy as np
+
+    import oracle as O
+    dev, stride = "cuda", 8448
+    results = []
+    for slots in slots_list:
+        rng = O.Rng(3)
+        depths = [512 + int(rng.uniform() * 7681) for _ in range(slots)]
+        g = torch.Generator(device=dev).manual_seed(3 + slots)
+        slot_bytes = KV * stride * ROW
+        kc = [torch.zeros(slots * slot_bytes, dtype=torch.uint8, device=dev) for _ in range(layers)]
+        vc = [torch.zeros(slots * slot_bytes, dtype=torch.uint8, device=dev) for _ in range(layers)]
+        for l in range(layers):
+            for s, d in enumerate(depths):
+                kf = torch.randn(d, W, device=dev, generator=g)
+                vf = torch.randn(d, W, device=dev, generator=g)
+                api.kv_encode_bulk(kf, vf, kc[l][s * slot_bytes:], vc[l][s * slot_bytes:], KV, D, stride,
+                                   0, 0, d)
+        splits = api.batch_splits(stride, slots)
+        acc_slot, ml_slot = H * splits * D, H * splits * 2
+        acc = torch.empty(slots * acc_slot, device=dev)
+        ml = torch.empty(slots * ml_slot, device=dev)
+        q = torch.randn(steps, layers, slots, QW, device=dev, generator=g)
+        kn = torch.randn(steps, layers, slots, W, device=dev, generator=g)
+        vn = torch.randn(steps, layers, slots, W, device=dev, generator=g)
+        out = torch.empty(steps, layers, slots, QW, device=dev)
+        pos = torch.tensor([[[d + i, d + i + 1] for d in depths] for i in range(steps)],
+                           dtype=torch.int32, device=dev)
+
+        def token(i):
+            for l in range(layers):
+                api.kv_encode_rows(kn[i, l], vn[i, l], kc[l], vc[l], KV, D, stride, pos[i], slot_bytes,
+                                   slots)
+                api.attn_decode_batch(pos[i], q[i, l], kc[l], vc[l], acc, ml, out[i, l], H, KV, D,
+                                      stride, SCALE, splits, slot_bytes, acc_slot, ml_slot, QW, slots, 0)
+
+        token(0)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(steps):
+                    token(i)
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms_step = min(times) / steps
+        kv_bytes = sum(layers * 2 * KV * (d + i + 1) * ROW for d in depths for i in range(steps)) / steps
+        gbs = kv_bytes / (ms_step * 1e-3) / 1e9
+        worst_abs, worst_rel, i = 0.0, 0.0, steps - 1
+        kb = kc[0].cpu().numpy().reshape(slots, KV, stride, ROW)
+        vb = vc[0].cpu().numpy().reshape(slots, KV, stride, ROW)
+        for s, d in enumerate(depths):
+            want = O.attn_decode_kv_q8(q[i, 0, s].cpu().numpy(), kb[s], vb[s], H, KV, D, d + steps, SCALE,
+                                       stride=stride)
+            got = out[i, 0, s].cpu().numpy()
+            worst_abs = max(worst_abs, O.max_abs(want, got))
+            worst_rel = max(worst_rel, O.rel_l2(want, got))
+        results.append({"slots": slots, "depths": depths, "splits": splits, "ms_per_step": ms_step,
+                        "tok_s": slots * 1e3 / ms_step, "kv_bytes_per_step": kv_bytes, "kv_gbs": gbs,
+                        "frac_hbm": gbs / hbm_gbs, "l2_assisted": True,
+                        "parity": {"max_abs": worst_abs, "rel_l2": worst_rel}})
+        del kc, vc, graph
+        torch.cuda.empty_cache()
+    return results
+
+
+def prefill_long(torch, api, tokens, heads, n_kv, q_part=None, layers=1, reps=2):
+    """BASELINE configs[4], prefill phase: a `tokens`-token causal prefill in 2048-token chunks
+    over the q8_0 cache (stride tokens + 8), timed per layer. The same Q/K/V serve every
+    repetition; (heads, n_kv) are this rank's shard; q_part(ci, n) -> (offset, rows) selects the
+    rank's share of a chunk's query rows (None = all)."""
+    dev = "cuda"
+    stride = tokens + 8
+    qw, w = heads * D, n_kv * D
+    g = torch.Generator(device=dev).manual_seed(4)
+    q = torch.randn(tokens, qw, device=dev, generator=g)
+    k = torch.randn(tokens, w, device=dev, generator=g)
+    v = torch.randn(tokens, w, device=dev, generator=g)
+    out = torch.empty(tokens, qw, device=dev)
+    kc = torch.zeros(n_kv * stride * ROW, dtype=torch.uint8, device=dev)
+    vc = torch.zeros_like(kc)
+    cap = (tokens + 127) // 128 * 128
+    ws = torch.empty(api.attn_chunk_workspace_bytes(n_kv, D, 0, cap), dtype=torch.uint8, device=dev)
+    chunks = [(p, min(CHUNK, tokens - p)) for p in range(0, tokens, CHUNK)]
+
+    def layer():
+        for ci, (pos0, n) in enumerate(chunks):
+            api.kv_encode_bulk(k[pos0:pos0 + n], v[pos0:pos0 + n], kc, vc, n_kv, D, stride, pos0, 0, n)
+            api.attn_chunk_stage(kc, vc, n_kv, D, 1, stride, pos0, pos0 + n, cap, ws)
+            off, rows = (0, n) if q_part is None else q_part(ci, n)
+            if rows > 0:
+                api.attn_chunk_staged(q[pos0 + off:pos0 + off + rows], out[pos0 + off:pos0 + off + rows],
+                                      heads, n_kv, D, pos0 + off, rows, cap, ws)
+
+    layer()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(layers):
+            layer()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / layers)
+    return min(times), torch.isfinite(out).all().item()
+
+
 def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs, reps=3):
     """Decode at `depth` with the cache rows split across the ranks by sequence: per layer the
     owner of the new position appends its row, every rank folds its rows to one
@@ -541,8 +665,28 @@ def gpu_main(args):
             line["decode"] = decode_bench(torch, api, DECODE_DEPTHS, DECODE_STEPS, LAYERS,
                                           pk["hbm_gbs"])
             line["decode_peak_hbm_gbs"] = pk["hbm_gbs"]
+            line["decode_batched"] = decode_batched(torch, api, (8, 16), LAYERS, pk["hbm_gbs"])
+    if not args.no_decode:
+        # BASELINE configs[4], prefill phase: 100,000 tokens, one layer timed, same partition
+        pf = None
+        torch.cuda.empty_cache()
+        part = None
+        if q_shards > 1:
+            part = lambda ci, n: sharding.query_part(ci, n, q_shards, q_index)  # noqa: E731
+        long_tokens = 100000
+        ms_layer, finite = prefill_long(torch, api, long_tokens, heads_local, n_kv_local, part)
+        if dist is not None:
+            tms = torch.tensor([ms_layer], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ms_layer = float(tms.item())
+        flop_layer = attn_flops(chunk_pairs(0, long_tokens))
+        line["long_context_prefill"] = {
+            "tokens": long_tokens, "chunk": CHUNK, "layers_timed": 1, "ms_per_layer": ms_layer,
+            "tok_s_16_layers": long_tokens / (LAYERS * ms_layer * 1e-3),
+            "algorithmic_tflops_all_gpus": flop_layer / (ms_layer * 1e-3) / 1e12,
+            "frac_of_peak_all_gpus": flop_layer / (ms_layer * 1e-3) / 1e12 / (pk["tflops"] * world),
+            "finite": bool(finite)}
     if world > 1 and not args.no_decode:
-        del pf
         torch.cuda.empty_cache()
         line["decode"] = [decode_sharded(torch, dist, api, 100000, DECODE_STEPS, LAYERS, world, rank,
                                          pk["hbm_gbs"])]

@@ -20,7 +20,7 @@
 //    group, 128 rows = 21 queries x 6 heads on the shipped shape, so one staged K/V tile
 //    feeds all six heads. Per 128-key step:
 //        S = Q K^T           tcgen05.mma  M=128 N=128 K=256, Q (A) and K (B) from shared memory
-//        P = exp2(S - m)     four softmax warps, one TMEM lane (row) per thread, P written
+//        P = exp2(S - m)     eight softmax warps, two threads per TMEM lane (row), P written
 //                            back over S in TMEM as f16 high/low pairs
 //        O += P V            tcgen05.mma  M=128 N=2x128 K=128, P (A) from TMEM, V^T (B) from
 //                            shared memory
@@ -32,8 +32,9 @@
 //    ~1e-5 of the f32 definition; mode 1 issues hi*hi only (the reference kernel's own
 //    single-pass f16 precision).
 //
-// Roles: warps 0-3 softmax/epilogue (thread = row), warp 4 lane 0 TMA producer, warp 5
-// lane 0 MMA issuer. Every mbarrier wait is bounded: when a wait runs out the thread
+// Roles: warps 0-7 softmax/epilogue (two threads per row: TMEM lane = row, each owns half of
+// the score and output columns), warp 8 lane 0 TMA producer, warp 9 lane 0 MMA issuer.
+// Every mbarrier wait is bounded: when a wait runs out the thread
 // records a code in the device status word, raises a CTA-wide abort flag that every other
 // wait observes, and the CTA falls through to its teardown (TMEM is always released).
 #include <cuda.h>
@@ -65,8 +66,10 @@ constexpr int kStages = 3;
 constexpr int kTileBytes = 128 * 128;            // 128 rows x 64 f16, swizzled
 constexpr int kStageBytes = 2 * kTileBytes;      // hi + lo
 constexpr int kQBytes = 8 * kTileBytes;          // 4 dim-chunks x (hi, lo)
-constexpr int kTcThreads = 192;
-constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kTcThreads = 320;   // 8 softmax warps, TMA producer warp, MMA warp
+constexpr int kXchBytes = 2 * 256 * 4;   // the two halves of a row meet here (double-buffered)
+constexpr int kSmemNeed = kQBytes + kStages * kStageBytes + 256 /*barriers*/ + kXchBytes;
+constexpr int kSmemBytes = 232448;        // everything an SM offers: kSmemNeed + 768 B of alignment slack
 constexpr unsigned kSpinLimit = 1u << 22;        // polls per wait before giving up
 constexpr float kRescaleThreshold = 8.0f;        // log2 units: P stays <= 256
 
@@ -312,12 +315,18 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem =
         reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
+    if ((size_t)(smem - smem_raw) + kSmemNeed > (size_t)kSmemBytes) {
+        // The dynamic window starts further from a 1 KB boundary than the slack covers.
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 9);
+        return;
+    }
     unsigned char *q_smem = smem;                       // 8 tiles: hi chunks 0..3, lo chunks 0..3
     unsigned char *ring = smem + kQBytes;               // kStages x (hi tile, lo tile)
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kStages * kStageBytes);
-    // bars: full[3], empty[3], s_ready[2], p_ready[2], o_done[2]
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 12);
-    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 13);
+    // bars: full[3], empty[3], s_ready[2], p_ready[2], o_done[2], halves_met[2]
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 14);
+    unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars + 15);
+    float *xch = reinterpret_cast<float *>(bars + 32);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
@@ -327,6 +336,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
 
     const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 3);
     const unsigned bar_s = smem_u32(bars + 6), bar_p = smem_u32(bars + 8), bar_o = smem_u32(bars + 10);
+    const unsigned bar_x = smem_u32(bars + 12);
 
     // Key tiles this CTA walks: rows of the tile see cache rows < pos0 + t0 + nq.
     const int n_tiles_all = (p.pos0 + t0 + nq + kKeyTile - 1) / kKeyTile;
@@ -342,8 +352,10 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         }
         mbar_init(bar_s, 1);
         mbar_init(bar_s + 8, 1);
-        mbar_init(bar_p, 128);
-        mbar_init(bar_p + 8, 128);
+        mbar_init(bar_p, 256);
+        mbar_init(bar_p + 8, 256);
+        mbar_init(bar_x, 256);
+        mbar_init(bar_x + 8, 256);
         mbar_init(bar_o, 1);
         mbar_init(bar_o + 8, 1);
         *abort_flag = 0;
@@ -390,7 +402,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     const unsigned tmem_s[2] = {tmem + 256, tmem + 384};
     const int terms = p.single_pass ? 1 : 3;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0 && n_tiles > 0) {
             unsigned n = 0;  // chunks issued
@@ -426,7 +438,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                         if (mbar_try_wait(bar_full + 8 * (i % kStages), (i / kStages) & 1)) break;
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0 && n_tiles > 0) {
             unsigned n = 0;  // chunks consumed
@@ -491,31 +503,47 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         }
     } else {
         // ---------------------------------------------------------------- softmax + epilogue
-        const int r = tid;                                  // row = TMEM lane
-        const unsigned lane_addr = (unsigned)(warp * 32) << 16;
+        // Two threads per row: thread (row, half) owns score columns [64*half, +64) of the
+        // tile and output columns [128*half, +128). The halves of a row meet once per tile
+        // through shared memory and an mbarrier (bounded wait) to agree on the row maximum.
+        const int r = tid & 127, half = tid >> 7;           // row = TMEM lane
+        const unsigned lane_addr = (unsigned)((warp & 3) * 32) << 16;
         const int qi = min(r / p.group, nq - 1);            // dead rows shadow a live query
         const int kmax = p.pos0 + t0 + qi;                  // last visible cache row
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         unsigned v[32];
+        // x-th meeting of the two halves: returns the other half's value
+        auto meet = [&](int x, float mine, float &other) -> bool {
+            float *buf = xch + (x & 1) * 256;
+            buf[half * 128 + r] = mine;
+            mbar_arrive(bar_x + 8 * (x & 1));
+            if (!mbar_wait(bar_x + 8 * (x & 1), (x >> 1) & 1, abort_flag, p.status, 8)) return false;
+            other = buf[(half ^ 1) * 128 + r];
+            return true;
+        };
         for (int i = 0; i < n_tiles && ok; i++) {
-            const int key0 = (kt_lo + i) * kKeyTile;
-            const unsigned s_addr = tmem_s[i & 1] + lane_addr;
+            const int key0 = (kt_lo + i) * kKeyTile + 64 * half;
+            const unsigned s_addr = tmem_s[i & 1] + lane_addr + 64 * half;
             ok = mbar_wait(bar_s + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 5);
             if (!ok) break;
             tc_fence_after();
-            // pass 1: row maximum over the visible keys
-            float m_tile = -INFINITY;
+            // pass 1: maximum over this thread's visible keys, then over the row
+            float m_half = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
+            for (int j = 0; j < 2; j++) {
                 tmem_ld32(s_addr + 32 * j, v);
 #pragma unroll
                 for (int e = 0; e < 32; e++)
-                    if (key0 + 32 * j + e <= kmax) m_tile = fmaxf(m_tile, __uint_as_float(v[e]));
+                    if (key0 + 32 * j + e <= kmax) m_half = fmaxf(m_half, __uint_as_float(v[e]));
             }
-            const float m_new = fmaxf(m_used, m_tile);
+            float m_other;
+            ok = meet(i, m_half, m_other);
+            if (!ok) break;
+            const float m_new = fmaxf(m_used, fmaxf(m_half, m_other));
             // Rescale O only when the maximum moved by more than the threshold (P <= 2^8
-            // otherwise); the decision is per warp because the TMEM accesses are collective.
+            // otherwise); the decision is per warp because the TMEM accesses are collective
+            // (both halves of a row see the same maxima, so they decide alike).
             const bool want = (i > 0) && (m_new > m_used + kRescaleThreshold ||
                                           (m_used == -INFINITY && m_new > -INFINITY));
             if (i == 0) m_used = m_new;
@@ -525,11 +553,11 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                 tc_fence_after();
                 const float corr = (m_used == -INFINITY) ? 0.0f : exp2f(m_used - m_new);
 #pragma unroll 1
-                for (int j = 0; j < 8; j++) {
-                    tmem_ld32(tmem_o + lane_addr + 32 * j, v);
+                for (int j = 0; j < 4; j++) {
+                    tmem_ld32(tmem_o + lane_addr + 128 * half + 32 * j, v);
 #pragma unroll
                     for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
-                    tmem_st32(tmem_o + lane_addr + 32 * j, v);
+                    tmem_st32(tmem_o + lane_addr + 128 * half + 32 * j, v);
                 }
                 tmem_wait_st();
                 l *= corr;
@@ -537,14 +565,14 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             }
             // pass 2: P = exp2(S - m), written over S as f16 hi/lo pairs per 16-key step
 #pragma unroll 1
-            for (int j = 0; j < 4; j++) {
+            for (int j = 0; j < 2; j++) {
                 tmem_ld32(s_addr + 32 * j, v);
                 unsigned o[32];
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
+                for (int hh = 0; hh < 2; hh++) {
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
-                        const int ka = half * 16 + 2 * e;
+                        const int ka = hh * 16 + 2 * e;
                         const bool va = key0 + 32 * j + ka <= kmax, vb = key0 + 32 * j + ka + 1 <= kmax;
                         const float pa = va ? exp2f(__uint_as_float(v[ka]) - m_used) : 0.0f;
                         const float pb = vb ? exp2f(__uint_as_float(v[ka + 1]) - m_used) : 0.0f;
@@ -552,8 +580,8 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                         __half ha, la, hb, lb;
                         split_half(pa, ha, la);
                         split_half(pb, hb, lb);
-                        o[half * 16 + e] = pack2(ha, hb);
-                        o[half * 16 + 8 + e] = pack2(la, lb);
+                        o[hh * 16 + e] = pack2(ha, hb);
+                        o[hh * 16 + 8 + e] = pack2(la, lb);
                     }
                 }
                 tmem_st32(s_addr + 32 * j, o);
@@ -562,7 +590,10 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             tc_fence_before();
             mbar_arrive(bar_p + 8 * (i & 1));
         }
-        // epilogue: O / l (or the raw partial)
+        // epilogue: the row sum is the two halves' sums; O / l (or the raw partial)
+        float l_other = 0.0f;
+        if (ok) ok = meet(n_tiles, l, l_other);
+        l += l_other;
         if (ok && n_tiles > 0) {
             ok = mbar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag,
                            p.status, 7);
@@ -573,46 +604,29 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         const int h = kvh * p.group + rh;
         if (ok) {
             tc_fence_after();
-            if (p.splits < 2) {
-                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                float *dst = p.out + ((size_t)(t0 + rq) * p.n_heads + h) * kD;
+            const bool norm = p.splits < 2;
+            const float inv = norm ? (l > 0.0f ? 1.0f / l : 0.0f) : 1.0f;
+            const size_t slot = ((size_t)sp * p.qslots + (t0 + rq)) * p.n_heads + h;
+            float *dst = (norm ? p.out + ((size_t)(t0 + rq) * p.n_heads + h) * kD : p.part_acc + slot * kD) +
+                         128 * half;
 #pragma unroll 1
-                for (int j = 0; j < 8; j++) {
-                    if (n_tiles > 0) tmem_ld32(tmem_o + lane_addr + 32 * j, v);
-                    if (live) {
-#pragma unroll
-                        for (int e = 0; e < 32; e += 4) {
-                            float4 w;
-                            w.x = n_tiles > 0 ? __uint_as_float(v[e]) * inv : 0.0f;
-                            w.y = n_tiles > 0 ? __uint_as_float(v[e + 1]) * inv : 0.0f;
-                            w.z = n_tiles > 0 ? __uint_as_float(v[e + 2]) * inv : 0.0f;
-                            w.w = n_tiles > 0 ? __uint_as_float(v[e + 3]) * inv : 0.0f;
-                            *reinterpret_cast<float4 *>(dst + 32 * j + e) = w;
-                        }
-                    }
-                }
-            } else {
-                const size_t slot = ((size_t)sp * p.qslots + (t0 + rq)) * p.n_heads + h;
-                float *dst = p.part_acc + slot * kD;
-#pragma unroll 1
-                for (int j = 0; j < 8; j++) {
-                    if (n_tiles > 0) tmem_ld32(tmem_o + lane_addr + 32 * j, v);
-                    if (live) {
-#pragma unroll
-                        for (int e = 0; e < 32; e += 4) {
-                            float4 w;
-                            w.x = n_tiles > 0 ? __uint_as_float(v[e]) : 0.0f;
-                            w.y = n_tiles > 0 ? __uint_as_float(v[e + 1]) : 0.0f;
-                            w.z = n_tiles > 0 ? __uint_as_float(v[e + 2]) : 0.0f;
-                            w.w = n_tiles > 0 ? __uint_as_float(v[e + 3]) : 0.0f;
-                            *reinterpret_cast<float4 *>(dst + 32 * j + e) = w;
-                        }
-                    }
-                }
+            for (int j = 0; j < 4; j++) {
+                if (n_tiles > 0) tmem_ld32(tmem_o + lane_addr + 128 * half + 32 * j, v);
                 if (live) {
-                    p.part_ml[slot * 2] = m_used;
-                    p.part_ml[slot * 2 + 1] = l;
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        float4 w;
+                        w.x = n_tiles > 0 ? __uint_as_float(v[e]) * inv : 0.0f;
+                        w.y = n_tiles > 0 ? __uint_as_float(v[e + 1]) * inv : 0.0f;
+                        w.z = n_tiles > 0 ? __uint_as_float(v[e + 2]) * inv : 0.0f;
+                        w.w = n_tiles > 0 ? __uint_as_float(v[e + 3]) * inv : 0.0f;
+                        *reinterpret_cast<float4 *>(dst + 32 * j + e) = w;
+                    }
                 }
+            }
+            if (!norm && live && half == 0) {
+                p.part_ml[slot * 2] = m_used;
+                p.part_ml[slot * 2 + 1] = l;
             }
         }
     }
