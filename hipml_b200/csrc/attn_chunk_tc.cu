@@ -32,8 +32,22 @@
 //    ~1e-5 of the f32 definition; mode 1 issues hi*hi only (the reference kernel's own
 //    single-pass f16 precision).
 //
+//
+//    The default form runs CTA pairs (thread-block clusters of two, tcgen05 cta_group::2):
+//    the two CTAs of a pair own consecutive query tiles of one KV head and walk the same key
+//    tiles; one MMA of M = 256 spans both (each CTA's 128 rows accumulate in its own TMEM) and
+//    takes half of its B operand from each CTA's shared memory, so each CTA loads only half of
+//    every K tile (64 of the 128 keys) and half of every V^T tile (128 of the 256 dims). That
+//    halves the bytes each SM pulls from L2 per FLOP and doubles the time one ring slot
+//    lasts. The leader CTA's MMA thread issues for the pair; completion is signalled to both
+//    CTAs' barriers (tcgen05.commit with a CTA mask), the peer's TMA loads complete on the
+//    leader's barriers, and the peer's softmax warps arrive on the leader's barrier when
+//    their P is written. Every load is an ordinary one-destination TMA copy into the issuing
+//    CTA's own shared memory. The single-CTA form (M = 128) is kept for A/B.
+//
 // Roles: warps 0-7 softmax/epilogue (two threads per row: TMEM lane = row, each owns half of
-// the score and output columns), warp 8 lane 0 TMA producer, warp 9 lane 0 MMA issuer.
+// the score and output columns), warp 8 lane 0 TMA producer, warp 9 lane 0 MMA issuer (of
+// the leader CTA in the pair form).
 // Every mbarrier wait is bounded: when a wait runs out the thread
 // records a code in the device status word, raises a CTA-wide abort flag that every other
 // wait observes, and the CTA falls through to its teardown (TMEM is always released).
@@ -103,8 +117,9 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
 
 // Bounded wait. Returns false when the wait ran out (status word set, abort raised) or
 // another thread of the CTA aborted.
+// `peer_abort` is the shared::cluster address of the other CTA's abort flag (0: no peer).
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int *abort_flag,
-                                          int *status, int code) {
+                                          unsigned peer_abort, int *status, int code) {
     for (unsigned i = 0; i < kSpinLimit; i++) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255) == 255 && *abort_flag) return false;
@@ -112,28 +127,78 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     }
     atomicCAS(status, 0, code);
     *abort_flag = 1;
+    if (peer_abort)
+        asm volatile("st.relaxed.cluster.shared::cluster.u32 [%0], %1;" ::"r"(peer_abort), "r"(1)
+                     : "memory");
     __threadfence_block();
     return false;
 }
 
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y,
-                                            unsigned bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
-        "{%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
+// ---- thread-block cluster (CTA pair) helpers
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank`
+__device__ __forceinline__ unsigned map_to_cta(unsigned addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                 : "memory");
 }
 
-__device__ __forceinline__ void tmem_alloc(unsigned smem_dst, unsigned cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
-                 "r"(cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+// kCtas = 1: plain load, completion on this CTA's barrier. kCtas = 2: the pair form of the
+// load, whose completion barrier may live in the other CTA of the pair (`bar` is then a
+// shared::cluster address); the data always lands in the executing CTA's shared memory.
+template <int kCtas>
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *map, int x, int y,
+                                            unsigned bar) {
+    if constexpr (kCtas == 1) {
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+            "{%2, %3}], [%4];"
+            ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+            : "memory");
+    } else {
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+            "[%0], [%1, {%2, %3}], [%4];"
+            ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+            : "memory");
+    }
 }
+
+template <int kCtas>
+__device__ __forceinline__ void tmem_alloc(unsigned smem_dst, unsigned cols) {
+    if constexpr (kCtas == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                     "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                     "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+}
+template <int kCtas>
 __device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
-                 : "memory");
+    if constexpr (kCtas == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                     : "memory");
+    else
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                     : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -141,27 +206,55 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
+// Arrive on `bar` when every MMA this thread issued so far has completed. In the pair form
+// the arrival goes to the barrier at the same offset in both CTAs.
+template <int kCtas>
 __device__ __forceinline__ void tc_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
+    if constexpr (kCtas == 1) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                     : "memory");
+    } else {
+        const unsigned short both = 3;
+        asm volatile(
+            "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+            "[%0], %1;"
+            ::"r"(bar), "h"(both)
+            : "memory");
+    }
 }
 // D[tmem] (+)= A[smem] * B[smem]
+template <int kCtas>
 __device__ __forceinline__ void tc_mma_ss(unsigned d, uint64_t a, uint64_t b, unsigned idesc,
                                           unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (kCtas == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]
+template <int kCtas>
 __device__ __forceinline__ void tc_mma_ts(unsigned d, unsigned a, uint64_t b, unsigned idesc,
                                           unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (kCtas == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+            ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+            ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
@@ -205,8 +298,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(unsigned addr) {
     return d;
 }
 
-// Instruction descriptor: f16 x f16 -> f32, both operands K-major, M = 128, N = 128.
-constexpr unsigned kIdesc = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: f16 x f16 -> f32 accumulate, both operands K-major, M x N.
+__host__ __device__ constexpr unsigned idesc_f16(unsigned m, unsigned n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
 
 // Byte offset of element (row, col) of a [128][64] f16 tile in the swizzled image.
 __device__ __forceinline__ int sw128_offset(int row, int col) {
@@ -308,6 +403,9 @@ __global__ void __launch_bounds__(256) attn_chunk_stage(StageParams p) {
 
 // ------------------------------------------------------------------ main kernel
 
+// kCtas = 1: one CTA per query tile. kCtas = 2: launched as clusters of two along x; the
+// K maps then have 64-key boxes (a CTA loads its half of the keys of a tile).
+template <int kCtas>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constant__ CUtensorMap map_k_lo,
               const __grid_constant__ CUtensorMap map_vt_hi,
@@ -329,17 +427,28 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     float *xch = reinterpret_cast<float *>(bars + 32);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qt = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+    // The launch order is heaviest first: x = 0 holds the last query tiles, which walk the
+    // most keys, so the tail of the grid is made of the short tiles.
+    const unsigned rank = kCtas == 2 ? cluster_rank() : 0;
+    const int unit = (int)(gridDim.x / kCtas) - 1 - (int)(blockIdx.x / kCtas);  // tile or pair
+    const int qt = unit * kCtas + (int)rank, kvh = blockIdx.y, sp = blockIdx.z;
     const int t0 = qt * p.qtile;
-    const int nq = min(p.qtile, p.tokens - t0);  // live queries of this tile (>= 1)
+    // live queries of this tile; 0 for the second CTA of the last pair when the tile count is odd
+    const int nq = max(0, min(p.qtile, p.tokens - t0));
     const int rows_live = nq * p.group;
 
     const unsigned bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 3);
     const unsigned bar_s = smem_u32(bars + 6), bar_p = smem_u32(bars + 8), bar_o = smem_u32(bars + 10);
     const unsigned bar_x = smem_u32(bars + 12);
+    // Barriers of the leader CTA that this CTA signals (its own when there is no pair).
+    const unsigned lead_full = kCtas == 2 ? map_to_cta(bar_full, 0) : bar_full;
+    const unsigned lead_p = kCtas == 2 ? map_to_cta(bar_p, 0) : bar_p;
+    const unsigned peer_abort =
+        kCtas == 2 ? map_to_cta(smem_u32(const_cast<int *>(abort_flag)), rank ^ 1) : 0;
 
-    // Key tiles this CTA walks: rows of the tile see cache rows < pos0 + t0 + nq.
-    const int n_tiles_all = (p.pos0 + t0 + nq + kKeyTile - 1) / kKeyTile;
+    // Key tiles the CTA (pair) walks: its rows see cache rows < pos0 + (last live query + 1).
+    const int t_end = min(p.tokens, (unit + 1) * kCtas * p.qtile);
+    const int n_tiles_all = (p.pos0 + t_end + kKeyTile - 1) / kKeyTile;
     const int nsp = p.splits < 2 ? 1 : p.splits;
     const int kt_lo = (int)((long long)n_tiles_all * sp / nsp);
     const int kt_hi = (int)((long long)n_tiles_all * (sp + 1) / nsp);
@@ -352,8 +461,9 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         }
         mbar_init(bar_s, 1);
         mbar_init(bar_s + 8, 1);
-        mbar_init(bar_p, 256);
-        mbar_init(bar_p + 8, 256);
+        // P ready: one arrival per softmax warp of every CTA of the pair (on the leader)
+        mbar_init(bar_p, 8 * kCtas);
+        mbar_init(bar_p + 8, 8 * kCtas);
         mbar_init(bar_x, 256);
         mbar_init(bar_x + 8, 256);
         mbar_init(bar_o, 1);
@@ -363,7 +473,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     }
     if (warp == 0) {
         __syncwarp();
-        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_alloc<kCtas>(smem_u32(tmem_slot), 512);  // in the pair form: warp 0 of both CTAs
     }
 
     // Q tile: f32 -> scaled hi/lo f16 in the swizzled K-major image. Row r = query r/group,
@@ -395,44 +505,85 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     // Make the generic-proxy writes of Q visible to the tensor-core (async) proxy.
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
-    __syncthreads();
+    // Barriers initialised, Q written, TMEM allocated: in every CTA of the pair before any
+    // of them signals the other or the leader's MMAs read the peer's shared memory.
+    if constexpr (kCtas == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const unsigned tmem = *tmem_slot;
     const unsigned tmem_o = tmem;                 // columns [0,256)
     const unsigned tmem_s[2] = {tmem + 256, tmem + 384};
     const int terms = p.single_pass ? 1 : 3;
+    constexpr unsigned kIdescS = idesc_f16(128 * kCtas, 128);         // S = Q K^T
+    constexpr unsigned kIdescO = idesc_f16(128 * kCtas, 128 * kCtas); // O += P V (per MMA)
+    constexpr int kHalf = kStageBytes / 2;   // low plane of a ring slot
 
     if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0 && n_tiles > 0) {
             unsigned n = 0;  // chunks issued
             bool ok = true;
-            auto issue = [&](const CUtensorMap *hi, const CUtensorMap *lo, int x, int y) {
+            // Takes the next ring slot once the MMAs that read it have completed and arms its
+            // full barrier; in a pair only the leader arms, with both CTAs' bytes (the peer's
+            // copies complete on the leader's barrier).
+            auto acquire = [&](unsigned &dst, unsigned &full) {
                 const unsigned stage = n % kStages, phase = (n / kStages) & 1;
-                ok = ok && mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1);
+                ok = ok && mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, peer_abort, p.status, 1);
                 if (!ok) return;
-                const unsigned dst = smem_u32(ring + stage * kStageBytes);
-                mbar_arrive_expect_tx(bar_full + 8 * stage, p.single_pass ? kTileBytes : kStageBytes);
-                tma_load_2d(dst, hi, x, y, bar_full + 8 * stage);
-                if (!p.single_pass) tma_load_2d(dst + kTileBytes, lo, x, y, bar_full + 8 * stage);
+                dst = smem_u32(ring + stage * kStageBytes);
+                full = lead_full + 8 * stage;
+                if (rank == 0)
+                    mbar_arrive_expect_tx(bar_full + 8 * stage,
+                                          kCtas * (p.single_pass ? kStageBytes / 2 : kStageBytes));
                 n++;
             };
             auto load_k = [&](int kt) {
-                for (int c = 0; c < 4 && ok; c++)
-                    issue(&map_k_hi, &map_k_lo, c * 64, kvh * p.lpad + kt * kKeyTile);
+                unsigned dst = 0, full = 0;
+                if constexpr (kCtas == 1) {
+                    // slot = 128 keys x 64 dims (hi, lo)
+                    for (int c = 0; c < 4 && ok; c++) {
+                        acquire(dst, full);
+                        if (!ok) return;
+                        const int y = kvh * p.lpad + kt * kKeyTile;
+                        tma_load_2d<1>(dst, &map_k_hi, c * 64, y, full);
+                        if (!p.single_pass) tma_load_2d<1>(dst + kHalf, &map_k_lo, c * 64, y, full);
+                    }
+                } else {
+                    // slot = this CTA's 64 keys x two 64-dim chunks (hi c, hi c+1, lo c, lo c+1)
+                    for (int cp = 0; cp < 2 && ok; cp++) {
+                        acquire(dst, full);
+                        if (!ok) return;
+                        const int y = kvh * p.lpad + kt * kKeyTile + 64 * (int)rank;
+                        for (int cc = 0; cc < 2; cc++) {
+                            const int x = (2 * cp + cc) * 64;
+                            tma_load_2d<2>(dst + cc * (kHalf / 2), &map_k_hi, x, y, full);
+                            if (!p.single_pass)
+                                tma_load_2d<2>(dst + kHalf + cc * (kHalf / 2), &map_k_lo, x, y, full);
+                        }
+                    }
+                }
             };
             auto load_v = [&](int kt) {
+                unsigned dst = 0, full = 0;
+                // slot = 128 dims x 64 keys (hi, lo); a pair CTA loads only its half of the dims
                 for (int kc = 0; kc < 2 && ok; kc++)
-                    for (int dh = 0; dh < 2 && ok; dh++)
-                        issue(&map_vt_hi, &map_vt_lo, kt * kKeyTile + kc * 64, kvh * kD + dh * 128);
+                    for (int dh = 0; dh < (kCtas == 1 ? 2 : 1) && ok; dh++) {
+                        acquire(dst, full);
+                        if (!ok) return;
+                        const int x = kt * kKeyTile + kc * 64;
+                        const int y = kvh * kD + (kCtas == 1 ? dh : (int)rank) * 128;
+                        tma_load_2d<kCtas>(dst, &map_vt_hi, x, y, full);
+                        if (!p.single_pass) tma_load_2d<kCtas>(dst + kHalf, &map_vt_lo, x, y, full);
+                    }
             };
             load_k(kt_lo);
             for (int kt = kt_lo; kt < kt_hi && ok; kt++) {
                 if (kt + 1 < kt_hi) load_k(kt + 1);
                 load_v(kt);
             }
-            if (!ok) {
-                // Let copies already in flight land before the CTA's shared memory is released.
+            if (!ok && rank == 0) {
+                // Let copies already in flight land before the CTA's shared memory is released
+                // (the leader's barriers count the peer's copies too, and the peer stays
+                // resident until the leader reaches the closing cluster barrier).
                 for (unsigned i = (n > kStages ? n - kStages : 0); i < n; i++)
                     for (unsigned spin = 0; spin < kSpinLimit; spin++)
                         if (mbar_try_wait(bar_full + 8 * (i % kStages), (i / kStages) & 1)) break;
@@ -440,41 +591,60 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         }
     } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0 && n_tiles > 0) {
-            unsigned n = 0;  // chunks consumed
+        if (lane == 0 && n_tiles > 0 && rank == 0) {
+            unsigned n = 0;  // ring slots consumed
             bool ok = true;
             const unsigned q_addr = smem_u32(q_smem);
+            // Waits for ring slot n to be full (in a pair: both CTAs' halves) and returns its base.
+            auto slot = [&](int code) -> unsigned {
+                const unsigned stage = n % kStages, phase = (n / kStages) & 1;
+                ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, peer_abort, p.status, code);
+                if (ok) tc_fence_after();
+                return smem_u32(ring + stage * kStageBytes);
+            };
+            auto release = [&]() {  // the slot is free once the MMAs issued so far are done
+                tc_commit<kCtas>(bar_empty + 8 * (n % kStages));
+                n++;
+            };
+            // S += Q[:, 64-dim chunk c] K[:, chunk c]^T with the K chunk (hi at b_hi, lo at b_lo)
+            auto qk_chunk = [&](unsigned d, int c, unsigned b_hi, unsigned b_lo) {
+                const unsigned a_hi = q_addr + c * kTileBytes, a_lo = a_hi + 4 * kTileBytes;
+                for (int term = 0; term < terms; term++) {
+                    const unsigned a = term == 1 ? a_lo : a_hi;
+                    const unsigned b = term == 2 ? b_lo : b_hi;
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; k16++)
+                        tc_mma_ss<kCtas>(d, smem_desc_sw128(a + k16 * 32), smem_desc_sw128(b + k16 * 32),
+                                         kIdescS, (c | term | k16) != 0);
+                }
+            };
             auto qk = [&](int i) {  // i = tile index relative to kt_lo
                 const unsigned d = tmem_s[i & 1];
-                for (int c = 0; c < 4 && ok; c++) {
-                    const unsigned stage = n % kStages, phase = (n / kStages) & 1;
-                    ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 2);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const unsigned b_hi = smem_u32(ring + stage * kStageBytes), b_lo = b_hi + kTileBytes;
-                    const unsigned a_hi = q_addr + c * kTileBytes, a_lo = a_hi + 4 * kTileBytes;
-                    for (int term = 0; term < terms; term++) {
-                        const unsigned a = term == 1 ? a_lo : a_hi;
-                        const unsigned b = term == 2 ? b_lo : b_hi;
-#pragma unroll
-                        for (int k16 = 0; k16 < 4; k16++)
-                            tc_mma_ss(d, smem_desc_sw128(a + k16 * 32), smem_desc_sw128(b + k16 * 32),
-                                      kIdesc, (c | term | k16) != 0);
+                if constexpr (kCtas == 1) {
+                    for (int c = 0; c < 4 && ok; c++) {
+                        const unsigned b = slot(2);
+                        if (!ok) break;
+                        qk_chunk(d, c, b, b + kHalf);
+                        release();
                     }
-                    tc_commit(bar_empty + 8 * stage);
-                    n++;
+                } else {
+                    for (int cp = 0; cp < 2 && ok; cp++) {
+                        const unsigned b = slot(2);
+                        if (!ok) break;
+                        for (int cc = 0; cc < 2; cc++)
+                            qk_chunk(d, 2 * cp + cc, b + cc * (kHalf / 2), b + kHalf + cc * (kHalf / 2));
+                        release();
+                    }
                 }
-                if (ok) tc_commit(bar_s + 8 * (i & 1));
+                if (ok) tc_commit<kCtas>(bar_s + 8 * (i & 1));
             };
             auto pv = [&](int i) {
                 const unsigned a_base = tmem_s[i & 1];
                 for (int kc = 0; kc < 2 && ok; kc++)
-                    for (int dh = 0; dh < 2 && ok; dh++) {
-                        const unsigned stage = n % kStages, phase = (n / kStages) & 1;
-                        ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 3);
+                    for (int dh = 0; dh < (kCtas == 1 ? 2 : 1) && ok; dh++) {
+                        const unsigned b_hi = slot(3), b_lo = b_hi + kHalf;
                         if (!ok) break;
-                        tc_fence_after();
-                        const unsigned b_hi = smem_u32(ring + stage * kStageBytes), b_lo = b_hi + kTileBytes;
+                        // single CTA: 128 output dims per slot; pair: all 256 (half from each CTA)
                         const unsigned d = tmem_o + dh * 128;
                         for (int term = 0; term < terms; term++) {
                             const unsigned b = term == 2 ? b_lo : b_hi;
@@ -482,20 +652,19 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                             for (int k16 = 0; k16 < 4; k16++) {
                                 // P of keys [16*(4kc+k16), +16): hi pairs in 8 columns, lo in the next 8
                                 const unsigned a = a_base + (kc * 4 + k16) * 16 + (term == 1 ? 8 : 0);
-                                tc_mma_ts(d, a, smem_desc_sw128(b + k16 * 32), kIdesc,
-                                          (i | kc | term | k16) != 0);
+                                tc_mma_ts<kCtas>(d, a, smem_desc_sw128(b + k16 * 32), kIdescO,
+                                                 (i | kc | term | k16) != 0);
                             }
                         }
-                        tc_commit(bar_empty + 8 * stage);
-                        n++;
+                        release();
                     }
-                if (ok) tc_commit(bar_o + 8 * (i & 1));
+                if (ok) tc_commit<kCtas>(bar_o + 8 * (i & 1));
             };
             qk(0);
             for (int i = 0; i < n_tiles && ok; i++) {
                 if (i + 1 < n_tiles) qk(i + 1);
                 if (!ok) break;
-                ok = mbar_wait(bar_p + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 4);
+                ok = mbar_wait(bar_p + 8 * (i & 1), (i >> 1) & 1, abort_flag, peer_abort, p.status, 4);
                 if (!ok) break;
                 tc_fence_after();
                 pv(i);
@@ -518,14 +687,16 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             float *buf = xch + (x & 1) * 256;
             buf[half * 128 + r] = mine;
             mbar_arrive(bar_x + 8 * (x & 1));
-            if (!mbar_wait(bar_x + 8 * (x & 1), (x >> 1) & 1, abort_flag, p.status, 8)) return false;
+            if (!mbar_wait(bar_x + 8 * (x & 1), (x >> 1) & 1, abort_flag, peer_abort, p.status, 8)) return false;
             other = buf[(half ^ 1) * 128 + r];
             return true;
         };
         for (int i = 0; i < n_tiles && ok; i++) {
             const int key0 = (kt_lo + i) * kKeyTile + 64 * half;
             const unsigned s_addr = tmem_s[i & 1] + lane_addr + 64 * half;
-            ok = mbar_wait(bar_s + 8 * (i & 1), (i >> 1) & 1, abort_flag, p.status, 5);
+            // (votes keep the warp together: the TMEM accesses below are warp-collective)
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s + 8 * (i & 1), (i >> 1) & 1, abort_flag,
+                                                   peer_abort, p.status, 5));
             if (!ok) break;
             tc_fence_after();
             // pass 1: maximum over this thread's visible keys, then over the row
@@ -538,7 +709,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                     if (key0 + 32 * j + e <= kmax) m_half = fmaxf(m_half, __uint_as_float(v[e]));
             }
             float m_other;
-            ok = meet(i, m_half, m_other);
+            ok = __all_sync(0xffffffffu, meet(i, m_half, m_other));
             if (!ok) break;
             const float m_new = fmaxf(m_used, fmaxf(m_half, m_other));
             // Rescale O only when the maximum moved by more than the threshold (P <= 2^8
@@ -548,7 +719,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                                           (m_used == -INFINITY && m_new > -INFINITY));
             if (i == 0) m_used = m_new;
             if (__any_sync(0xffffffffu, want)) {
-                ok = mbar_wait(bar_o + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, p.status, 6);
+                ok = mbar_wait(bar_o + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, peer_abort, p.status, 6);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                 tc_fence_after();
                 const float corr = (m_used == -INFINITY) ? 0.0f : exp2f(m_used - m_new);
@@ -588,7 +759,12 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar_p + 8 * (i & 1));
+            // one arrival per warp, on the CTA that issues the MMAs
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (kCtas == 2) mbar_arrive_cluster(lead_p + 8 * (i & 1));
+                else mbar_arrive(bar_p + 8 * (i & 1));
+            }
         }
         // epilogue: the row sum is the two halves' sums; O / l (or the raw partial)
         float l_other = 0.0f;
@@ -596,7 +772,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         l += l_other;
         if (ok && n_tiles > 0) {
             ok = mbar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag,
-                           p.status, 7);
+                           peer_abort, p.status, 7);
         }
         ok = __all_sync(0xffffffffu, ok);
         const bool live = r < rows_live;
@@ -631,11 +807,13 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         }
     }
 
+    // Nothing of the pair may still be in flight towards either CTA (MMAs reading the peer's
+    // shared memory, barrier arrivals, copies) when one of them releases its TMEM and exits.
     tc_fence_before();
-    __syncthreads();
+    if constexpr (kCtas == 2) cluster_sync_all(); else __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        tmem_dealloc(tmem, 512);
+        tmem_dealloc<kCtas>(tmem, 512);
     }
 }
 
@@ -657,13 +835,13 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 2D f16 tensor [rows][cols] (cols contiguous), box 128 rows x 64 cols, 128-byte swizzle.
-int make_map(CUtensorMap *map, void *base, uint64_t cols, uint64_t rows) {
+// 2D f16 tensor [rows][cols] (cols contiguous), box `box_rows` rows x 64 cols, 128-byte swizzle.
+int make_map(CUtensorMap *map, void *base, uint64_t cols, uint64_t rows, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(HIPML_ERR_INVALID_ARGUMENT, "cuTensorMapEncodeTiled is not available");
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t box[2] = {64, box_rows};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, elem,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -708,25 +886,32 @@ int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_c
 }
 
 // Launches the tensor-core kernel over a workspace staged for `cap` keys per head.
-// Shapes are validated by the caller.
+// variant bit 0: single-pass precision (hi*hi only); bit 1: the single-CTA form instead of
+// CTA pairs. Shapes are validated by the caller.
 int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part_acc,
                     float *part_ml, int n_heads, int n_kv, int pos0, int tokens, int cap,
-                    int splits, int single_pass, void *workspace, int *status) {
+                    int splits, int variant, void *workspace, int *status) {
     const size_t plane = (size_t)n_kv * cap * kD;
     __half *ws = reinterpret_cast<__half *>(workspace);
+    const bool pair = (variant & 2) == 0;
+    const int single_pass = variant & 1;
     int rc;
     CUtensorMap mk_hi, mk_lo, mv_hi, mv_lo;
-    if ((rc = make_map(&mk_hi, ws, kD, (uint64_t)n_kv * cap))) return rc;
-    if ((rc = make_map(&mk_lo, ws + plane, kD, (uint64_t)n_kv * cap))) return rc;
-    if ((rc = make_map(&mv_hi, ws + 2 * plane, cap, (uint64_t)n_kv * kD))) return rc;
-    if ((rc = make_map(&mv_lo, ws + 3 * plane, cap, (uint64_t)n_kv * kD))) return rc;
+    const uint32_t k_box = pair ? 64 : 128;   // a pair CTA loads its 64 keys of a 128-key tile
+    if ((rc = make_map(&mk_hi, ws, kD, (uint64_t)n_kv * cap, k_box))) return rc;
+    if ((rc = make_map(&mk_lo, ws + plane, kD, (uint64_t)n_kv * cap, k_box))) return rc;
+    if ((rc = make_map(&mv_hi, ws + 2 * plane, cap, (uint64_t)n_kv * kD, 128))) return rc;
+    if ((rc = make_map(&mv_lo, ws + 3 * plane, cap, (uint64_t)n_kv * kD, 128))) return rc;
 
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_chunk_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_chunk_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
@@ -749,8 +934,28 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part
     p.qslots = (tokens + 31) / 32 * 32;
     p.single_pass = single_pass;
     const int nsp = splits < 2 ? 1 : splits;
-    dim3 grid((tokens + p.qtile - 1) / p.qtile, n_kv, nsp);
-    attn_chunk_tc<<<grid, kTcThreads, kSmemBytes, stream>>>(mk_hi, mk_lo, mv_hi, mv_lo, p);
+    const int qtiles = (tokens + p.qtile - 1) / p.qtile;
+    if (!pair) {
+        attn_chunk_tc<1><<<dim3(qtiles, n_kv, nsp), kTcThreads, kSmemBytes, stream>>>(mk_hi, mk_lo, mv_hi,
+                                                                                     mv_lo, p);
+        return launch_status();
+    }
+    // Clusters of two CTAs along x: consecutive query tiles of one KV head (an odd tile
+    // count leaves the last pair's second CTA without live queries).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((qtiles + 1) / 2 * 2, n_kv, nsp);
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_chunk_tc<2>, mk_hi, mk_lo, mv_hi, mv_lo, p);
+    if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 

@@ -318,7 +318,7 @@ int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
     if (kv_dtype == 1 && pos0 + tokens > stride)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "position %d beyond KV cache %d", pos0 + tokens,
                     stride);
-    if (mode < 0 || mode > 2) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown mode %d", mode);
+    if (mode < 0 || mode > 3) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown mode %d", mode);
     if (tokens == 0) return 0;
     if (splits >= 2 && (!part_acc || !part_ml))
         return fail(HIPML_ERR_INVALID_ARGUMENT, "split attention needs part_acc and part_ml");
@@ -399,7 +399,8 @@ int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, i
     if (head_dim != 256 || n_heads / n_kv > 8)
         return fail(HIPML_ERR_INVALID_ARGUMENT,
                     "tensor-core chunk attention: only head_dim 256 with a GQA group <= 8");
-    if (mode != 0 && mode != 1) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown mode %d", mode);
+    if (mode != 0 && mode != 1 && mode != 3)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown mode %d", mode);
     if (pos0 < 0 || tokens < 0 || key_capacity % 128 != 0 || pos0 + tokens > key_capacity)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "rows [%d, %d) with capacity %d", pos0,
                     pos0 + tokens, key_capacity);
@@ -417,7 +418,8 @@ int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, i
     int *status = device_status_word();
     if (!status) return launch_status();
     if (int e = launch_chunk_tc(as_stream(stream), q, out, part_acc, part_ml, n_heads, n_kv, pos0,
-                                tokens, key_capacity, splits, mode == 1, workspace, status))
+                                tokens, key_capacity, splits, mode == 1 ? 1 : (mode == 3 ? 2 : 0), workspace,
+                                status))
         return e;
     if (splits >= 2)
         return launch_chunk_combine(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,

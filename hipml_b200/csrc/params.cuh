@@ -68,7 +68,7 @@ int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_c
                        void *workspace);
 int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part_acc,
                     float *part_ml, int n_heads, int n_kv, int pos0, int tokens, int cap,
-                    int splits, int single_pass, void *workspace, int *status);
+                    int splits, int variant, void *workspace, int *status);
 
 // f32-cache decode for `rows` consecutive columns (attn_decode_f32.cu): split pass + fold.
 int launch_decode_cols_f32(cudaStream_t stream, const float *q, const float *k, const float *v,

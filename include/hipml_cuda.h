@@ -260,8 +260,9 @@ size_t hipml_attn_chunk_workspace_bytes(int n_kv, int head_dim, int pos0, int to
  * writes out (attn_chunk_split.hip:343-376).
  * mode: 0 = tensor-core kernel with error-compensated half-precision operands (meets the f32
  * tolerance), 1 = tensor-core kernel, single half-precision pass (the reference kernel's own
- * precision), 2 = scalar f32 kernel (any head_dim multiple of 32 up to 256; no workspace).
- * workspace: device memory of at least hipml_attn_chunk_workspace_bytes(...) for modes 0/1. */
+ * precision), 2 = scalar f32 kernel (any head_dim multiple of 32 up to 256; no workspace),
+ * 3 = as 0 but one CTA per query tile instead of CTA pairs (A/B form of the same arithmetic).
+ * workspace: device memory of at least hipml_attn_chunk_workspace_bytes(...) for modes 0/1/3. */
 int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
                      const void *v_cache, float *out, int n_heads, int n_kv, int head_dim,
                      int pos0, int tokens, int kv_dtype, int stride, float *part_acc,
@@ -277,7 +278,7 @@ int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
  * hipml_attn_chunk_stage converts cache rows [key_from, key_to) (whole 64-row tiles are
  * rewritten; rows from key_to to the next multiple of 128 are zero-filled).
  * hipml_attn_chunk_staged runs the attention of rows pos0..pos0+tokens-1 over staged rows
- * [0, pos0+tokens); mode 0 or 1 as in hipml_attn_chunk. */
+ * [0, pos0+tokens); mode 0, 1 or 3 as in hipml_attn_chunk. */
 int hipml_attn_chunk_stage(hipml_stream_t stream, const void *k_cache, const void *v_cache,
                            int n_kv, int head_dim, int kv_dtype, int stride, int key_from,
                            int key_to, int key_capacity, void *workspace,

@@ -62,20 +62,22 @@ def _assert_bar(expected, got, mode, label=""):
         assert ok, (ma, rl)
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2], ids=["tc_compensated", "tc_single_pass", "scalar"])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3],
+                         ids=["tc_compensated", "tc_single_pass", "scalar", "tc_single_cta"])
 def test_reference_case_37_queries_at_29_f32_cache(mode):
     c = cases.chunk_case_f32()
     _assert_bar(cases.chunk_expected(c), _run_chunk(c, 0, mode), mode, "37@29 f32")
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2], ids=["tc_compensated", "tc_single_pass", "scalar"])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3],
+                         ids=["tc_compensated", "tc_single_pass", "scalar", "tc_single_cta"])
 @pytest.mark.parametrize("splits", [1, 4])
 def test_reference_case_37_queries_at_29_q8_cache(mode, splits):
     c = cases.chunk_case_q8()
     _assert_bar(cases.chunk_expected(c), _run_chunk(c, 1, mode, splits), mode, f"37@29 q8 x{splits}")
 
 
-@pytest.mark.parametrize("mode", [0, 2], ids=["tc_compensated", "scalar"])
+@pytest.mark.parametrize("mode", [0, 2, 3], ids=["tc_compensated", "scalar", "tc_single_cta"])
 def test_q8_cache_with_stride_beyond_live_length(mode):
     # HIPML_CHUNK_PARITY_PAD in the reference: the engine's layout, stride = n_ctx
     c = cases.chunk_case_q8(tok=50, pos0=131, pad=77)
@@ -107,7 +109,7 @@ def test_config1_prefill_672_tokens_f32_cache():
     v = rng.normals(tok * n_kv * hd).reshape(tok, n_kv * hd)
     c = cases.ChunkCase(q, k, v, None, None, heads, n_kv, hd, 0, tok, tok)
     expected = cases.chunk_expected(c, threads=8)
-    for mode in (0, 1, 2):
+    for mode in (0, 1, 2, 3):
         _assert_bar(expected, _run_chunk(c, 0, mode), mode, "config 1")
 
 
