@@ -643,6 +643,11 @@ def gpu_main(args):
             "algorithmic_flop_per_launch": flops / n_launch,
             "issued_over_algorithmic": 3.0,
             "kernel_share_of_step": kernel_ms / ms,
+            # the same per chunk position (mean over layers): [pos0, ms, algorithmic TFLOP/s]
+            "by_chunk": [[p, sum(ev[0][l][c].elapsed_time(ev[1][l][c]) for l in range(LAYERS)) / LAYERS,
+                          attn_flops(chunk_pairs(p, n)) * LAYERS /
+                          (sum(ev[0][l][c].elapsed_time(ev[1][l][c]) for l in range(LAYERS)) * 1e9)]
+                         for c, (p, n) in enumerate(pf.chunks)],
         }
         # parity of the timed configuration + CPU baseline (1 core, the reference's own loop)
         want, rows, cpu = prefill_parity_and_cpu(torch, pf)

@@ -368,20 +368,28 @@ __device__ __forceinline__ void stage_store8(__half *hi, __half *lo, size_t at, 
         make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
 }
 
-// grid (tiles, n_kv), block 256: one CTA stages 64 keys of one KV head.
+// grid (tiles, n_kv, 3), block 256: 64 keys of one KV head; z = 0 stages K, z = 1, 2 the two
+// 128-dim halves of V (three times the CTAs of a fused pass: the chunk's 2048 new keys
+// would otherwise fill less than one wave of the device).
 __global__ void __launch_bounds__(256) attn_chunk_stage(StageParams p) {
     __shared__ float vs[64][129];
     const int kvh = blockIdx.y, key0 = (p.tile0 + blockIdx.x) * 64;
     const int tid = threadIdx.x;
-    // K: row-major copy. Thread -> dims [8*(tid%32), +8) of keys tid/32 + 8*i.
-    for (int i = 0; i < 8; i++) {
-        const int key = key0 + (tid >> 5) + 8 * i, d0 = (tid & 31) * 8;
-        float x[8];
-        stage_fetch(p, p.k, kvh, key, d0, x);
-        stage_store8(p.k_hi, p.k_lo, ((size_t)kvh * p.lpad + key) * kD + d0, x);
+    if (blockIdx.z == 0) {
+        // K: row-major copy. Thread -> dims [8*(tid%32), +8) of keys tid/32 + 8*i.
+#pragma unroll 4
+        for (int i = 0; i < 8; i++) {
+            const int key = key0 + (tid >> 5) + 8 * i, d0 = (tid & 31) * 8;
+            float x[8];
+            stage_fetch(p, p.k, kvh, key, d0, x);
+            stage_store8(p.k_hi, p.k_lo, ((size_t)kvh * p.lpad + key) * kD + d0, x);
+        }
+        return;
     }
-    // V: transposed through shared memory, 128 dims at a time.
-    for (int dh = 0; dh < 2; dh++) {
+    // V: transposed through shared memory, 128 dims per CTA.
+    {
+        const int dh = blockIdx.z - 1;
+#pragma unroll
         for (int i = 0; i < 4; i++) {
             const int kl = (tid >> 4) + 16 * i, d0 = (tid & 15) * 8;
             float x[8];
@@ -390,14 +398,15 @@ __global__ void __launch_bounds__(256) attn_chunk_stage(StageParams p) {
             for (int j = 0; j < 8; j++) vs[kl][d0 + j] = x[j];
         }
         __syncthreads();
-        const int d = tid & 127, kb0 = (tid >> 7) * 32;
-        for (int kb = kb0; kb < kb0 + 32; kb += 8) {
+        // Eight lanes write the 64 keys (128 contiguous bytes) of one dim: whole sectors.
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int item = tid + 256 * i, kb = (item & 7) * 8, d = item >> 3;
             float x[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) x[j] = vs[kb + j][d];
             stage_store8(p.vt_hi, p.vt_lo, ((size_t)kvh * kD + dh * 128 + d) * p.lpad + key0 + kb, x);
         }
-        __syncthreads();
     }
 }
 
@@ -881,7 +890,7 @@ int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_c
     sp.tile0 = key_from / 64;
     const int tile_end = (key_to + kKeyTile - 1) / kKeyTile * kKeyTile / 64;
     if (tile_end <= sp.tile0) return 0;
-    attn_chunk_stage<<<dim3(tile_end - sp.tile0, n_kv), 256, 0, stream>>>(sp);
+    attn_chunk_stage<<<dim3(tile_end - sp.tile0, n_kv, 3), 256, 0, stream>>>(sp);
     return launch_status();
 }
 

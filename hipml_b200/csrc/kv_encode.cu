@@ -23,7 +23,8 @@ constexpr int kMaxRowBytes = 8 * kQ8BlockBytes;  // head_dim 256
 
 // Quantise x (this lane's value of block `blk`) into row image `row`.
 __device__ __forceinline__ void q8_put(float x, int blk, int lane, unsigned char *row) {
-    const float amax = warp_max(fabsf(x));
+    // max from 0 that ignores NaN operands, as the host definition's fold does
+    const float amax = fmaxf(0.0f, warp_max(fabsf(x)));
     const float d = amax / 127.0f;
     const float id = d > 0.0f ? 1.0f / d : 0.0f;
     const float r = roundf(x * id);
@@ -104,6 +105,71 @@ extern "C" __global__ void kv_encode_bulk_q8(const float *__restrict__ k,
         const size_t off = q8_row_offset(h, stride, start + r, head_dim);
         encode_pair(k + src, v + src, kc + off, vc + off, head_dim, krow, vrow);
     }
+}
+
+// Eight values of one 32-value block held by one lane (lanes 4b..4b+3 share block b).
+__device__ __forceinline__ void q8_put8(const float4 a, const float4 b, int lane,
+                                        unsigned char *row) {
+    const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(x[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float d = amax / 127.0f;
+    const float id = d > 0.0f ? 1.0f / d : 0.0f;
+    unsigned q[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float r = roundf(x[j] * id);
+        q[j] = (unsigned)((r != r) ? 0 : (int)fmaxf(-127.0f, fminf(127.0f, r))) & 0xffu;
+    }
+    unsigned char *blk = row + (lane >> 2) * kQ8BlockBytes;
+    if ((lane & 3) == 0) *reinterpret_cast<unsigned short *>(blk) = __half_as_ushort(__float2half_rn(d));
+    unsigned short *dst = reinterpret_cast<unsigned short *>(blk + 2 + (lane & 3) * 8);
+#pragma unroll
+    for (int j = 0; j < 4; j++) dst[j] = (unsigned short)(q[2 * j] | (q[2 * j + 1] << 8));
+}
+
+// The throughput form of the bulk append for head_dim 256 and 16-byte-aligned sources
+// (what hipml_kv_encode_bulk launches; the kernel above keeps the reference's launch shape
+// for launches by name). One warp per (row, KV head): a lane loads 8 consecutive values of
+// the K row and of the V row (four 16-byte loads in flight), four lanes agree on a block's
+// maximum with two shuffles, the 272-byte images are assembled in shared memory and leave
+// as 16-byte stores. grid = ceil(n_kv*rows / 8), block 256. Same arithmetic per value as
+// q8_put, so the bytes are identical.
+__global__ void __launch_bounds__(256) kv_encode_bulk_q8_w(const float *__restrict__ k,
+                                                           const float *__restrict__ v,
+                                                           unsigned char *__restrict__ kc,
+                                                           unsigned char *__restrict__ vc, int n_kv,
+                                                           int stride, int start, int rows,
+                                                           int src0) {
+    __shared__ __align__(16) unsigned char img[8][2][kMaxRowBytes];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * 8 + warp;
+    if (idx >= (long long)n_kv * rows) return;
+    const int r = (int)(idx / n_kv);
+    const int h = (int)(idx - (long long)r * n_kv);
+    const size_t src = ((size_t)(src0 + r) * n_kv + h) * 256 + (size_t)lane * 8;
+    const float4 ka = __ldg(reinterpret_cast<const float4 *>(k + src));
+    const float4 kb = __ldg(reinterpret_cast<const float4 *>(k + src) + 1);
+    const float4 va = __ldg(reinterpret_cast<const float4 *>(v + src));
+    const float4 vb = __ldg(reinterpret_cast<const float4 *>(v + src) + 1);
+    q8_put8(ka, kb, lane, img[warp][0]);
+    q8_put8(va, vb, lane, img[warp][1]);
+    __syncwarp();
+    const size_t off = q8_row_offset(h, stride, start + r, 256);
+    row_store(kc + off, img[warp][0], kMaxRowBytes, lane, 32);
+    row_store(vc + off, img[warp][1], kMaxRowBytes, lane, 32);
+}
+
+int launch_kv_encode_bulk_rows(cudaStream_t stream, const float *k, const float *v,
+                               unsigned char *kc, unsigned char *vc, int n_kv, int stride,
+                               int start, int src0, int rows) {
+    const long long pairs = (long long)n_kv * rows;
+    kv_encode_bulk_q8_w<<<(unsigned)((pairs + 7) / 8), 256, 0, stream>>>(k, v, kc, vc, n_kv, stride,
+                                                                         start, rows, src0);
+    return launch_status();
 }
 
 // grid (n_kv, slots): slot s appends its row at pos[2*s] in the cache at s*slot_bytes.

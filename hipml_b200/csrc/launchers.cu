@@ -59,7 +59,11 @@ int hipml_kv_encode_bulk(hipml_stream_t stream, int dtype, const float *k_f32, c
         return fail(HIPML_ERR_INVALID_ARGUMENT, "rows [%d, %d) beyond KV cache %d", start,
                     start + rows, stride);
     if (rows == 0) return 0;
-    // One CTA per (row, head) pair up to a few waves of the device; the kernel strides.
+    if (head_dim == 256 && ((reinterpret_cast<size_t>(k_f32) | reinterpret_cast<size_t>(v_f32)) & 15) == 0)
+        return launch_kv_encode_bulk_rows(as_stream(stream), k_f32, v_f32, (unsigned char *)k_cache,
+                                          (unsigned char *)v_cache, n_kv, stride, start, src0, rows);
+    // Any other head_dim or alignment: the kernel with the reference's launch shape, one CTA
+    // per (row, head) pair up to a few waves of the device; the kernel strides.
     const long long pairs = (long long)n_kv * rows;
     const unsigned grid = (unsigned)(pairs < 148LL * 64 ? pairs : 148LL * 64);
     void *args[] = {&k_f32, &v_f32, &k_cache, &v_cache, &n_kv, &head_dim, &stride, &start, &rows,

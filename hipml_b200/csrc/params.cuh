@@ -61,6 +61,11 @@ int launch_chunk_scalar(cudaStream_t stream, const ChunkScalarParams &p);
 int launch_chunk_combine(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int tokens, int qslots, int splits);
 
+// Throughput form of the q8_0 bulk append, head_dim 256 and 16-byte-aligned sources (kv_encode.cu).
+int launch_kv_encode_bulk_rows(cudaStream_t stream, const float *k, const float *v,
+                               unsigned char *kc, unsigned char *vc, int n_kv, int stride,
+                               int start, int src0, int rows);
+
 // Tensor-core chunk attention (attn_chunk_tc.cu).
 size_t chunk_tc_workspace_bytes(int n_kv, int n_keys);
 int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_cache, int n_kv,

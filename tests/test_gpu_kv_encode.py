@@ -80,6 +80,8 @@ def test_single_row_shapes_and_edge_values(hd):
     if hd >= 64:
         v[32:64] = np.float32(1e30)
         v[40] = np.float32(np.nan)
+    if hd >= 96:
+        k[64:96] = np.float32(np.nan)   # a block of NaNs only: scale 0, codes 0
     row_bytes = hd // 32 * 34
     kc, vc = _cache(n_kv * stride * row_bytes), _cache(n_kv * stride * row_bytes)
     api.kv_encode(_step(pos), _dev(k), _dev(v), kc, vc, n_kv, hd, stride)
@@ -89,16 +91,32 @@ def test_single_row_shapes_and_edge_values(hd):
     assert np.array_equal(vc.cpu().numpy(), _expect_rows(vc.cpu().numpy(), vrows, n_kv, stride, pos, row_bytes))
 
 
-def test_bulk_rows_land_at_start_plus_r_from_src0_plus_r():
+@pytest.mark.parametrize("misaligned", [False, True], ids=["warp_per_row", "reference_shape"])
+def test_bulk_rows_land_at_start_plus_r_from_src0_plus_r(misaligned):
     from hipml_b200 import api
     n_kv, hd, stride = 4, 256, 300
     start, src0, rows, total = 37, 5, 130, 140
     rng = O.Rng(0xB01C)
     k = rng.normals(total * n_kv * hd).reshape(total, n_kv, hd)
     v = rng.normals(total * n_kv * hd, 3.0).reshape(total, n_kv, hd)
+    # edge values inside the copied rows: zero block, half-way codes, huge, subnormal scale,
+    # one NaN, a block of NaNs only
+    k[src0 + 1, 0, 0:32] = 0.0
+    k[src0 + 1, 1, 32:64] = 0.0
+    k[src0 + 1, 1, 32:36] = (127.0, 0.5, -0.5, 1.5)
+    v[src0 + 2, 2, 64:96] = np.float32(1e30)
+    v[src0 + 2, 2, 70] = np.float32(np.nan)
+    v[src0 + 3, 3, 0:32] = np.float32(1e-7)
+    k[src0 + 4, 3, 224:256] = np.float32(np.nan)
     row_bytes = 272
     kc, vc = _cache(n_kv * stride * row_bytes), _cache(n_kv * stride * row_bytes)
-    api.kv_encode_bulk(_dev(k), _dev(v), kc, vc, n_kv, hd, stride, start, src0, rows)
+    kd, vd = _dev(k), _dev(v)
+    if misaligned:
+        # sources 4 bytes off a 16-byte boundary take the kernel with the reference's launch shape
+        kd = torch.cat([kd.new_zeros(1), kd.flatten()])[1:]
+        vd = torch.cat([vd.new_zeros(1), vd.flatten()])[1:]
+        assert kd.data_ptr() % 16 == 4
+    api.kv_encode_bulk(kd, vd, kc, vc, n_kv, hd, stride, start, src0, rows)
     torch.cuda.synchronize()
     for src, cache in ((k, kc), (v, vc)):
         want = np.full((n_kv, stride, row_bytes), CANARY, dtype=np.uint8)
