@@ -145,6 +145,17 @@ class Prefill:
         self.chunks = [(p, min(chunk, tokens - p)) for p in range(0, tokens, chunk)]
         self.launches_per_step = layers * len(self.chunks) * 3
         self.events = None
+        self.splits, self.pa, self.pm = 1, None, None
+
+    def use_key_splits(self, splits, max_rows):
+        """Cut every query tile's key range into `splits` slices (partials + combine pass): a
+        rank that owns few KV heads has fewer query-tile pairs than the device has SM pairs."""
+        self.splits = splits
+        if splits >= 2:
+            qslots = (max_rows + 31) // 32 * 32
+            self.pa = self.torch.empty(splits * qslots * self.qw, device="cuda")
+            self.pm = self.torch.empty(splits * qslots * self.heads * 2, device="cuda")
+            self.launches_per_step = self.layers * len(self.chunks) * 4
 
     def layer(self, l, q, k, v, out, kc, vc, ws, mode=0, timed=None):
         api = self.api
@@ -155,7 +166,7 @@ class Prefill:
             if timed is not None:
                 timed[0][l][ci].record()
             api.attn_chunk_staged(q[pos0:pos0 + n], out[pos0:pos0 + n], self.heads, self.n_kv, D,
-                                  pos0, n, self.cap, ws, mode=mode)
+                                  pos0, n, self.cap, ws, self.pa, self.pm, self.splits, mode=mode)
             if timed is not None:
                 timed[1][l][ci].record()
 
@@ -602,8 +613,11 @@ def gpu_main(args):
                                    pos0, 0, n)
                 api.attn_chunk_stage(kc, vc, pf.n_kv, D, 1, pf.stride, pos0, pos0 + n, pf.cap, ws)
                 api.attn_chunk_staged(q[pos0 + qoff:pos0 + qoff + qn], out[pos0 + qoff:pos0 + qoff + qn],
-                                      pf.heads, pf.n_kv, D, pos0 + qoff, qn, pf.cap, ws, mode=mode)
+                                      pf.heads, pf.n_kv, D, pos0 + qoff, qn, pf.cap, ws, pf.pa, pf.pm,
+                                      pf.splits, mode=mode)
         pf.layer = layer
+    key_splits = sharding.prefill_key_splits(CHUNK // q_shards, heads_local // n_kv_local, n_kv_local)
+    pf.use_key_splits(key_splits, CHUNK)
 
     gpu_index = local
     with ClockSampler(gpu_index) as clocks:
@@ -618,7 +632,8 @@ def gpu_main(args):
         "data": "synthetic N(0,1), seeded, generated on device",
         "config": {"workload": "prefill T=8192 in 2048-token chunks, q8_0 KV, 24/4/256, 16 layers "
                                "(BASELINE configs[1])",
-                   "parallelism": f"kv_head x{kv_shards}" + (f", query x{q_shards}" if q_shards > 1 else ""),
+                   "parallelism": f"kv_head x{kv_shards}" + (f", query x{q_shards}" if q_shards > 1 else "")
+                                  + (f", key slices x{key_splits} per query tile" if key_splits > 1 else ""),
                    "l2": "inputs larger than L2 (7.6 GB of Q/K/V per step)"},
         "gpu_launches": pf.launches_per_step * args.steps,
         "clocks": clocks.summary(),
@@ -774,29 +789,37 @@ def profile_case(args):
     g = torch.Generator(device=dev).manual_seed(7)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.reps)]
     if args.case == "chunk":
+        # --kv-heads < 4 stands for one rank's share of a KV-head-sharded job
         pos0, n, stride = 6144, 2048, 8200
-        q = torch.randn(n, QW, device=dev, generator=g)
-        kf = torch.randn(pos0 + n, W, device=dev, generator=g)
-        vf = torch.randn(pos0 + n, W, device=dev, generator=g)
-        kc = torch.zeros(KV * stride * ROW, dtype=torch.uint8, device=dev)
+        kv, sp = args.kv_heads, args.splits
+        heads, qw, w = 6 * kv, 6 * kv * D, kv * D
+        q = torch.randn(n, qw, device=dev, generator=g)
+        kf = torch.randn(pos0 + n, w, device=dev, generator=g)
+        vf = torch.randn(pos0 + n, w, device=dev, generator=g)
+        kc = torch.zeros(kv * stride * ROW, dtype=torch.uint8, device=dev)
         vc = torch.zeros_like(kc)
-        out = torch.empty(n, QW, device=dev)
+        out = torch.empty(n, qw, device=dev)
         cap = 8192
-        ws = torch.empty(api.attn_chunk_workspace_bytes(KV, D, 0, cap), dtype=torch.uint8, device=dev)
-        api.kv_encode_bulk(kf, vf, kc, vc, KV, D, stride, 0, 0, pos0)
-        api.attn_chunk_stage(kc, vc, KV, D, 1, stride, 0, pos0, cap, ws)
+        ws = torch.empty(api.attn_chunk_workspace_bytes(kv, D, 0, cap), dtype=torch.uint8, device=dev)
+        pa = pm = None
+        if sp >= 2:
+            qslots = (n + 31) // 32 * 32
+            pa = torch.empty(sp * qslots * heads * D, device=dev)
+            pm = torch.empty(sp * qslots * heads * 2, device=dev)
+        api.kv_encode_bulk(kf, vf, kc, vc, kv, D, stride, 0, 0, pos0)
+        api.attn_chunk_stage(kc, vc, kv, D, 1, stride, 0, pos0, cap, ws)
         for r in range(args.reps):
-            api.kv_encode_bulk(kf[pos0:], vf[pos0:], kc, vc, KV, D, stride, pos0, 0, n)
-            api.attn_chunk_stage(kc, vc, KV, D, 1, stride, pos0, pos0 + n, cap, ws)
+            api.kv_encode_bulk(kf[pos0:], vf[pos0:], kc, vc, kv, D, stride, pos0, 0, n)
+            api.attn_chunk_stage(kc, vc, kv, D, 1, stride, pos0, pos0 + n, cap, ws)
             ev[2 * r].record()
-            api.attn_chunk_staged(q, out, H, KV, D, pos0, n, cap, ws, mode=args.mode)
+            api.attn_chunk_staged(q, out, heads, kv, D, pos0, n, cap, ws, pa, pm, sp, mode=args.mode)
             ev[2 * r + 1].record()
         torch.cuda.synchronize()
-        flops = attn_flops(chunk_pairs(pos0, n))
+        flops = attn_flops(chunk_pairs(pos0, n)) * kv / KV
         for r in range(args.reps):
             ms = ev[2 * r].elapsed_time(ev[2 * r + 1])
-            print(json.dumps({"case": "chunk 2048@6144", "mode": args.mode, "ms": ms,
-                              "algorithmic_tflops": flops / ms / 1e9}))
+            print(json.dumps({"case": "chunk 2048@6144", "mode": args.mode, "kv_heads": kv,
+                              "splits": sp, "ms": ms, "algorithmic_tflops": flops / ms / 1e9}))
     else:
         depth = args.depth
         stride = depth + 136
@@ -837,6 +860,8 @@ def main():
                     help="run one small profiling case instead of the benchmark")
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--mode", type=int, default=0)
+    ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--kv-heads", type=int, default=4)
     ap.add_argument("--selector", type=int, default=0)
     ap.add_argument("--depth", type=int, default=100000)
     ap.add_argument("--gpus", type=int, default=1)

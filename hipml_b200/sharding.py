@@ -74,3 +74,16 @@ def fold_triples(gathered: np.ndarray) -> np.ndarray:
     with np.errstate(invalid="ignore", divide="ignore"):
         out = np.where(den[:, None] > 0, num / den[:, None], np.float32(0))
     return out.astype(np.float32)
+
+
+def prefill_key_splits(chunk_rows: int, group: int, local_n_kv: int, sm_pairs: int = 74) -> int:
+    """Key slices per query tile for a rank's share of a prefill chunk. The tensor-core chunk
+    kernel runs one CTA pair per two query tiles of 128 // group queries; a rank that owns
+    all 4 KV heads has more pairs than SM pairs and runs unsplit, a rank with fewer pairs cuts
+    the key axis so that about two waves of the device are filled (measured on the 2048-token
+    chunk: 1 / 2 / 3 slices are the fastest for 4 / 2 / 1 local KV heads)."""
+    qtile = max(128 // group, 1)
+    pairs = -(-(-(-chunk_rows // qtile)) // 2) * local_n_kv
+    if pairs >= 2 * sm_pairs:
+        return 1
+    return max(1, min(8, round(2 * sm_pairs / pairs)))

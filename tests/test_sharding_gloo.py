@@ -120,3 +120,14 @@ def test_fold_handles_empty_shards():
     g[1, :, :4] = [2.0, 4.0, 6.0, 8.0]
     g[1, :, 4], g[1, :, 5] = 0.5, 2.0
     assert np.allclose(sharding.fold_triples(g), [[1.0, 2.0, 3.0, 4.0]] * 2)
+
+
+def test_prefill_key_split_policy_fills_two_waves():
+    """A rank with all 4 KV heads runs unsplit; fewer local pairs get more key slices."""
+    from hipml_b200 import sharding
+    assert sharding.prefill_key_splits(2048, 6, 4) == 1
+    assert sharding.prefill_key_splits(2048, 6, 2) == 2
+    assert sharding.prefill_key_splits(2048, 6, 1) == 3
+    assert sharding.prefill_key_splits(1024, 6, 1) == 6
+    assert sharding.prefill_key_splits(1, 6, 1) == 8          # capped
+    assert sharding.prefill_key_splits(100000, 6, 4) == 1
