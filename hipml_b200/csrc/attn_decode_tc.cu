@@ -1,9 +1,12 @@
 // Split-K flash-decode over the q8_0 cache, tensor-core body (head_dim 256).
 //
 // A CTA of 8 warps owns one (KV head, split[, slot]) and streams its rows through a
-// double-buffered shared-memory ring with 16-byte asynchronous copies: rows are 272 B,
-// 16-byte aligned, and consecutive positions of one head are contiguous, so a 64-key tile
-// of K (or V) is one linear 17 KB run. Both contractions run on the tensor cores
+// three-stage shared-memory ring filled by bulk asynchronous copies (cp.async.bulk, one per
+// tensor and tile, completion on an mbarrier): rows are 272 B, 16-byte aligned, and
+// consecutive positions of one head are contiguous, so a 64-key tile of K (or V) is one
+// linear 17 KB run. One thread issues the copy of tile i+2 as soon as tile i-1 has been
+// consumed, so two tiles (70 KB per CTA, two CTAs per SM) are always in flight while the
+// third is being computed on. Both contractions run on the tensor cores
 // (mma.sync m16n8k16, f16 operands, f32 accumulate) with operands built in registers:
 //   * int8 codes are exact in f16 (0x6400 | (code ^ 0x80) is 1152 + code);
 //   * the query and the softmax weights are split into f16 high + low parts stacked along
@@ -34,22 +37,48 @@ constexpr int kSsStride = 72;                    // padded row of the score tile
 constexpr int kPStride = 72;                     // padded row of the weight tile (halves)
 constexpr float kPScale = 1024.0f;               // keeps weight*scale in f16's normal range
 
-// Dynamic shared memory: K[2] | V[2] | scores [2][8][72] f32 | weights hi, lo [8][72] f16 |
-// corr[8] f32. The query staging area [8][256] f32 aliases V[1] during set-up.
-constexpr int kOffSs = 4 * kTileBytes;
+constexpr int kStages = 3;                       // ring depth (tiles of K and V)
+constexpr unsigned kSpinLimit = 1u << 24;        // polls of a full barrier before giving up
+
+// Dynamic shared memory: stage[3] = (K tile | V tile) | scores [2][8][72] f32 | weights hi,
+// lo [8][72] f16 | corr[8] f32 | full barriers [3]. The query staging area [8][256] f32
+// aliases stage 2 during set-up (stage 2 is first filled after the set-up).
+constexpr int kOffSs = 2 * kStages * kTileBytes;
 constexpr int kOffPh = kOffSs + 2 * 8 * kSsStride * 4;
 constexpr int kOffPl = kOffPh + 8 * kPStride * 2;
 constexpr int kOffCorr = kOffPl + 8 * kPStride * 2;
-constexpr int kSmemBytes = kOffCorr + 8 * 4;
+constexpr int kOffBar = kOffCorr + 8 * 4;
+constexpr int kSmemBytes = kOffBar + kStages * 8;
+static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs per SM");
 
-__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+__device__ __forceinline__ unsigned smem_u32(const void *p) {
+    return (unsigned)__cvta_generic_to_shared(p);
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Linear global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned);
+// the bytes are counted on `bar` as they land.
+__device__ __forceinline__ void bulk_load(unsigned dst, const void *src, unsigned bytes, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
 }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0,
@@ -110,11 +139,32 @@ __device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
     return *reinterpret_cast<const unsigned *>(&r);
 }
 
-__device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int &lo,
-                                            int &hi) {
+// Rows [lo, hi) of split `split`. The partials are scratch: only their fold is defined, so
+// the rows are dealt out to suit this kernel rather than as ceil(len / splits) runs. A run
+// is a whole number of 64-key tiles (no split ends in a mostly empty tile), and the number
+// of tiles per run is the one that minimises waves x (tiles + 1) for the CTA slots of the
+// device (`cta_slots`; the +1 stands for a CTA's query set-up and partial write): 100,000
+// rows in 256 splits would be 1024 CTAs of 6.1 tiles = 3.5 waves of 7 tile times, 143 runs
+// of 11 tiles per KV head are 1.9 waves = 2 x 11. Splits past the last run get no rows and
+// write neutral partials.
+__device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split,
+                                            int cta_slots, int &lo, int &hi) {
     const int len = p.len[slot * p.len_stride + p.len_offset];
-    const int span = p.by_stride ? p.stride : len;
-    const int per = (span + p.splits - 1) / p.splits;
+    const int tiles = (len + kTile - 1) / kTile;
+    const int t_min = max((tiles + p.splits - 1) / p.splits, 1);
+    const int ctas_per_run = p.n_kv * (int)gridDim.y;
+    int best_t = t_min, best_cost = 0x7fffffff;
+    for (int t = t_min; t < t_min + 24; t++) {
+        const int runs = (tiles + t - 1) / t;
+        const int waves = (runs * ctas_per_run + cta_slots - 1) / cta_slots;
+        const int cost = waves * (t + 1);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best_t = t;
+        }
+        if (runs <= 1) break;
+    }
+    const int per = best_t * kTile;
     lo = min(split * per, len);
     hi = min(lo + per, len);
 }
@@ -141,11 +191,16 @@ __device__ __forceinline__ void score_block(const unsigned char *ktile, int key_
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int cta_slots,
+                                                                  int *status) {
     extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char *ktile[2] = {smem, smem + kTileBytes};
-    unsigned char *vtile[2] = {smem + 2 * kTileBytes, smem + 3 * kTileBytes};
-    float *qs = reinterpret_cast<float *>(vtile[1]);                 // set-up only
+    unsigned char *ktile[kStages], *vtile[kStages];
+#pragma unroll
+    for (int s = 0; s < kStages; s++) {
+        ktile[s] = smem + 2 * s * kTileBytes;
+        vtile[s] = ktile[s] + kTileBytes;
+    }
+    float *qs = reinterpret_cast<float *>(ktile[2]);                 // set-up only
     float *ss = reinterpret_cast<float *>(smem + kOffSs);            // [2][8][kSsStride]
     __half *ph = reinterpret_cast<__half *>(smem + kOffPh);          // [8][kPStride]
     __half *pl = reinterpret_cast<__half *>(smem + kOffPl);
@@ -159,25 +214,49 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p)
     const int kg = warp & 3, dh = warp >> 2;
 
     int lo, hi;
-    split_range(p, slot, split, lo, hi);
+    split_range(p, slot, split, cta_slots, lo, hi);
     const int ntiles = (hi - lo + kTile - 1) / kTile;
+    if (ntiles == 0) {
+        // A split without rows: neutral partials (zero sum, -inf maximum), nothing else.
+        for (int i = tid; i < group * 256; i += kThreads) {
+            const int h = kvh * group + (i >> 8);
+            p.part_acc[(size_t)slot * p.acc_slot + ((size_t)h * p.splits + split) * 256 + (i & 255)] = 0.0f;
+        }
+        if (tid < group) {
+            float *pm = p.part_ml + (size_t)slot * p.ml_slot +
+                        ((size_t)(kvh * group + tid) * p.splits + split) * 2;
+            pm[0] = -INFINITY;
+            pm[1] = 0.0f;
+        }
+        return;
+    }
 
     const size_t head_byte = (size_t)slot * p.kv_slot_bytes + q8_row_offset(kvh, p.stride, 0, 256);
     const unsigned char *kbase = p.k + head_byte;
     const unsigned char *vbase = p.v + head_byte;
 
-    auto prefetch = [&](int tile, int buf) {
+    // Ring: stage tile % 3; thread 0 arms the stage's barrier with the byte count and issues
+    // the two copies. A stage is re-filled only after the __syncthreads that ends the tile
+    // which last read it.
+    const unsigned bar_full = smem_u32(smem + kOffBar);
+    auto fetch = [&](int tile) {
+        const int stage = tile % kStages;
         const int r0 = lo + tile * kTile;
-        const int nrows = min(kTile, hi - r0);
+        const unsigned bytes = (unsigned)(min(kTile, hi - r0) * kRowBytes);
         const size_t off = (size_t)r0 * kRowBytes;
-        const int chunks = nrows * (kRowBytes / 16);
-        for (int i = tid; i < chunks; i += kThreads) {
-            cp_async_16(ktile[buf] + i * 16, kbase + off + (size_t)i * 16);
-            cp_async_16(vtile[buf] + i * 16, vbase + off + (size_t)i * 16);
-        }
-        cp_async_commit();
+        // earlier generic-proxy writes to the stage (zero fill, query staging) come first
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * bytes);
+        bulk_load(smem_u32(ktile[stage]), kbase + off, bytes, bar_full + 8 * stage);
+        bulk_load(smem_u32(vtile[stage]), vbase + off, bytes, bar_full + 8 * stage);
     };
-    if (ntiles > 0) prefetch(0, 0);
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; s++) mbar_init(bar_full + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fetch(0);
+        if (ntiles > 1) fetch(1);
+    }
 
     // Query rows of this KV head's group in log2 units; rows past the group are zero.
     const float *q = p.q + (size_t)slot * p.q_slot + (size_t)kvh * group * 256;
@@ -203,7 +282,10 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p)
         qa[ks][2] = pack_half2(xh[2], xh[3]);
         qa[ks][3] = pack_half2(xl[2], xl[3]);
     }
-    __syncthreads();  // qs aliases V[1]: every warp is done with it before tile 1 is fetched
+    // qs aliases stage 2: every warp is done with it (and its generic-proxy writes are ordered
+    // before the bulk copy's) before tile 2 is fetched
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
 
     float acc[4][4];  // block `warp`: [byte i of the code word][c0..c3]
 #pragma unroll
@@ -212,16 +294,23 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p)
         for (int c = 0; c < 4; c++) acc[i][c] = 0.0f;
     float m_run = -INFINITY, l_run = 0.0f;  // meaningful in warp g' = head of the group
 
+    bool landed = true;
     for (int tile = 0; tile < ntiles; tile++) {
-        const int buf = tile & 1;
-        if (tile + 1 < ntiles) {
-            prefetch(tile + 1, buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+        const int buf = tile % kStages;
+        // the stage of tile + 2 was read last by tile - 1, which every warp has left
+        if (tid == 0 && tile + 2 < ntiles) fetch(tile + 2);
+        {
+            const unsigned bar = bar_full + 8 * buf, parity = (unsigned)(tile / kStages) & 1u;
+            unsigned spin = 0;
+            while (!mbar_try_wait(bar, parity)) {
+                if (++spin > kSpinLimit) {  // the copy never landed: flag it and carry on
+                    landed = false;
+                    break;
+                }
+            }
         }
         const int nvalid = min(kTile, hi - (lo + tile * kTile));
-        __syncthreads();
+        // (no barrier here: every thread has seen the copy land for itself)
         if (nvalid < kTile) {
             // Rows past the split's end hold stale bytes; their V scales must read as zero.
             for (int i = tid; i < (kTile - nvalid) * (kRowBytes / 16); i += kThreads)
@@ -321,6 +410,8 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p)
         __syncthreads();  // tile buffers, ss and the weight tile are reused by the next tile
     }
 
+    if (!landed && status) atomicCAS(status, 0, 21);
+
     // ---- partials. Output column n of MMA i is dim 32*blk + 4n + i; this thread holds
     // columns 2t, 2t+1, i.e. dims 32*blk + 8t + i and 32*blk + 8t + 4 + i of head g
     // (c0/c1: high-part row, c2/c3: low-part row).
@@ -347,17 +438,23 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p)
 }  // namespace
 
 int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
-    static bool configured[64] = {};
+    static int cta_slots[64] = {};   // 2 resident CTAs per SM; 0 = device not set up yet
+    static int *status_word[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cta_slots[dev] == 0) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kv_tc,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
-        configured[dev] = true;
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        status_word[dev] = device_status_word();
+        cta_slots[dev] = 2 * (sms > 0 ? sms : 1);
     }
     dim3 grid(p.n_kv * p.splits, slots);
-    attn_decode_kv_tc<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    attn_decode_kv_tc<<<grid, kThreads, kSmemBytes, stream>>>(p, cta_slots[dev], status_word[dev]);
     return launch_status();
 }
 
