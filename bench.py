@@ -525,7 +525,7 @@ def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs,
     shard = torch.empty(H, D + 2, device=dev)
     gathered = torch.empty(world, H, D + 2, device=dev)
 
-    def token(i):
+    def token_nccl(i):
         splits = api.decode_splits(max(step_host[i][1], 1))
         for l in range(layers):
             if owners[i] == rank:
@@ -535,44 +535,85 @@ def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs,
             dist.all_gather_into_tensor(gathered, shard)
             api.attn_decode_combine(gathered, out[i, l], H, D, world)
 
-    token(0)
-    torch.cuda.synchronize()
-    dist.barrier()
-    mode = "cuda graph"
+    # The exchange inside the kernel: every rank's workspace is mapped by all ranks (torch's
+    # symmetric memory; no multicast binding is asked for) and the fold kernel stores its
+    # triple straight into the peers' tables.
+    peer_ws, symm_note = None, None
     try:
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        nbytes = api.decode_exchange_bytes(H, D, world)
+        ws_t = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        hdl = symm_mem.rendezvous(ws_t, dist.group.WORLD)
+        ws_t.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        peer_ws = [int(a) for a in hdl.buffer_ptrs]
+    except Exception as e:  # no symmetric memory on this box: the NCCL form only
+        symm_note = f"{type(e).__name__}: {e}"[:160]
+
+    def token_peer(i):
+        splits = api.decode_splits(max(step_host[i][1], 1))
+        for l in range(layers):
+            if owners[i] == rank:
+                api.kv_encode(step_buf[i], kn[i, l], vn[i, l], kc[l], vc[l], KV, D, stride)
+            api.attn_decode_kv_shard_exchange(step_buf[i], q[i, l], kc[l], vc[l], acc, ml, out[i, l],
+                                              H, KV, D, stride, SCALE, splits, peer_ws, rank)
+
+    def measure(token):
+        token(0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        mode = "cuda graph"
+        try:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(steps):
+                        token(i)
+            torch.cuda.current_stream().wait_stream(side)
+            run = graph.replay
+        except Exception as e:  # capture refused: time the eager loop instead
+            mode = f"eager ({type(e).__name__})"
+
+            def run():
                 for i in range(steps):
                     token(i)
-        torch.cuda.current_stream().wait_stream(side)
-        run = graph.replay
-    except Exception as e:  # capture of the collective refused: time the eager loop instead
-        mode = f"eager ({type(e).__name__})"
-
-        def run():
-            for i in range(steps):
-                token(i)
-    run()
-    torch.cuda.synchronize()
-    times = []
-    for _ in range(reps):
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
         run()
-        e1.record()
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        times.append(float(t.item()))
-    ms_step = min(times) / steps
+        times = []
+        for _ in range(reps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times.append(float(t.item()))
+        return min(times) / steps, mode, out[steps - 1].clone()
+
+    ms_nccl, mode_nccl, out_nccl = measure(token_nccl)
+    ms_step, mode, exchange = ms_nccl, mode_nccl, "nccl all_gather"
+    peer = None
+    if peer_ws is not None:
+        out.zero_()
+        ms_peer, mode_peer, out_peer = measure(token_peer)
+        ok = api.check_device_status() == 0
+        same = bool(torch.allclose(out_peer, out_nccl, rtol=0, atol=1e-6))
+        peer = {"ms_per_step": ms_peer, "launch": mode_peer, "status_ok": ok,
+                "matches_nccl_form": same}
+        if ok and same and ms_peer < ms_nccl:
+            ms_step, mode, exchange = ms_peer, mode_peer, "peer-memory stores inside the fold kernel"
     kv_bytes = sum(layers * 2 * KV * (depth + i + 1) * ROW for i in range(steps)) / steps
     gbs = kv_bytes / (ms_step * 1e-3) / 1e9
     return {"depth": depth, "ranks": world, "partition": "sequence", "launch": mode,
+            "exchange": exchange, "ms_per_step_nccl": ms_nccl, "peer_memory_exchange": peer,
+            "symmetric_memory_error": symm_note,
             "ms_per_step": ms_step, "tok_s": 1e3 / ms_step, "kv_bytes_per_step": kv_bytes,
             "kv_gbs": gbs, "frac_hbm_of_all_gpus": gbs / (hbm_gbs * world),
             "exchange_bytes_per_layer_step": world * H * (D + 2) * 4,

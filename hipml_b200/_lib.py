@@ -71,6 +71,10 @@ SIGNATURES = {
     "hipml_attn_decode_kv_shard": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _f, _i, _sz, _sz]),
     "hipml_attn_decode_combine": (_i, [_vp, _vp, _vp, _i, _i, _i]),
+    "hipml_decode_exchange_bytes": (_sz, [_i, _i, _i]),
+    "hipml_attn_decode_kv_shard_exchange": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
+                                                 _i, _i, _f, _i, _sz, _sz, C.POINTER(_vp), _i, _i,
+                                                 _i, _u]),
     "hipml_attn_decode_kv_static": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i,
                                          _sz, _sz]),
     "hipml_attn_decode_cols_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i]),

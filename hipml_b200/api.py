@@ -81,6 +81,23 @@ def attn_decode_combine(gathered, out, n_heads, head_dim, shards):
         _stream(), _p(gathered), _p(out), n_heads, head_dim, shards))
 
 
+def decode_exchange_bytes(n_heads, head_dim, shards) -> int:
+    """Bytes of one rank's workspace for attn_decode_kv_shard_exchange (zero it once)."""
+    return int(_lib.load().hipml_decode_exchange_bytes(n_heads, head_dim, shards))
+
+
+def attn_decode_kv_shard_exchange(step, q, k, v, part_acc, part_ml, out, n_heads, n_kv, head_dim,
+                                  stride, scale, splits, peer_ws, rank, phases=3,
+                                  wait_limit_us=2_000_000, selector=0, k_off=0, v_off=0):
+    """Sequence-split decode with the exchange over peer memory: peer_ws = device addresses
+    (ints) of every rank's workspace as mapped in this process, peer_ws[rank] the local one."""
+    table = (C.c_void_p * len(peer_ws))(*[C.c_void_p(int(a)) for a in peer_ws])
+    _lib.check("attn_decode_kv_shard_exchange", _lib.load().hipml_attn_decode_kv_shard_exchange(
+        _stream(), _p(step), selector, _p(q), _p(k), _p(v), _p(part_acc), _p(part_ml), _p(out),
+        n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off, table, len(peer_ws), rank,
+        phases, wait_limit_us))
+
+
 def attn_decode_kv_static(step, q, k, v, out, n_heads, n_kv, head_dim, stride, scale, splits,
                           selector=0, k_off=0, v_off=0):
     """attn_decode_kv without caller scratch: for callers that cannot allocate device memory.

@@ -18,6 +18,7 @@ SOURCES = [
     "attn_decode_t5.cu",
     "attn_decode_f32.cu",
     "decode_static.cu",
+    "decode_exchange.cu",
     "attn_chunk_scalar.cu",
     "attn_chunk_tc.cu",
     "launchers.cu",

@@ -105,10 +105,17 @@ int hipml_kv_append_chunk_f32(hipml_stream_t stream, float *k_cache, float *v_ca
                                  dim3(256), args, 0, as_stream(stream));
 }
 
+// Peer-memory exchange that replaces the plain fold (hipml_attn_decode_kv_shard_exchange).
+struct ExchangeArgs {
+    void *const *peer_ws;
+    int shards, rank, phases;
+    unsigned wait_limit_us;
+};
+
 static int decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
                      const void *k, const void *v, float *part_acc, float *part_ml, float *out,
                      int n_heads, int n_kv, int head_dim, int stride, float scale, int splits,
-                     size_t k_off, size_t v_off, bool shard) {
+                     size_t k_off, size_t v_off, bool shard, const ExchangeArgs *xch = nullptr) {
     if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
     // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
     // experimental variants have no counterpart here.
@@ -164,6 +171,13 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     } else if (int e = launch_decode_split(as_stream(stream), p, 1, tensor_core)) {
         return e;
     }
+    if (xch) {
+        int *status = device_status_word();
+        if (!status) return launch_status();
+        return launch_decode_fold_exchange(as_stream(stream), part_acc, part_ml, out, n_heads,
+                                           head_dim, splits, xch->peer_ws, xch->shards, xch->rank,
+                                           xch->phases, xch->wait_limit_us, status);
+    }
     if (!shard)
         return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
                                     splits, 1, 0, 0, 0);
@@ -198,6 +212,44 @@ int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selec
                                size_t v_off) {
     return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, shard_out, n_heads, n_kv,
                      head_dim, stride, scale, splits, k_off, v_off, true);
+}
+
+size_t hipml_decode_exchange_bytes(int n_heads, int head_dim, int shards) {
+    if (n_heads <= 0 || head_dim <= 0 || shards <= 0) return 0;
+    return decode_exchange_bytes(n_heads, head_dim, shards);
+}
+
+int hipml_attn_decode_kv_shard_exchange(hipml_stream_t stream, const int *step, int selector,
+                                        const float *q, const void *k, const void *v,
+                                        float *part_acc, float *part_ml, float *out, int n_heads,
+                                        int n_kv, int head_dim, int stride, float scale, int splits,
+                                        size_t k_off, size_t v_off, void *const *peer_ws,
+                                        int shards, int rank, int phases,
+                                        unsigned wait_limit_us) {
+    if (shards < 1 || shards > 16 || rank < 0 || rank >= shards)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: rank %d of %d shards (1..16)", rank,
+                    shards);
+    if (phases < 1 || phases > 3)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: phases %d (1 publish, 2 collect, 3 both)",
+                    phases);
+    if (!peer_ws) return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: no workspace table");
+    for (int w = 0; w < shards; w++)
+        if (!peer_ws[w] || (reinterpret_cast<size_t>(peer_ws[w]) & 255) != 0)
+            return fail(HIPML_ERR_WORKSPACE, "exchange: workspace %d missing or not 256-byte aligned", w);
+    if (wait_limit_us > 10000000u) wait_limit_us = 10000000u;
+    ExchangeArgs x = {peer_ws, shards, rank, phases, wait_limit_us};
+    if (phases == 2) {
+        // collect only: no split pass, the partials are not read
+        if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
+        if (head_dim % 32 != 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "head_dim %d", head_dim);
+        int *status = device_status_word();
+        if (!status) return launch_status();
+        return launch_decode_fold_exchange(as_stream(stream), part_acc, part_ml, out, n_heads,
+                                           head_dim, splits < 1 ? 1 : splits, peer_ws, shards, rank,
+                                           2, wait_limit_us, status);
+    }
+    return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
+                     head_dim, stride, scale, splits, k_off, v_off, true, &x);
 }
 
 int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, float *out,

@@ -75,6 +75,13 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part
                     float *part_ml, int n_heads, int n_kv, int pos0, int tokens, int cap,
                     int splits, int variant, void *workspace, int *status);
 
+// Fold + peer-memory exchange + final fold of a sequence-split decode (decode_exchange.cu).
+size_t decode_exchange_bytes(int n_heads, int head_dim, int shards);
+int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, const float *part_ml,
+                                float *out, int n_heads, int head_dim, int splits,
+                                void *const *peer_ws, int shards, int rank, int phases,
+                                unsigned wait_limit_us, int *status);
+
 // f32-cache decode for `rows` consecutive columns (attn_decode_f32.cu): split pass + fold.
 int launch_decode_cols_f32(cudaStream_t stream, const float *q, const float *k, const float *v,
                            float *part_acc, float *part_ml, float *out, int n_heads, int n_kv,

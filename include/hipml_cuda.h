@@ -208,6 +208,29 @@ int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selec
 int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, float *out,
                               int n_heads, int head_dim, int shards);
 
+/* The same sequence-split decode with the exchange done by the kernel itself over peer memory
+ * instead of a collective call (no counterpart in the reference). Every rank owns a workspace
+ * of hipml_decode_exchange_bytes(...) bytes, 256-byte aligned, zero-filled once before the
+ * first call, that every other rank has mapped (peer access, IPC handle or symmetric memory);
+ * peer_ws is a HOST array of `shards` device pointers, peer_ws[w] = rank w's workspace as
+ * mapped in this process, peer_ws[rank] = the local one. One call = split pass over the local
+ * rows, then one kernel that folds the local partials, stores the folded triple into every
+ * rank's workspace, raises this rank's flag there, waits until every rank's flag of the same
+ * call has arrived and folds the shards into out f32 [n_heads][head_dim]. All ranks must make
+ * the same sequence of calls. phases: 3 = all of it; 1 = split pass + publish only and 2 =
+ * wait + final fold only (the two halves, for hosts that drive several ranks from one stream).
+ * The wait is bounded by wait_limit_us (capped at 10 s): when it runs out the kernel leaves
+ * `out` untouched and hipml_check_device_status reports 31. Safe to capture in a graph and
+ * replay (the call counters live in the workspace and only grow). */
+size_t hipml_decode_exchange_bytes(int n_heads, int head_dim, int shards);
+int hipml_attn_decode_kv_shard_exchange(hipml_stream_t stream, const int *step, int selector,
+                                        const float *q, const void *k, const void *v,
+                                        float *part_acc, float *part_ml, float *out, int n_heads,
+                                        int n_kv, int head_dim, int stride, float scale, int splits,
+                                        size_t k_off, size_t v_off, void *const *peer_ws,
+                                        int shards, int rank, int phases,
+                                        unsigned wait_limit_us);
+
 /* The same decode for callers that cannot allocate device memory (this entry has no
  * counterpart in the reference): a host that serves from a fixed arena and may not call
  * cudaMalloc, a binding without a device allocator, a loop that must stay clear of the

@@ -245,6 +245,79 @@ def test_sequence_split_shards_fold_to_the_whole_cache(shards, seq):
     assert O.max_abs(mirror.ravel(), out.cpu().numpy()) < 1e-6
 
 
+@pytest.mark.parametrize("shards,seq", [(2, 700), (4, 3000), (8, 5)])
+def test_peer_memory_exchange_on_one_gpu_in_two_phases(shards, seq):
+    """The fused fold + exchange + fold of the multi-GPU decode, with every rank's workspace
+    on this one GPU. The two halves run as separate calls in stream order (all ranks publish,
+    then all collect), so no kernel ever waits for a later one; three tokens in a row check
+    the epoch counters and the alternating table slots."""
+    from hipml_b200 import api, sharding
+    heads, n_kv, hd, scale = 24, 4, 256, 0.0625
+    capacity = seq + 9
+    rng = O.Rng(0xE8C4 + shards)
+    kb = O.quantize_q8(rng.normals(n_kv * (seq + 3) * hd)).reshape(n_kv, seq + 3, 272)
+    vb = O.quantize_q8(rng.normals(n_kv * (seq + 3) * hd)).reshape(n_kv, seq + 3, 272)
+    nbytes = api.decode_exchange_bytes(heads, hd, shards)
+    ws = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(shards)]
+    table = [w.data_ptr() for w in ws]
+    ranks = []
+    for r in range(shards):
+        lo, hi = sharding.decode_shard_range(capacity, shards, r)
+        stride = max(hi - lo, 1)
+        kc, vc = _canary_cache(n_kv, stride, 272), _canary_cache(n_kv, stride, 272)
+        n = sharding.local_length(seq + 3, lo, hi)
+        kc[:, :n], vc[:, :n] = kb[:, lo:lo + n], vb[:, lo:lo + n]
+        ranks.append((lo, hi, stride, _dev(kc), _dev(vc)))
+    for tok in range(3):
+        live = seq + tok + 1
+        q = rng.normals(heads * hd)
+        expected = O.attn_decode_kv_q8(q, kb[:, :live], vb[:, :live], heads, n_kv, hd, live, scale)
+        dq = _dev(q)
+        outs = [torch.full((heads * hd,), float("nan"), device="cuda") for _ in range(shards)]
+        scratch = []
+        for phase in (1, 2):
+            for r, (lo, hi, stride, kc, vc) in enumerate(ranks):
+                n = sharding.local_length(live, lo, hi)
+                splits = api.decode_splits(max(n, 1))
+                if phase == 1:
+                    scratch.append((torch.full((heads * splits * hd,), float("nan"), device="cuda"),
+                                    torch.full((heads * splits * 2,), float("nan"), device="cuda")))
+                acc, ml = scratch[r]
+                api.attn_decode_kv_shard_exchange(_step(max(n - 1, 0), n), dq, kc, vc, acc, ml,
+                                                  outs[r], heads, n_kv, hd, stride, scale, splits,
+                                                  table, r, phases=phase, wait_limit_us=1000)
+        assert api.check_device_status() == 0
+        for r in range(shards):
+            _assert_close(expected, outs[r].cpu().numpy())
+    # header of every workspace: epoch 3, CTA counter back at 0, every rank's flag at 3
+    for w in ws:
+        hdr = w[:256].view(torch.int32).cpu().numpy()
+        assert hdr[0] == 3 and hdr[1] == 0 and list(hdr[4:4 + shards]) == [3] * shards
+
+
+def test_exchange_wait_is_bounded_and_reports_status():
+    """A collect whose peer never publishes gives up after the limit: status 31, `out` as it was."""
+    from hipml_b200 import api
+    heads, n_kv, hd, shards = 24, 4, 256, 2
+    nbytes = api.decode_exchange_bytes(heads, hd, shards)
+    ws = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(shards)]
+    # rank 0 has published epoch 1 (flag of rank 0 only); rank 1 stays silent
+    hdr = ws[0][:256].view(torch.int32)
+    hdr[0] = 1
+    hdr[4] = 1
+    out = torch.full((heads * hd,), 7.0, device="cuda")
+    dummy = torch.zeros(heads * hd + heads * 2, device="cuda")
+    step = _step(0, 1)
+    z = torch.zeros(272 * n_kv, dtype=torch.uint8, device="cuda")
+    api.attn_decode_kv_shard_exchange(step, dummy, z, z, dummy, dummy, out, heads, n_kv, hd, 1,
+                                      0.0625, 1, [w.data_ptr() for w in ws], 0, phases=2,
+                                      wait_limit_us=200)
+    with pytest.raises(Exception, match="code 31"):
+        api.check_device_status()          # reports the code and clears the word
+    assert api.check_device_status() == 0
+    assert torch.all(out == 7.0)
+
+
 @pytest.mark.parametrize("rows,pos0,n_ctx", [(1, 36, 37), (1, 0, 8), (4, 29, 80), (3, 997, 1000)])
 def test_f32_cache_decode_columns(rows, pos0, n_ctx):
     """AttnLayer::attention_cols over the f32 position-major cache: the reference's
