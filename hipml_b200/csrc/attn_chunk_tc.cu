@@ -298,6 +298,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(unsigned addr) {
     return d;
 }
 
+// The same descriptor in two steps: its low word for a tile base (start address in 16-byte
+// units, leading byte offset field 1), and the 64-bit value for a low word that may have
+// been advanced by a k step (the high word is constant: stride 1024 B, version 1, 128-byte
+// swizzle). Shared-memory addresses stay below 256 KB, so the sum cannot leave the field.
+__device__ __forceinline__ unsigned desc_lo_sw128(unsigned addr) {
+    return ((addr & 0x3ffff) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint64_t desc_from(unsigned lo) {
+    constexpr unsigned kHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)kHi << 32) | lo;
+}
+
 // Instruction descriptor: f16 x f16 -> f32 accumulate, both operands K-major, M x N.
 __host__ __device__ constexpr unsigned idesc_f16(unsigned m, unsigned n) {
     return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
@@ -615,31 +627,45 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                 tc_commit<kCtas>(bar_empty + 8 * (n % kStages));
                 n++;
             };
+            // The issuing thread is a serial instruction stream: an MMA of N = 128 keeps the
+            // tensor pipe busy for only ~64 cycles, so every instruction between two MMAs
+            // counts. Descriptors are therefore formed once per 64-element chunk and advanced
+            // by adding the 16-byte-unit offset of the k step to their low word.
             // S += Q[:, 64-dim chunk c] K[:, chunk c]^T with the K chunk (hi at b_hi, lo at b_lo)
             auto qk_chunk = [&](unsigned d, int c, unsigned b_hi, unsigned b_lo) {
                 const unsigned a_hi = q_addr + c * kTileBytes, a_lo = a_hi + 4 * kTileBytes;
-                for (int term = 0; term < terms; term++) {
-                    const unsigned a = term == 1 ? a_lo : a_hi;
-                    const unsigned b = term == 2 ? b_lo : b_hi;
+                const unsigned da[2] = {desc_lo_sw128(a_hi), desc_lo_sw128(a_lo)};
+                const unsigned db[2] = {desc_lo_sw128(b_hi), desc_lo_sw128(b_lo)};
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; k16++)
-                        tc_mma_ss<kCtas>(d, smem_desc_sw128(a + k16 * 32), smem_desc_sw128(b + k16 * 32),
-                                         kIdescS, (c | term | k16) != 0);
+                for (int term = 0; term < 3; term++) {
+                    if (term < terms) {
+                        const unsigned a = da[term == 1], b = db[term == 2];
+#pragma unroll
+                        for (int k16 = 0; k16 < 4; k16++)
+                            tc_mma_ss<kCtas>(d, desc_from(a + 2 * k16), desc_from(b + 2 * k16), kIdescS,
+                                             (c | term | k16) != 0);
+                    }
                 }
             };
             auto qk = [&](int i) {  // i = tile index relative to kt_lo
                 const unsigned d = tmem_s[i & 1];
+                // (unrolled: the chunk index decides at compile time which MMA overwrites S)
                 if constexpr (kCtas == 1) {
-                    for (int c = 0; c < 4 && ok; c++) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        if (!ok) break;
                         const unsigned b = slot(2);
                         if (!ok) break;
                         qk_chunk(d, c, b, b + kHalf);
                         release();
                     }
                 } else {
-                    for (int cp = 0; cp < 2 && ok; cp++) {
+#pragma unroll
+                    for (int cp = 0; cp < 2; cp++) {
+                        if (!ok) break;
                         const unsigned b = slot(2);
                         if (!ok) break;
+#pragma unroll
                         for (int cc = 0; cc < 2; cc++)
                             qk_chunk(d, 2 * cp + cc, b + cc * (kHalf / 2), b + kHalf + cc * (kHalf / 2));
                         release();
@@ -649,20 +675,29 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             };
             auto pv = [&](int i) {
                 const unsigned a_base = tmem_s[i & 1];
-                for (int kc = 0; kc < 2 && ok; kc++)
-                    for (int dh = 0; dh < (kCtas == 1 ? 2 : 1) && ok; dh++) {
+                const unsigned later = i != 0;   // only the first tile's first MMA overwrites O
+#pragma unroll
+                for (int kc = 0; kc < 2; kc++)
+#pragma unroll
+                    for (int dh = 0; dh < (kCtas == 1 ? 2 : 1); dh++) {
+                        if (!ok) break;
                         const unsigned b_hi = slot(3), b_lo = b_hi + kHalf;
                         if (!ok) break;
                         // single CTA: 128 output dims per slot; pair: all 256 (half from each CTA)
                         const unsigned d = tmem_o + dh * 128;
-                        for (int term = 0; term < terms; term++) {
-                            const unsigned b = term == 2 ? b_lo : b_hi;
+                        const unsigned db[2] = {desc_lo_sw128(b_hi), desc_lo_sw128(b_lo)};
+                        const unsigned a0 = a_base + kc * 64;
 #pragma unroll
-                            for (int k16 = 0; k16 < 4; k16++) {
-                                // P of keys [16*(4kc+k16), +16): hi pairs in 8 columns, lo in the next 8
-                                const unsigned a = a_base + (kc * 4 + k16) * 16 + (term == 1 ? 8 : 0);
-                                tc_mma_ts<kCtas>(d, a, smem_desc_sw128(b + k16 * 32), kIdescO,
-                                                 (i | kc | term | k16) != 0);
+                        for (int term = 0; term < 3; term++) {
+                            if (term < terms) {
+                                const unsigned b = db[term == 2];
+#pragma unroll
+                                for (int k16 = 0; k16 < 4; k16++) {
+                                    // P of keys [16*(4kc+k16), +16): hi pairs in 8 columns, lo in the next 8
+                                    const unsigned a = a0 + k16 * 16 + (term == 1 ? 8 : 0);
+                                    tc_mma_ts<kCtas>(d, a, desc_from(b + 2 * k16), kIdescO,
+                                                     (kc | term | k16) != 0 ? 1u : later);
+                                }
                             }
                         }
                         release();

@@ -9,7 +9,7 @@
 //   publish  each CTA folds its (head, 32 dims) of the local partials and stores the result
 //            into slot [e & 1][rank] of EVERY rank's table (its own included); the last CTA
 //            to finish (counter) fences at system scope, stores e into flags[rank] of every
-//            rank with release semantics and advances the local epoch;
+//            rank and advances the local epoch;
 //   collect  each CTA waits until flags[w] >= e for every rank w of its own header (bounded
 //            polling: when the limit runs out it records status 31 and leaves `out` alone),
 //            then folds the shards' triples of its (head, 32 dims) into `out`.
@@ -44,8 +44,8 @@ __device__ __forceinline__ int ld_acquire_sys(const int *p) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(int *p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(int *p, int v) {
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float *gather_slot(unsigned char *ws, int parity, int shards, int n_heads,
@@ -111,10 +111,12 @@ __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams 
                 const int done = atomicAdd(hdr + 1, 1);
                 if (done == (int)gridDim.x - 1) {
                     // last CTA of this rank: everything of epoch e is on its way
+                    // one system-scope fence orders all of it before the flags; the flag stores
+                    // themselves are relaxed so that they leave back to back
                     __threadfence_system();
                     hdr[1] = 0;
                     for (int w = 0; w < p.shards; w++)
-                        st_release_sys(reinterpret_cast<int *>(p.ws[w]) + 4 + p.rank, e);
+                        st_relaxed_sys(reinterpret_cast<int *>(p.ws[w]) + 4 + p.rank, e);
                     *reinterpret_cast<volatile int *>(hdr) = e;
                 }
             }
@@ -133,7 +135,7 @@ __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams 
                     ok = true;
                     break;
                 }
-                __nanosleep(500);
+                __nanosleep(100);
             }
             if (!ok) {
                 s_ok = 0;
@@ -182,7 +184,7 @@ int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, cons
     p.shards = shards;
     p.rank = rank;
     p.phases = phases;
-    p.wait_polls = wait_limit_us < 1 ? 1u : wait_limit_us * 2u;   // ~0.5 us per poll
+    p.wait_polls = wait_limit_us < 1 ? 1u : wait_limit_us * 4u;   // ~0.25 us per poll (sleep + load)
     for (int w = 0; w < kMaxShards; w++)
         p.ws[w] = w < shards ? reinterpret_cast<unsigned char *>(peer_ws[w]) : nullptr;
     attn_decode_fold_exchange<<<n_heads * (head_dim >> 5), 256, 0, stream>>>(p);
