@@ -17,6 +17,8 @@ namespace hipml {
 namespace {
 
 __global__ void __launch_bounds__(128) attn_chunk_scalar(ChunkScalarParams p) {
+    griddep_launch();
+    griddep_wait();
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int nsp = p.splits < 2 ? 1 : p.splits;
@@ -123,6 +125,8 @@ extern "C" __global__ void attn_chunk_combine_f32(const float *__restrict__ part
                                                   float *__restrict__ out, int n_heads,
                                                   int head_dim, int tokens, int qslots,
                                                   int splits) {
+    griddep_launch();
+    griddep_wait();
     const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     if (t >= tokens || d >= head_dim) return;
     float big = -INFINITY;
@@ -147,8 +151,7 @@ int launch_chunk_scalar(cudaStream_t stream, const ChunkScalarParams &p) {
     const long long warps = (long long)p.tokens * p.n_heads * nsp;
     if (warps == 0) return 0;
     const long long blocks = (warps + 3) / 4;
-    attn_chunk_scalar<<<(unsigned)blocks, 128, 0, stream>>>(p);
-    return launch_status();
+    return launch_pdl(attn_chunk_scalar, dim3((unsigned)blocks), dim3(128), 0, stream, 1, p);
 }
 
 // The same fold for head_dim 256 with 16-byte accesses: 64 threads per (row, head), four
@@ -158,6 +161,8 @@ __global__ void __launch_bounds__(256) attn_chunk_combine_256(const float *__res
                                                               const float *__restrict__ part_ml,
                                                               float *__restrict__ out, int n_heads,
                                                               int tokens, int qslots, int splits) {
+    griddep_launch();
+    griddep_wait();
     const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 6);
     if (pair >= (long long)tokens * n_heads) return;
     const int t = (int)(pair / n_heads), h = (int)(pair - (long long)t * n_heads);
@@ -192,14 +197,12 @@ int launch_chunk_combine(cudaStream_t stream, const float *part_acc, const float
         ((reinterpret_cast<size_t>(part_acc) | reinterpret_cast<size_t>(out)) & 15) == 0 &&
         (reinterpret_cast<size_t>(part_ml) & 7) == 0) {
         const long long pairs = (long long)tokens * n_heads;
-        attn_chunk_combine_256<<<(unsigned)((pairs + 3) / 4), 256, 0, stream>>>(
-            part_acc, part_ml, out, n_heads, tokens, qslots, splits);
-        return launch_status();
+        return launch_pdl(attn_chunk_combine_256, dim3((unsigned)((pairs + 3) / 4)), dim3(256), 0, stream, 1,
+                          part_acc, part_ml, out, n_heads, tokens, qslots, splits);
     }
     dim3 grid(qslots, n_heads);
-    attn_chunk_combine_f32<<<grid, head_dim, 0, stream>>>(part_acc, part_ml, out, n_heads,
-                                                          head_dim, tokens, qslots, splits);
-    return launch_status();
+    return launch_pdl(attn_chunk_combine_f32, grid, dim3(head_dim), 0, stream, 1, part_acc, part_ml, out,
+                      n_heads, head_dim, tokens, qslots, splits);
 }
 
 const void *lookup_chunk_kernel(const char *name) {

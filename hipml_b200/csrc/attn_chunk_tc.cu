@@ -385,6 +385,8 @@ __device__ __forceinline__ void stage_store8(__half *hi, __half *lo, size_t at, 
 // would otherwise fill less than one wave of the device).
 __global__ void __launch_bounds__(256) attn_chunk_stage(StageParams p) {
     __shared__ float vs[64][129];
+    griddep_launch();
+    griddep_wait();
     const int kvh = blockIdx.y, key0 = (p.tile0 + blockIdx.x) * 64;
     const int tid = threadIdx.x;
     if (blockIdx.z == 0) {
@@ -432,6 +434,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
               const __grid_constant__ CUtensorMap map_vt_hi,
               const __grid_constant__ CUtensorMap map_vt_lo, ChunkTcParams p) {
     extern __shared__ unsigned char smem_raw[];
+    griddep_launch();
     unsigned char *smem =
         reinterpret_cast<unsigned char *>((reinterpret_cast<size_t>(smem_raw) + 1023) & ~(size_t)1023);
     if ((size_t)(smem - smem_raw) + kSmemNeed > (size_t)kSmemBytes) {
@@ -543,6 +546,10 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         if (lane == 0 && n_tiles > 0) {
             unsigned n = 0;  // chunks issued
             bool ok = true;
+            // The staged image (and, behind it, the scratch and the output rows) belongs to
+            // the previous grids; the query tile above is the caller's input. Everything the
+            // CTA does to memory from here on follows one of this thread's copies.
+            griddep_wait();
             // Takes the next ring slot once the MMAs that read it have completed and arms its
             // full barrier; in a pair only the leader arms, with both CTAs' bytes (the peer's
             // copies complete on the leader's barrier).
@@ -823,6 +830,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         const int rq = r / p.group, rh = r - rq * p.group;
         const int h = kvh * p.group + rh;
         if (ok) {
+            griddep_wait();   // (already satisfied unless the CTA had no key tiles to wait for)
             tc_fence_after();
             const bool norm = p.splits < 2;
             const float inv = norm ? (l > 0.0f ? 1.0f / l : 0.0f) : 1.0f;
@@ -925,8 +933,7 @@ int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_c
     sp.tile0 = key_from / 64;
     const int tile_end = (key_to + kKeyTile - 1) / kKeyTile * kKeyTile / 64;
     if (tile_end <= sp.tile0) return 0;
-    attn_chunk_stage<<<dim3(tile_end - sp.tile0, n_kv, 3), 256, 0, stream>>>(sp);
-    return launch_status();
+    return launch_pdl(attn_chunk_stage, dim3(tile_end - sp.tile0, n_kv, 3), dim3(256), 0, stream, 1, sp);
 }
 
 // Launches the tensor-core kernel over a workspace staged for `cap` keys per head.
@@ -980,27 +987,13 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part
     const int nsp = splits < 2 ? 1 : splits;
     const int qtiles = (tokens + p.qtile - 1) / p.qtile;
     if (!pair) {
-        attn_chunk_tc<1><<<dim3(qtiles, n_kv, nsp), kTcThreads, kSmemBytes, stream>>>(mk_hi, mk_lo, mv_hi,
-                                                                                     mv_lo, p);
-        return launch_status();
+        return launch_pdl(attn_chunk_tc<1>, dim3(qtiles, n_kv, nsp), dim3(kTcThreads), (size_t)kSmemBytes,
+                          stream, 1, mk_hi, mk_lo, mv_hi, mv_lo, p);
     }
     // Clusters of two CTAs along x: consecutive query tiles of one KV head (an odd tile
     // count leaves the last pair's second CTA without live queries).
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((qtiles + 1) / 2 * 2, n_kv, nsp);
-    cfg.blockDim = dim3(kTcThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_chunk_tc<2>, mk_hi, mk_lo, mv_hi, mv_lo, p);
-    if (e != cudaSuccess) return (int)e;
-    return launch_status();
+    return launch_pdl(attn_chunk_tc<2>, dim3((qtiles + 1) / 2 * 2, n_kv, nsp), dim3(kTcThreads),
+                      (size_t)kSmemBytes, stream, 2, mk_hi, mk_lo, mv_hi, mv_lo, p);
 }
 
 }  // namespace hipml

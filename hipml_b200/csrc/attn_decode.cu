@@ -43,6 +43,8 @@ __device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int
 // ------------------------------------------------------------ scalar body
 
 __global__ void __launch_bounds__(128) attn_decode_kv_scalar(DecodeParams p) {
+    griddep_launch();
+    griddep_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int slot = blockIdx.y;
@@ -119,6 +121,8 @@ __global__ void __launch_bounds__(128) attn_decode_kv_scalar(DecodeParams p) {
 // serial walk over the splits, which costs tens of microseconds at 256 splits; here a CTA
 // of 8 warps owns 32 output dims of one head and each warp folds every 8th split.
 __global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
+    griddep_launch();
+    griddep_wait();
     __shared__ float s_max[8];
     __shared__ float s_num[8][32];
     __shared__ float s_den[8];
@@ -173,6 +177,8 @@ extern "C" __global__ void attn_decode_kv_reduce(const float *__restrict__ part_
                                                  const float *__restrict__ part_ml,
                                                  float *__restrict__ out, int head_dim,
                                                  int splits) {
+    griddep_launch();
+    griddep_wait();
     const int h = blockIdx.x, d = threadIdx.x;
     if (d >= head_dim) return;
     const float *ml = part_ml + (size_t)h * splits * 2;
@@ -193,6 +199,8 @@ extern "C" __global__ void attn_decode_kv_reduce_b(const float *__restrict__ par
                                                    float *__restrict__ out, int head_dim,
                                                    int splits, int acc_slot, int ml_slot,
                                                    int out_slot) {
+    griddep_launch();
+    griddep_wait();
     const int slot = blockIdx.y;
     const int h = blockIdx.x, d = threadIdx.x;
     if (d >= head_dim) return;
@@ -215,15 +223,13 @@ int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, b
     if (tensor_core) return launch_decode_tc(stream, p, slots);
     const int warps = p.n_heads * p.splits;
     dim3 grid((warps + 3) / 4, slots);
-    attn_decode_kv_scalar<<<grid, 128, 0, stream>>>(p);
-    return launch_status();
+    return launch_pdl(attn_decode_kv_scalar, grid, dim3(128), 0, stream, 1, p);
 }
 
 // Host-side launch of the fold.
 int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots) {
     dim3 grid(n_heads * (p.head_dim >> 5), slots);
-    attn_decode_fold<<<grid, 256, 0, stream>>>(p);
-    return launch_status();
+    return launch_pdl(attn_decode_fold, grid, dim3(256), 0, stream, 1, p);
 }
 
 // The usual case: partials [n_heads][splits][head_dim] / [n_heads][splits][2] -> out[slot][h][d].

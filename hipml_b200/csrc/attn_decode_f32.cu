@@ -27,6 +27,8 @@ struct ColsParams {
 namespace {
 
 __global__ void __launch_bounds__(128) attn_decode_cols_f32(ColsParams p) {
+    griddep_launch();
+    griddep_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int col = blockIdx.y;
@@ -83,6 +85,8 @@ extern "C" __global__ void kv_append_cols_f32(float *__restrict__ k_cache,
                                               const float *__restrict__ k,
                                               const float *__restrict__ v, int pos0, int rows,
                                               int width) {
+    griddep_launch();
+    griddep_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= 2LL * width * rows) return;
     const int c = (int)(i / (2 * width));
@@ -117,7 +121,7 @@ int launch_decode_cols_f32(cudaStream_t stream, const float *q, const float *k, 
     p.splits = splits;
     p.per = (n_ctx + splits - 1) / splits;
     dim3 grid((n_heads * splits + 3) / 4, rows);
-    attn_decode_cols_f32<<<grid, 128, 0, stream>>>(p);
+    if (int e = launch_pdl(attn_decode_cols_f32, grid, dim3(128), 0, stream, 1, p)) return e;
     if (int e = launch_status()) return e;
     return launch_decode_reduce(stream, part_acc, part_ml, out, n_heads, head_dim, splits, rows,
                                 (long long)n_heads * splits * head_dim,

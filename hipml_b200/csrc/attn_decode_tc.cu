@@ -139,32 +139,18 @@ __device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
     return *reinterpret_cast<const unsigned *>(&r);
 }
 
-// Rows [lo, hi) of split `split`. The partials are scratch: only their fold is defined, so
-// the rows are dealt out to suit this kernel rather than as ceil(len / splits) runs. A run
-// is a whole number of 64-key tiles (no split ends in a mostly empty tile), and the number
-// of tiles per run is the one that minimises waves x (tiles + 1) for the CTA slots of the
-// device (`cta_slots`; the +1 stands for a CTA's query set-up and partial write): 100,000
-// rows in 256 splits would be 1024 CTAs of 6.1 tiles = 3.5 waves of 7 tile times, 143 runs
-// of 11 tiles per KV head are 1.9 waves = 2 x 11. Splits past the last run get no rows and
-// write neutral partials.
-__device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split,
-                                            int cta_slots, int &lo, int &hi) {
+// Rows [lo, hi) of split `split`: the reference's runs of ceil(span / splits) rows (span =
+// the live length, or the cache capacity for the multi-slot form), rounded up to whole
+// 64-key tiles so that no run ends in a mostly empty tile. The partials are scratch (only
+// their fold is defined), so splits past the last run simply get no rows and write neutral
+// partials. Coarser runs were measured too (fewer, longer CTAs chosen from the device's CTA
+// slots): no gain for one stream at 100,000 rows and 20 % slower for 8 - 16 slots of mixed
+// depth, where the longest CTAs form the tail.
+__device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int &lo,
+                                            int &hi) {
     const int len = p.len[slot * p.len_stride + p.len_offset];
-    const int tiles = (len + kTile - 1) / kTile;
-    const int t_min = max((tiles + p.splits - 1) / p.splits, 1);
-    const int ctas_per_run = p.n_kv * (int)gridDim.y;
-    int best_t = t_min, best_cost = 0x7fffffff;
-    for (int t = t_min; t < t_min + 24; t++) {
-        const int runs = (tiles + t - 1) / t;
-        const int waves = (runs * ctas_per_run + cta_slots - 1) / cta_slots;
-        const int cost = waves * (t + 1);
-        if (cost < best_cost) {
-            best_cost = cost;
-            best_t = t;
-        }
-        if (runs <= 1) break;
-    }
-    const int per = best_t * kTile;
+    const int span = p.by_stride ? p.stride : len;
+    const int per = ((span + p.splits - 1) / p.splits + kTile - 1) / kTile * kTile;
     lo = min(split * per, len);
     hi = min(lo + per, len);
 }
@@ -191,9 +177,9 @@ __device__ __forceinline__ void score_block(const unsigned char *ktile, int key_
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int cta_slots,
-                                                                  int *status) {
+__global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int *status) {
     extern __shared__ __align__(16) unsigned char smem[];
+    griddep_launch();
     unsigned char *ktile[kStages], *vtile[kStages];
 #pragma unroll
     for (int s = 0; s < kStages; s++) {
@@ -214,10 +200,11 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     const int kg = warp & 3, dh = warp >> 2;
 
     int lo, hi;
-    split_range(p, slot, split, cta_slots, lo, hi);
+    split_range(p, slot, split, lo, hi);
     const int ntiles = (hi - lo + kTile - 1) / kTile;
     if (ntiles == 0) {
         // A split without rows: neutral partials (zero sum, -inf maximum), nothing else.
+        griddep_wait();   // the scratch may still be read by the previous grid
         for (int i = tid; i < group * 256; i += kThreads) {
             const int h = kvh * group + (i >> 8);
             p.part_acc[(size_t)slot * p.acc_slot + ((size_t)h * p.splits + split) * 256 + (i & 255)] = 0.0f;
@@ -254,6 +241,11 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
 #pragma unroll
         for (int s = 0; s < kStages; s++) mbar_init(bar_full + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The cache rows (the append of this step among them) and the scratch belong to the
+        // previous grids: nothing of them is touched before this wait. Every later access of
+        // the CTA follows one of these copies, so the other threads need no wait of their
+        // own; the query set-up below overlaps the previous grid's tail.
+        griddep_wait();
         fetch(0);
         if (ntiles > 1) fetch(1);
     }
@@ -411,6 +403,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     }
 
     if (!landed && status) atomicCAS(status, 0, 21);
+    griddep_wait();   // (long satisfied: thread 0 waited before the first copy)
 
     // ---- partials. Output column n of MMA i is dim 32*blk + 4n + i; this thread holds
     // columns 2t, 2t+1, i.e. dims 32*blk + 8t + i and 32*blk + 8t + 4 + i of head g
@@ -438,24 +431,20 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
 }  // namespace
 
 int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
-    static int cta_slots[64] = {};   // 2 resident CTAs per SM; 0 = device not set up yet
-    static int *status_word[64] = {};
+    static int *status_word[64] = {};   // nullptr = device not set up yet
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    if (cta_slots[dev] == 0) {
+    if (status_word[dev] == nullptr) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kv_tc,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
-        int sms = 0;
-        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return (int)e;
         status_word[dev] = device_status_word();
-        cta_slots[dev] = 2 * (sms > 0 ? sms : 1);
+        if (status_word[dev] == nullptr) return launch_status();
     }
     dim3 grid(p.n_kv * p.splits, slots);
-    attn_decode_kv_tc<<<grid, kThreads, kSmemBytes, stream>>>(p, cta_slots[dev], status_word[dev]);
-    return launch_status();
+    return launch_pdl(attn_decode_kv_tc, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, p,
+                      status_word[dev]);
 }
 
 }  // namespace hipml

@@ -4,19 +4,22 @@
 // call.
 //
 // Every rank owns a workspace that all ranks have mapped (peer access, IPC or symmetric
-// memory): a header { epoch, CTA counter, flags[16] } and a double-buffered table
-// gather[2][shards][n_heads][head_dim + 2]. A call with epoch e (the local epoch + 1):
-//   publish  each CTA folds its (head, 32 dims) of the local partials and stores the result
-//            into slot [e & 1][rank] of EVERY rank's table (its own included); the last CTA
-//            to finish (counter) fences at system scope, stores e into flags[rank] of every
-//            rank and advances the local epoch;
-//   collect  each CTA waits until flags[w] >= e for every rank w of its own header (bounded
-//            polling: when the limit runs out it records status 31 and leaves `out` alone),
-//            then folds the shards' triples of its (head, 32 dims) into `out`.
+// memory): a header { epoch, CTA counter } and a double-buffered table
+// cell[2][shards][n_heads][head_dim + 2] of 8-byte cells { value bits, epoch tag }. A call
+// with epoch e (the local epoch + 1):
+//   publish  each CTA folds its (head, 32 dims) of the local partials and stores every
+//            result, paired with the tag e in ONE 8-byte store, into slot [e & 1][rank] of
+//            EVERY rank's table (its own included). A cell is valid the moment its tag
+//            reads e, so there is no fence, no flag and no second round trip: the exchange
+//            costs one NVLink store latency.
+//   collect  each CTA polls the cells of its (head, 32 dims) of every rank in its own table
+//            until their tags read e (bounded polling: when the limit runs out it records
+//            status 31 and leaves `out` alone), then folds the shards' triples into `out`.
 // A rank can run at most one epoch ahead of a peer (its collect of epoch e needs the peer's
 // publish of e, which comes after the peer's collect of e - 1), so two table slots are
-// enough. The epochs live in device memory and only grow, so a captured graph can be
-// replayed. All ranks must make the same sequence of calls.
+// enough. The epoch lives in device memory and only grows (the last CTA of a call advances
+// it), so a captured graph can be replayed. All ranks must make the same sequence of calls,
+// and the workspace starts zero-filled (tag 0 is never a valid epoch).
 //
 // The algebra is the reference's split-K reduce (crates/hipml-kernels/kernels/
 // attn_decode_kv.hip:491-532) applied twice; the reference itself is single-GPU.
@@ -27,7 +30,7 @@ namespace hipml {
 namespace {
 
 constexpr int kMaxShards = 16;
-constexpr int kHeaderBytes = 256;   // int epoch, counter, pad[2], flags[16]
+constexpr int kHeaderBytes = 256;   // int epoch, CTA counter
 
 struct ExchangeParams {
     const float *acc;    // local partials [n_heads][splits][head_dim]
@@ -39,27 +42,47 @@ struct ExchangeParams {
     unsigned char *ws[kMaxShards];   // every rank's workspace as mapped in this process
 };
 
-__device__ __forceinline__ int ld_acquire_sys(const int *p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// One 8-byte store / load, system scope, no ordering with other accesses needed: the tag
+// travels with the value.
+__device__ __forceinline__ void st_cell(uint2 *p, float value, int tag) {
+    asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(value)),
+                 "r"(tag)
+                 : "memory");
+}
+__device__ __forceinline__ uint2 ld_cell(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_relaxed_sys(int *p, int v) {
-    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+
+__device__ __forceinline__ uint2 *cell_row(unsigned char *ws, int parity, int shards, int n_heads,
+                                           int head_dim, int shard, int h) {
+    uint2 *g = reinterpret_cast<uint2 *>(ws + kHeaderBytes);
+    return g + (((size_t)parity * shards + shard) * n_heads + h) * (head_dim + 2);
 }
 
-__device__ __forceinline__ float *gather_slot(unsigned char *ws, int parity, int shards, int n_heads,
-                                              int head_dim, int shard, int h) {
-    float *g = reinterpret_cast<float *>(ws + kHeaderBytes);
-    return g + (((size_t)parity * shards + shard) * n_heads + h) * (head_dim + 2);
+// Polls one cell until its tag is e; false when the limit ran out.
+__device__ __forceinline__ bool wait_cell(const uint2 *p, int e, unsigned polls, float &value) {
+    for (unsigned i = 0; i < polls; i++) {
+        const uint2 v = ld_cell(p);
+        if ((int)v.y == e) {
+            value = __uint_as_float(v.x);
+            return true;
+        }
+        if (i > 16) __nanosleep(100);
+    }
+    return false;
 }
 
 // grid n_heads * head_dim / 32, block 256 (as attn_decode_fold).
 __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams p) {
+    griddep_launch();
+    griddep_wait();
     __shared__ float s_max[8];
     __shared__ float s_num[8][32];
     __shared__ float s_den[8];
-    __shared__ int s_ok;
+    __shared__ float s_m[kMaxShards], s_l[kMaxShards];
+    __shared__ int s_bad;
     const int chunks = p.head_dim >> 5;
     const int h = blockIdx.x / chunks, chunk = blockIdx.x - h * chunks;
     const int dl = threadIdx.x & 31, sg = threadIdx.x >> 5;
@@ -68,6 +91,7 @@ __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams 
     // only after the last CTA has done so: all CTAs of a call see the same value.
     const int e = *reinterpret_cast<volatile int *>(hdr) + ((p.phases & 1) ? 1 : 0);
     const int parity = e & 1;
+    if (threadIdx.x == 0) s_bad = 0;
 
     if (p.phases & 1) {
         // ---- publish: fold the local partials of (h, chunk) ...
@@ -96,27 +120,20 @@ __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams 
                 n += s_num[i][dl];
                 d += s_den[i];
             }
-            // ... and store it into every rank's table
+            // ... and store it, tagged, into every rank's table
             for (int w = 0; w < p.shards; w++) {
-                float *dst = gather_slot(p.ws[w], parity, p.shards, p.n_heads, p.head_dim, p.rank, h);
-                dst[chunk * 32 + dl] = n;
+                uint2 *dst = cell_row(p.ws[w], parity, p.shards, p.n_heads, p.head_dim, p.rank, h);
+                st_cell(dst + chunk * 32 + dl, n, e);
                 if (chunk == 0 && dl == 0) {
-                    dst[p.head_dim] = big;
-                    dst[p.head_dim + 1] = d;
+                    st_cell(dst + p.head_dim, big, e);
+                    st_cell(dst + p.head_dim + 1, d, e);
                 }
             }
-            __syncwarp();
             if (dl == 0) {
-                __threadfence_system();
+                // epoch bookkeeping, off the critical path: the last CTA advances the epoch
                 const int done = atomicAdd(hdr + 1, 1);
                 if (done == (int)gridDim.x - 1) {
-                    // last CTA of this rank: everything of epoch e is on its way
-                    // one system-scope fence orders all of it before the flags; the flag stores
-                    // themselves are relaxed so that they leave back to back
-                    __threadfence_system();
                     hdr[1] = 0;
-                    for (int w = 0; w < p.shards; w++)
-                        st_relaxed_sys(reinterpret_cast<int *>(p.ws[w]) + 4 + p.rank, e);
                     *reinterpret_cast<volatile int *>(hdr) = e;
                 }
             }
@@ -124,41 +141,47 @@ __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams 
     }
 
     if (p.phases & 2) {
-        // ---- collect: wait for every rank's epoch e (bounded), then fold the shards
-        if (threadIdx.x == 0) s_ok = 1;
+        // ---- collect: warp sg takes shards sg, sg + 8; lane dl the cell of dim chunk*32 + dl
         __syncthreads();
-        if (threadIdx.x < p.shards) {
-            const int *flag = hdr + 4 + threadIdx.x;
-            bool ok = false;
-            for (unsigned i = 0; i < p.wait_polls; i++) {
-                if (ld_acquire_sys(flag) - e >= 0) {
-                    ok = true;
-                    break;
-                }
-                __nanosleep(100);
-            }
-            if (!ok) {
-                s_ok = 0;
-                atomicCAS(p.status, 0, 31);
+        float num[2] = {0.0f, 0.0f};
+        bool ok = true;
+        for (int k = 0; k < 2; k++) {
+            const int w = sg + 8 * k;
+            if (w >= p.shards) break;
+            const uint2 *src = cell_row(p.ws[p.rank], parity, p.shards, p.n_heads, p.head_dim, w, h);
+            ok = wait_cell(src + chunk * 32 + dl, e, p.wait_polls, num[k]) && ok;
+            if (dl < 2) {
+                float v = 0.0f;
+                ok = wait_cell(src + p.head_dim + dl, e, p.wait_polls, v) && ok;
+                (dl == 0 ? s_m : s_l)[w] = v;
             }
         }
+        if (!ok) s_bad = 1;
         __syncthreads();
-        if (s_ok && sg == 0) {
-            __threadfence_system();
+        if (s_bad) {
+            if (threadIdx.x == 0) atomicCAS(p.status, 0, 31);
+        } else {
             float big = -INFINITY;
-            for (int w = 0; w < p.shards; w++) {
-                const float *src = gather_slot(p.ws[p.rank], parity, p.shards, p.n_heads, p.head_dim, w, h);
-                big = fmaxf(big, __ldcg(src + p.head_dim));
+            for (int w = 0; w < p.shards; w++) big = fmaxf(big, s_m[w]);
+            float part = 0.0f;
+            for (int k = 0; k < 2; k++) {
+                const int w = sg + 8 * k;
+                if (w >= p.shards) break;
+                const float wt = (s_m[w] == -INFINITY) ? 0.0f : exp2f(s_m[w] - big);
+                part += num[k] * wt;
             }
-            float num = 0.0f, den = 0.0f;
-            for (int w = 0; w < p.shards; w++) {
-                const float *src = gather_slot(p.ws[p.rank], parity, p.shards, p.n_heads, p.head_dim, w, h);
-                const float m = __ldcg(src + p.head_dim);
-                const float wt = (m == -INFINITY) ? 0.0f : exp2f(m - big);
-                num += __ldcg(src + chunk * 32 + dl) * wt;
-                den += __ldcg(src + p.head_dim + 1) * wt;
+            s_num[sg][dl] = part;
+            __syncthreads();
+            if (sg == 0) {
+                float n = 0.0f, d = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) n += s_num[i][dl];
+                for (int w = 0; w < p.shards; w++) {
+                    const float wt = (s_m[w] == -INFINITY) ? 0.0f : exp2f(s_m[w] - big);
+                    d += s_l[w] * wt;
+                }
+                p.out[(size_t)h * p.head_dim + chunk * 32 + dl] = d > 0.0f ? n / d : 0.0f;
             }
-            p.out[(size_t)h * p.head_dim + chunk * 32 + dl] = den > 0.0f ? num / den : 0.0f;
         }
     }
 }
@@ -166,7 +189,7 @@ __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams 
 }  // namespace
 
 size_t decode_exchange_bytes(int n_heads, int head_dim, int shards) {
-    return (size_t)kHeaderBytes + 2 * (size_t)shards * n_heads * (head_dim + 2) * sizeof(float);
+    return (size_t)kHeaderBytes + 2 * (size_t)shards * n_heads * (head_dim + 2) * sizeof(uint2);
 }
 
 int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, const float *part_ml,
@@ -184,11 +207,10 @@ int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, cons
     p.shards = shards;
     p.rank = rank;
     p.phases = phases;
-    p.wait_polls = wait_limit_us < 1 ? 1u : wait_limit_us * 4u;   // ~0.25 us per poll (sleep + load)
+    p.wait_polls = wait_limit_us < 1 ? 16u : 16u + wait_limit_us * 4u;   // ~0.25 us per poll
     for (int w = 0; w < kMaxShards; w++)
         p.ws[w] = w < shards ? reinterpret_cast<unsigned char *>(peer_ws[w]) : nullptr;
-    attn_decode_fold_exchange<<<n_heads * (head_dim >> 5), 256, 0, stream>>>(p);
-    return launch_status();
+    return launch_pdl(attn_decode_fold_exchange, dim3(n_heads * (head_dim >> 5)), dim3(256), 0, stream, 1, p);
 }
 
 }  // namespace hipml

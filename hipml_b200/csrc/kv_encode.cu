@@ -79,6 +79,8 @@ extern "C" __global__ void kv_encode_q8(const float *__restrict__ k, const float
                                         unsigned char *__restrict__ kc,
                                         unsigned char *__restrict__ vc, int head_dim, int stride,
                                         const int *__restrict__ step) {
+    griddep_launch();
+    griddep_wait();
     __shared__ __align__(16) unsigned char krow[kMaxRowBytes];
     __shared__ __align__(16) unsigned char vrow[kMaxRowBytes];
     const int h = blockIdx.x;
@@ -95,6 +97,8 @@ extern "C" __global__ void kv_encode_bulk_q8(const float *__restrict__ k,
                                              unsigned char *__restrict__ vc, int n_kv,
                                              int head_dim, int stride, int start, int rows,
                                              int src0) {
+    griddep_launch();
+    griddep_wait();
     __shared__ __align__(16) unsigned char krow[kMaxRowBytes];
     __shared__ __align__(16) unsigned char vrow[kMaxRowBytes];
     const long long total = (long long)n_kv * rows;
@@ -145,6 +149,7 @@ __global__ void __launch_bounds__(256) kv_encode_bulk_q8_w(const float *__restri
                                                            int stride, int start, int rows,
                                                            int src0) {
     __shared__ __align__(16) unsigned char img[8][2][kMaxRowBytes];
+    griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long idx = (long long)blockIdx.x * 8 + warp;
     if (idx >= (long long)n_kv * rows) return;
@@ -158,6 +163,7 @@ __global__ void __launch_bounds__(256) kv_encode_bulk_q8_w(const float *__restri
     q8_put8(ka, kb, lane, img[warp][0]);
     q8_put8(va, vb, lane, img[warp][1]);
     __syncwarp();
+    griddep_wait();   // the loads above are of the caller's f32 rows; the cache is shared
     const size_t off = q8_row_offset(h, stride, start + r, 256);
     row_store(kc + off, img[warp][0], kMaxRowBytes, lane, 32);
     row_store(vc + off, img[warp][1], kMaxRowBytes, lane, 32);
@@ -167,9 +173,8 @@ int launch_kv_encode_bulk_rows(cudaStream_t stream, const float *k, const float 
                                unsigned char *kc, unsigned char *vc, int n_kv, int stride,
                                int start, int src0, int rows) {
     const long long pairs = (long long)n_kv * rows;
-    kv_encode_bulk_q8_w<<<(unsigned)((pairs + 7) / 8), 256, 0, stream>>>(k, v, kc, vc, n_kv, stride,
-                                                                         start, rows, src0);
-    return launch_status();
+    return launch_pdl(kv_encode_bulk_q8_w, dim3((unsigned)((pairs + 7) / 8)), dim3(256), 0, stream, 1, k, v,
+                      kc, vc, n_kv, stride, start, rows, src0);
 }
 
 // grid (n_kv, slots): slot s appends its row at pos[2*s] in the cache at s*slot_bytes.
@@ -178,6 +183,8 @@ extern "C" __global__ void kv_encode_q8_b(const float *__restrict__ k, const flo
                                           unsigned char *__restrict__ vc, int n_kv, int head_dim,
                                           int stride, const int *__restrict__ pos,
                                           int slot_bytes) {
+    griddep_launch();
+    griddep_wait();
     __shared__ __align__(16) unsigned char krow[kMaxRowBytes];
     __shared__ __align__(16) unsigned char vrow[kMaxRowBytes];
     const int h = blockIdx.x, slot = blockIdx.y;
@@ -191,6 +198,8 @@ extern "C" __global__ void kv_encode_q8_b(const float *__restrict__ k, const flo
 extern "C" __global__ void kv_append_f32(float *__restrict__ k_cache, float *__restrict__ v_cache,
                                          const float *__restrict__ k, const float *__restrict__ v,
                                          const int *__restrict__ step, int width) {
+    griddep_launch();
+    griddep_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= 2 * width) return;
     const size_t base = (size_t)step[0] * (size_t)width;
@@ -207,6 +216,8 @@ extern "C" __global__ void kv_append_chunk_f32(float *__restrict__ k_cache,
                                                const float *__restrict__ k,
                                                const float *__restrict__ v, int pos0, int width,
                                                int tokens) {
+    griddep_launch();
+    griddep_wait();
     const size_t n = (size_t)tokens * (size_t)width;
     const size_t base = (size_t)pos0 * (size_t)width;
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;

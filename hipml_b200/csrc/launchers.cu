@@ -47,8 +47,8 @@ int hipml_kv_encode(hipml_stream_t stream, const int *step, int dtype, const flo
                     int stride) {
     if (int e = check_encode(dtype, n_kv, head_dim, stride)) return e;
     void *args[] = {&k_row, &v_row, &k_cache, &v_cache, &head_dim, &stride, &step};
-    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_encode_q8"), dim3(n_kv), dim3(head_dim),
-                                 args, 0, as_stream(stream));
+    return launch_pdl_args(lookup_kv_kernel("kv_encode_q8"), dim3(n_kv), dim3(head_dim), args, 0,
+                           as_stream(stream));
 }
 
 int hipml_kv_encode_bulk(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
@@ -68,8 +68,8 @@ int hipml_kv_encode_bulk(hipml_stream_t stream, int dtype, const float *k_f32, c
     const unsigned grid = (unsigned)(pairs < 148LL * 64 ? pairs : 148LL * 64);
     void *args[] = {&k_f32, &v_f32, &k_cache, &v_cache, &n_kv, &head_dim, &stride, &start, &rows,
                     &src0};
-    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_encode_bulk_q8"), dim3(grid), dim3(head_dim),
-                                 args, 0, as_stream(stream));
+    return launch_pdl_args(lookup_kv_kernel("kv_encode_bulk_q8"), dim3(grid), dim3(head_dim), args, 0,
+                           as_stream(stream));
 }
 
 int hipml_kv_encode_rows(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
@@ -79,8 +79,8 @@ int hipml_kv_encode_rows(hipml_stream_t stream, int dtype, const float *k_f32, c
     if (slots <= 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "slots %d must be positive", slots);
     void *args[] = {&k_f32, &v_f32, &k_cache, &v_cache, &n_kv, &head_dim, &stride, &pos,
                     &slot_bytes};
-    return (int)cudaLaunchKernel(lookup_kv_kernel("kv_encode_q8_b"), dim3(n_kv, slots),
-                                 dim3(head_dim), args, 0, as_stream(stream));
+    return launch_pdl_args(lookup_kv_kernel("kv_encode_q8_b"), dim3(n_kv, slots), dim3(head_dim), args,
+                           0, as_stream(stream));
 }
 
 int hipml_kv_append_f32(hipml_stream_t stream, const int *step, float *k_cache, float *v_cache,

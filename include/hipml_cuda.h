@@ -215,8 +215,9 @@ int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, floa
  * peer_ws is a HOST array of `shards` device pointers, peer_ws[w] = rank w's workspace as
  * mapped in this process, peer_ws[rank] = the local one. One call = split pass over the local
  * rows, then one kernel that folds the local partials, stores the folded triple into every
- * rank's workspace, raises this rank's flag there, waits until every rank's flag of the same
- * call has arrived and folds the shards into out f32 [n_heads][head_dim]. All ranks must make
+ * rank's workspace (each value tagged with the call's number in the same 8-byte store), waits
+ * until every rank's values of the same call have arrived and folds the shards into out f32
+ * [n_heads][head_dim]. All ranks must make
  * the same sequence of calls. phases: 3 = all of it; 1 = split pass + publish only and 2 =
  * wait + final fold only (the two halves, for hosts that drive several ranks from one stream).
  * The wait is bounded by wait_limit_us (capped at 10 s): when it runs out the kernel leaves
