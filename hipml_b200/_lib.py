@@ -68,9 +68,18 @@ SIGNATURES = {
     "hipml_kv_append_chunk_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "hipml_attn_decode_kv": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f,
                                   _i, _sz, _sz]),
+    "hipml_attn_decode_kv_gated": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                                        _f, _i, _sz, _sz]),
     "hipml_attn_decode_kv_shard": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _f, _i, _sz, _sz]),
     "hipml_attn_decode_combine": (_i, [_vp, _vp, _vp, _i, _i, _i]),
+    "hipml_attn_front": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, C.POINTER(_i), _vp,
+                              _f, _f]),
+    "hipml_qg_split_chunk": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "hipml_norm_rope_chunk": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i]),
+    "hipml_q_gate": (_i, [_vp, _vp, _vp, _vp, C.c_longlong]),
+    "hipml_attn_front_append_q8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
+                                        _i, _i, C.POINTER(_i), _vp, _vp, _i, _i, _i, _f, _f]),
     "hipml_decode_exchange_bytes": (_sz, [_i, _i, _i]),
     "hipml_attn_decode_kv_shard_exchange": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                                                  _i, _i, _f, _i, _sz, _sz, C.POINTER(_vp), _i, _i,
@@ -89,6 +98,8 @@ SIGNATURES = {
     "hipml_attn_chunk_stage": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz]),
     "hipml_attn_chunk_staged": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp,
                                      _sz]),
+    "hipml_attn_chunk_staged_gated": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i,
+                                           _i, _vp, _sz]),
     "hipml_check_device_status": (_i, [_vp, C.POINTER(_i)]),
     "hipml_version": (C.c_char_p, []),
 }

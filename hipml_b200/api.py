@@ -66,6 +66,14 @@ def attn_decode_kv(step, q, k, v, part_acc, part_ml, out, n_heads, n_kv, head_di
         n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
 
 
+def attn_decode_kv_gated(step, q, k, v, part_acc, part_ml, out, gate, n_heads, n_kv, head_dim,
+                         stride, scale, splits, selector=0, k_off=0, v_off=0):
+    """attn_decode_kv with out *= sigmoid(gate) applied in the fold."""
+    _lib.check("attn_decode_kv_gated", _lib.load().hipml_attn_decode_kv_gated(
+        _stream(), _p(step), selector, _p(q), _p(k), _p(v), _p(part_acc), _p(part_ml), _p(out),
+        _p(gate), n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
+
+
 def attn_decode_kv_shard(step, q, k, v, part_acc, part_ml, shard_out, n_heads, n_kv, head_dim,
                          stride, scale, splits, selector=0, k_off=0, v_off=0):
     """One GPU's part of a sequence-split decode: writes [n_heads][head_dim+2] =
@@ -173,6 +181,55 @@ def attn_chunk_staged(q, out, n_heads, n_kv, head_dim, pos0, tokens, key_capacit
     """Chunk attention over rows already staged by attn_chunk_stage."""
     _lib.check("chunk_attention", _lib.load().hipml_attn_chunk_staged(
         _stream(), _p(q), _p(out), n_heads, n_kv, head_dim, pos0, tokens, _p(part_acc),
+        _p(part_ml), splits, mode, key_capacity, _p(workspace),
+        workspace.numel() * workspace.element_size()))
+
+
+# ---- attention front end and tail -----------------------------------------------------------
+
+def _sections(sections):
+    return None if sections is None else (C.c_int * 4)(*[int(v) for v in sections])
+
+
+def attn_front(qg, q, gate, k, q_norm, k_norm, n_heads, n_kv, head_dim, n_rot, sections, pos,
+               theta_base, eps):
+    """AttnLayer::front: one token, q|gate split + head RMS norm + M-RoPE (k in place)."""
+    _lib.check("attn_front", _lib.load().hipml_attn_front(
+        _stream(), _p(qg), _p(q), _p(gate), _p(k), _p(q_norm), _p(k_norm), n_heads, n_kv, head_dim,
+        n_rot, _sections(sections), _p(pos), theta_base, eps))
+
+
+def qg_split_chunk(qg, q, gate, n_heads, head_dim, tokens):
+    _lib.check("qg_split_chunk", _lib.load().hipml_qg_split_chunk(
+        _stream(), _p(qg), _p(q), _p(gate), n_heads, head_dim, tokens))
+
+
+def norm_rope_chunk(q, k, q_norm, k_norm, n_heads, n_kv, head_dim, n_rot, theta_base, eps, pos0,
+                    tokens):
+    _lib.check("norm_rope_chunk", _lib.load().hipml_norm_rope_chunk(
+        _stream(), _p(q), _p(k), _p(q_norm), _p(k_norm), n_heads, n_kv, head_dim, n_rot, theta_base,
+        eps, pos0, tokens))
+
+
+def q_gate(q, gate, y, n):
+    _lib.check("q_gate", _lib.load().hipml_q_gate(_stream(), _p(q), _p(gate), _p(y), n))
+
+
+def attn_front_append_q8(qg, k, v, q, gate, q_norm, k_norm, k_cache, v_cache, n_heads, n_kv,
+                         head_dim, n_rot, theta_base, eps, pos0=0, tokens=1, stride=0, sections=None,
+                         pos=None, step=None, k_out=None):
+    """Split + norm + rope + q8_0 append of `tokens` rows in one launch."""
+    _lib.check("attn_front_append_q8", _lib.load().hipml_attn_front_append_q8(
+        _stream(), _p(qg), _p(k), _p(v), _p(q), _p(gate), _p(k_out), _p(q_norm), _p(k_norm),
+        _p(k_cache), _p(v_cache), n_heads, n_kv, head_dim, n_rot, _sections(sections), _p(pos),
+        _p(step), pos0, tokens, stride, theta_base, eps))
+
+
+def attn_chunk_staged_gated(q, out, gate, n_heads, n_kv, head_dim, pos0, tokens, key_capacity,
+                            workspace, part_acc=None, part_ml=None, splits=1, mode=0):
+    """attn_chunk_staged with out *= sigmoid(gate) applied in the epilogue / combine."""
+    _lib.check("chunk_attention", _lib.load().hipml_attn_chunk_staged_gated(
+        _stream(), _p(q), _p(out), _p(gate), n_heads, n_kv, head_dim, pos0, tokens, _p(part_acc),
         _p(part_ml), splits, mode, key_capacity, _p(workspace),
         workspace.numel() * workspace.element_size()))
 

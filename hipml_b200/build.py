@@ -19,6 +19,7 @@ SOURCES = [
     "attn_decode_f32.cu",
     "decode_static.cu",
     "decode_exchange.cu",
+    "attn_front.cu",
     "attn_chunk_scalar.cu",
     "attn_chunk_tc.cu",
     "launchers.cu",

@@ -160,7 +160,8 @@ int launch_chunk_scalar(cudaStream_t stream, const ChunkScalarParams &p) {
 __global__ void __launch_bounds__(256) attn_chunk_combine_256(const float *__restrict__ part_acc,
                                                               const float *__restrict__ part_ml,
                                                               float *__restrict__ out, int n_heads,
-                                                              int tokens, int qslots, int splits) {
+                                                              int tokens, int qslots, int splits,
+                                                              const float *__restrict__ gate) {
     griddep_launch();
     griddep_wait();
     const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 6);
@@ -185,21 +186,29 @@ __global__ void __launch_bounds__(256) attn_chunk_combine_256(const float *__res
         den += ml.y * w;
     }
     const bool ok = den > 0.0f;
-    const float4 o = make_float4(ok ? num.x / den : 0.0f, ok ? num.y / den : 0.0f,
-                                 ok ? num.z / den : 0.0f, ok ? num.w / den : 0.0f);
+    float4 o = make_float4(ok ? num.x / den : 0.0f, ok ? num.y / den : 0.0f,
+                           ok ? num.z / den : 0.0f, ok ? num.w / den : 0.0f);
+    if (gate) {
+        const float4 g = reinterpret_cast<const float4 *>(gate + ((size_t)t * n_heads + h) * 256)[d4];
+        o.x *= 1.0f / (1.0f + expf(-g.x));
+        o.y *= 1.0f / (1.0f + expf(-g.y));
+        o.z *= 1.0f / (1.0f + expf(-g.z));
+        o.w *= 1.0f / (1.0f + expf(-g.w));
+    }
     reinterpret_cast<float4 *>(out + ((size_t)t * n_heads + h) * 256)[d4] = o;
 }
 
 int launch_chunk_combine(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int tokens, int qslots,
-                         int splits) {
+                         int splits, const float *gate) {
     if (head_dim == 256 &&
         ((reinterpret_cast<size_t>(part_acc) | reinterpret_cast<size_t>(out)) & 15) == 0 &&
         (reinterpret_cast<size_t>(part_ml) & 7) == 0) {
         const long long pairs = (long long)tokens * n_heads;
         return launch_pdl(attn_chunk_combine_256, dim3((unsigned)((pairs + 3) / 4)), dim3(256), 0, stream, 1,
-                          part_acc, part_ml, out, n_heads, tokens, qslots, splits);
+                          part_acc, part_ml, out, n_heads, tokens, qslots, splits, gate);
     }
+    if (gate) return fail(HIPML_ERR_INVALID_ARGUMENT, "gated combine: head_dim 256, 16-byte aligned rows");
     dim3 grid(qslots, n_heads);
     return launch_pdl(attn_chunk_combine_f32, grid, dim3(head_dim), 0, stream, 1, part_acc, part_ml, out,
                       n_heads, head_dim, tokens, qslots, splits);

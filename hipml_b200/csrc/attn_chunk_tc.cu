@@ -70,6 +70,7 @@ struct ChunkTcParams {
     float scale_log2;
     int splits, qslots;
     int single_pass;   // 1: hi*hi only
+    const float *gate; // optional [tokens][n_heads*256]: out *= sigmoid(gate) (one-pass form only)
 };
 
 namespace {
@@ -837,6 +838,8 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             const size_t slot = ((size_t)sp * p.qslots + (t0 + rq)) * p.n_heads + h;
             float *dst = (norm ? p.out + ((size_t)(t0 + rq) * p.n_heads + h) * kD : p.part_acc + slot * kD) +
                          128 * half;
+            const float *gsrc =
+                (norm && p.gate) ? p.gate + ((size_t)(t0 + rq) * p.n_heads + h) * kD + 128 * half : nullptr;
 #pragma unroll 1
             for (int j = 0; j < 4; j++) {
                 if (n_tiles > 0) tmem_ld32(tmem_o + lane_addr + 128 * half + 32 * j, v);
@@ -848,6 +851,13 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                         w.y = n_tiles > 0 ? __uint_as_float(v[e + 1]) * inv : 0.0f;
                         w.z = n_tiles > 0 ? __uint_as_float(v[e + 2]) * inv : 0.0f;
                         w.w = n_tiles > 0 ? __uint_as_float(v[e + 3]) * inv : 0.0f;
+                        if (gsrc) {   // the layer's output gate, applied where the row is produced
+                            const float4 g = *reinterpret_cast<const float4 *>(gsrc + 32 * j + e);
+                            w.x *= 1.0f / (1.0f + expf(-g.x));
+                            w.y *= 1.0f / (1.0f + expf(-g.y));
+                            w.z *= 1.0f / (1.0f + expf(-g.z));
+                            w.w *= 1.0f / (1.0f + expf(-g.w));
+                        }
                         *reinterpret_cast<float4 *>(dst + 32 * j + e) = w;
                     }
                 }
@@ -941,7 +951,7 @@ int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_c
 // CTA pairs. Shapes are validated by the caller.
 int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part_acc,
                     float *part_ml, int n_heads, int n_kv, int pos0, int tokens, int cap,
-                    int splits, int variant, void *workspace, int *status) {
+                    int splits, int variant, void *workspace, int *status, const float *gate) {
     const size_t plane = (size_t)n_kv * cap * kD;
     __half *ws = reinterpret_cast<__half *>(workspace);
     const bool pair = (variant & 2) == 0;
@@ -984,6 +994,7 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part
     p.splits = splits;
     p.qslots = (tokens + 31) / 32 * 32;
     p.single_pass = single_pass;
+    p.gate = gate;
     const int nsp = splits < 2 ? 1 : splits;
     const int qtiles = (tokens + p.qtile - 1) / p.qtile;
     if (!pair) {

@@ -157,7 +157,14 @@ __global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
         }
         float *o = p.out + (size_t)slot * p.out_slot + (size_t)h * p.out_head_stride;
         if (p.normalize) {
-            o[chunk * 32 + dl] = d > 0.0f ? n / d : 0.0f;
+            float r = d > 0.0f ? n / d : 0.0f;
+            if (p.gate) {
+                // the output gate of the layer, applied where the row is produced
+                const float g = p.gate[(size_t)slot * p.out_slot + (size_t)h * p.out_head_stride +
+                                       chunk * 32 + dl];
+                r *= 1.0f / (1.0f + expf(-g));
+            }
+            o[chunk * 32 + dl] = r;
         } else {
             // the folded triple of this shard: acc (unnormalised), then max (log2 units), sum
             o[chunk * 32 + dl] = n;
@@ -235,7 +242,8 @@ int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, in
 // The usual case: partials [n_heads][splits][head_dim] / [n_heads][splits][2] -> out[slot][h][d].
 int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int splits, int slots,
-                         long long acc_slot, long long ml_slot, long long out_slot) {
+                         long long acc_slot, long long ml_slot, long long out_slot,
+                         const float *gate) {
     FoldParams p;
     p.acc = part_acc;
     p.ml = part_ml;
@@ -251,6 +259,7 @@ int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float
     p.out_slot = out_slot;
     p.out_head_stride = head_dim;
     p.normalize = 1;
+    p.gate = gate;
     return launch_decode_fold(stream, p, n_heads, slots);
 }
 

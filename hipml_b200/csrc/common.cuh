@@ -94,6 +94,7 @@ const void *lookup_kv_kernel(const char *name);
 const void *lookup_decode_kernel(const char *name);
 const void *lookup_chunk_kernel(const char *name);
 const void *lookup_cols_kernel(const char *name);
+const void *lookup_front_kernel(const char *name);
 
 // Device status word set by kernels whose bounded waits ran out.
 int *device_status_word();

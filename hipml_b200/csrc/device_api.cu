@@ -204,6 +204,7 @@ int hipml_module_get_function(hipml_function_t *function, hipml_module_t module,
     if (!fn) fn = lookup_decode_kernel(name);
     if (!fn) fn = lookup_chunk_kernel(name);
     if (!fn) fn = lookup_cols_kernel(name);
+    if (!fn) fn = lookup_front_kernel(name);
     if (fn) {
         *function = const_cast<void *>(fn);
         return HIPML_SUCCESS;

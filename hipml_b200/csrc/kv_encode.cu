@@ -14,12 +14,12 @@
 // streams each finished 272-byte row to the cache with 16-byte stores, so the
 // cache sees whole-sector writes instead of one byte per lane.
 #include "common.cuh"
+#include "q8_pack.cuh"
 
 namespace hipml {
 
 namespace {
 
-constexpr int kMaxRowBytes = 8 * kQ8BlockBytes;  // head_dim 256
 
 // Quantise x (this lane's value of block `blk`) into row image `row`.
 __device__ __forceinline__ void q8_put(float x, int blk, int lane, unsigned char *row) {
@@ -33,24 +33,6 @@ __device__ __forceinline__ void q8_put(float x, int blk, int lane, unsigned char
     unsigned char *b = row + blk * kQ8BlockBytes;
     if (lane == 0) *reinterpret_cast<unsigned short *>(b) = __half_as_ushort(__float2half_rn(d));
     b[2 + lane] = (unsigned char)(signed char)q;
-}
-
-// Copy a finished row image to global memory with the widest store its
-// address and length allow (16 B for head_dim 256, whose rows are 272 B).
-__device__ __forceinline__ void row_store(unsigned char *dst, const unsigned char *row,
-                                          int row_bytes, int tid, int nthreads) {
-    const size_t a = reinterpret_cast<size_t>(dst) | (size_t)row_bytes;
-    if ((a & 15) == 0) {
-        for (int i = tid; i < row_bytes / 16; i += nthreads)
-            reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(row)[i];
-    } else if ((a & 3) == 0) {
-        for (int i = tid; i < row_bytes / 4; i += nthreads)
-            reinterpret_cast<uint32_t *>(dst)[i] = reinterpret_cast<const uint32_t *>(row)[i];
-    } else {
-        for (int i = tid; i < row_bytes / 2; i += nthreads)
-            reinterpret_cast<unsigned short *>(dst)[i] =
-                reinterpret_cast<const unsigned short *>(row)[i];
-    }
 }
 
 // One (K row, V row) pair of one KV head. All threads of the CTA must call it.
@@ -109,30 +91,6 @@ extern "C" __global__ void kv_encode_bulk_q8(const float *__restrict__ k,
         const size_t off = q8_row_offset(h, stride, start + r, head_dim);
         encode_pair(k + src, v + src, kc + off, vc + off, head_dim, krow, vrow);
     }
-}
-
-// Eight values of one 32-value block held by one lane (lanes 4b..4b+3 share block b).
-__device__ __forceinline__ void q8_put8(const float4 a, const float4 b, int lane,
-                                        unsigned char *row) {
-    const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(x[j]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const float d = amax / 127.0f;
-    const float id = d > 0.0f ? 1.0f / d : 0.0f;
-    unsigned q[8];
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const float r = roundf(x[j] * id);
-        q[j] = (unsigned)((r != r) ? 0 : (int)fmaxf(-127.0f, fminf(127.0f, r))) & 0xffu;
-    }
-    unsigned char *blk = row + (lane >> 2) * kQ8BlockBytes;
-    if ((lane & 3) == 0) *reinterpret_cast<unsigned short *>(blk) = __half_as_ushort(__float2half_rn(d));
-    unsigned short *dst = reinterpret_cast<unsigned short *>(blk + 2 + (lane & 3) * 8);
-#pragma unroll
-    for (int j = 0; j < 4; j++) dst[j] = (unsigned short)(q[2 * j] | (q[2 * j + 1] << 8));
 }
 
 // The throughput form of the bulk append for head_dim 256 and 16-byte-aligned sources

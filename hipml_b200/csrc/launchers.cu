@@ -115,7 +115,8 @@ struct ExchangeArgs {
 static int decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
                      const void *k, const void *v, float *part_acc, float *part_ml, float *out,
                      int n_heads, int n_kv, int head_dim, int stride, float scale, int splits,
-                     size_t k_off, size_t v_off, bool shard, const ExchangeArgs *xch = nullptr) {
+                     size_t k_off, size_t v_off, bool shard, const ExchangeArgs *xch = nullptr,
+                     const float *gate = nullptr) {
     if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
     // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
     // experimental variants have no counterpart here.
@@ -180,7 +181,7 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     }
     if (!shard)
         return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
-                                    splits, 1, 0, 0, 0);
+                                    splits, 1, 0, 0, 0, gate);
     FoldParams f;
     f.acc = part_acc;
     f.ml = part_ml;
@@ -194,6 +195,7 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     f.acc_slot = f.ml_slot = f.out_slot = 0;
     f.out_head_stride = head_dim + 2;
     f.normalize = 0;
+    f.gate = nullptr;
     return launch_decode_fold(as_stream(stream), f, n_heads, 1);
 }
 
@@ -203,6 +205,15 @@ int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, c
                          int splits, size_t k_off, size_t v_off) {
     return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
                      head_dim, stride, scale, splits, k_off, v_off, false);
+}
+
+int hipml_attn_decode_kv_gated(hipml_stream_t stream, const int *step, int selector, const float *q,
+                               const void *k, const void *v, float *part_acc, float *part_ml,
+                               float *out, const float *gate, int n_heads, int n_kv, int head_dim,
+                               int stride, float scale, int splits, size_t k_off, size_t v_off) {
+    if (!gate) return fail(HIPML_ERR_INVALID_ARGUMENT, "gated decode: no gate row");
+    return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
+                     head_dim, stride, scale, splits, k_off, v_off, false, nullptr, gate);
 }
 
 int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selector,
@@ -268,6 +279,7 @@ int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, floa
     f.acc_slot = f.ml_slot = f.out_slot = 0;
     f.out_head_stride = head_dim;
     f.normalize = 1;
+    f.gate = nullptr;
     return launch_decode_fold(as_stream(stream), f, n_heads, 1);
 }
 
@@ -445,10 +457,10 @@ int hipml_attn_chunk_stage(hipml_stream_t stream, const void *k_cache, const voi
                               key_to, key_capacity, workspace);
 }
 
-int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, int n_heads,
-                            int n_kv, int head_dim, int pos0, int tokens, float *part_acc,
-                            float *part_ml, int splits, int mode, int key_capacity,
-                            void *workspace, size_t workspace_bytes) {
+static int chunk_staged(hipml_stream_t stream, const float *q, float *out, int n_heads, int n_kv,
+                        int head_dim, int pos0, int tokens, float *part_acc, float *part_ml,
+                        int splits, int mode, int key_capacity, void *workspace,
+                        size_t workspace_bytes, const float *gate) {
     if (n_kv <= 0 || n_heads % n_kv != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "n_heads %d is not a multiple of n_kv %d", n_heads,
                     n_kv);
@@ -475,12 +487,30 @@ int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, i
     if (!status) return launch_status();
     if (int e = launch_chunk_tc(as_stream(stream), q, out, part_acc, part_ml, n_heads, n_kv, pos0,
                                 tokens, key_capacity, splits, mode == 1 ? 1 : (mode == 3 ? 2 : 0), workspace,
-                                status))
+                                status, splits >= 2 ? nullptr : gate))
         return e;
     if (splits >= 2)
         return launch_chunk_combine(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
-                                    tokens, (tokens + 31) / 32 * 32, splits);
+                                    tokens, (tokens + 31) / 32 * 32, splits, gate);
     return 0;
+}
+
+int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, int n_heads,
+                            int n_kv, int head_dim, int pos0, int tokens, float *part_acc,
+                            float *part_ml, int splits, int mode, int key_capacity,
+                            void *workspace, size_t workspace_bytes) {
+    return chunk_staged(stream, q, out, n_heads, n_kv, head_dim, pos0, tokens, part_acc, part_ml,
+                        splits, mode, key_capacity, workspace, workspace_bytes, nullptr);
+}
+
+int hipml_attn_chunk_staged_gated(hipml_stream_t stream, const float *q, float *out,
+                                  const float *gate, int n_heads, int n_kv, int head_dim, int pos0,
+                                  int tokens, float *part_acc, float *part_ml, int splits, int mode,
+                                  int key_capacity, void *workspace, size_t workspace_bytes) {
+    if (!gate || (reinterpret_cast<size_t>(gate) & 15) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "gated chunk attention: gate rows missing or unaligned");
+    return chunk_staged(stream, q, out, n_heads, n_kv, head_dim, pos0, tokens, part_acc, part_ml,
+                        splits, mode, key_capacity, workspace, workspace_bytes, gate);
 }
 
 int hipml_kv_append_cols_f32(hipml_stream_t stream, float *k_cache, float *v_cache,
@@ -493,6 +523,88 @@ int hipml_kv_append_cols_f32(hipml_stream_t stream, float *k_cache, float *v_cac
     return (int)cudaLaunchKernel(lookup_cols_kernel("kv_append_cols_f32"),
                                  dim3((unsigned)((n + 255) / 256)), dim3(256), args, 0,
                                  as_stream(stream));
+}
+
+// ---- attention front end and tail --------------------------------------------------------
+
+static int check_front(int n_heads, int n_kv, int head_dim, int n_rot) {
+    if (n_heads <= 0 || n_kv <= 0 || head_dim <= 0 || head_dim > 256)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "front end: n_heads %d / n_kv %d / head_dim %d (<= 256)",
+                    n_heads, n_kv, head_dim);
+    if (n_rot < 0 || n_rot > head_dim || n_rot % 2 != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "n_rot must be even and <= head_dim");
+    return 0;
+}
+
+int hipml_attn_front(hipml_stream_t stream, const float *qg, float *q, float *gate, float *k,
+                     const float *q_norm, const float *k_norm, int n_heads, int n_kv, int head_dim,
+                     int n_rot, const int *sections, const int *pos, float theta_base, float eps) {
+    if (int e = check_front(n_heads, n_kv, head_dim, n_rot)) return e;
+    int s0 = sections ? sections[0] : 0, s1 = sections ? sections[1] : 0;
+    int s2 = sections ? sections[2] : 0, s3 = sections ? sections[3] : 0;
+    void *args[] = {&qg, &q, &gate, &k, &q_norm, &k_norm, &n_heads, &n_kv, &head_dim, &n_rot,
+                    &s0, &s1, &s2, &s3, &pos, &theta_base, &eps};
+    return launch_pdl_args(lookup_front_kernel("attn_front_f32"), dim3(n_heads + n_kv), dim3(256), args,
+                           0, as_stream(stream));
+}
+
+int hipml_qg_split_chunk(hipml_stream_t stream, const float *qg, float *q, float *gate, int n_heads,
+                         int head_dim, int tokens) {
+    if (n_heads <= 0 || head_dim <= 0 || head_dim > 1024 || tokens < 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "qg_split: n_heads %d / head_dim %d / tokens %d",
+                    n_heads, head_dim, tokens);
+    if (tokens == 0) return 0;
+    void *args[] = {&qg, &q, &gate, &n_heads, &head_dim, &tokens};
+    return launch_pdl_args(lookup_front_kernel("qg_split_chunk_f32"), dim3(n_heads, tokens),
+                           dim3(head_dim), args, 0, as_stream(stream));
+}
+
+int hipml_norm_rope_chunk(hipml_stream_t stream, float *q, float *k, const float *q_norm,
+                          const float *k_norm, int n_heads, int n_kv, int head_dim, int n_rot,
+                          float theta_base, float eps, int pos0, int tokens) {
+    if (int e = check_front(n_heads, n_kv, head_dim, n_rot)) return e;
+    if (head_dim % 32 != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "head_dim %d: must be a multiple of 32", head_dim);
+    if (tokens < 0 || pos0 < 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "pos0 %d / tokens %d", pos0, tokens);
+    if (tokens == 0) return 0;
+    void *args[] = {&q, &k, &q_norm, &k_norm, &n_heads, &n_kv, &head_dim, &n_rot, &theta_base, &eps,
+                    &pos0, &tokens};
+    return launch_pdl_args(lookup_front_kernel("norm_rope_chunk_f32"), dim3(n_heads + n_kv, tokens),
+                           dim3(head_dim), args, 0, as_stream(stream));
+}
+
+int hipml_q_gate(hipml_stream_t stream, const float *q, const float *gate, float *y, long long n) {
+    if (n < 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "q_gate: n %lld", n);
+    return launch_q_gate(as_stream(stream), q, gate, y, n);
+}
+
+int hipml_attn_front_append_q8(hipml_stream_t stream, const float *qg, const float *k,
+                               const float *v, float *q, float *gate, float *k_out,
+                               const float *q_norm, const float *k_norm, void *k_cache,
+                               void *v_cache, int n_heads, int n_kv, int head_dim, int n_rot,
+                               const int *sections, const int *pos, const int *step, int pos0,
+                               int tokens, int stride, float theta_base, float eps) {
+    if (int e = check_front(n_heads, n_kv, head_dim, n_rot)) return e;
+    if (head_dim != 256 || n_rot % 16 != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT,
+                    "fused front end: head_dim 256 and n_rot a multiple of 16 (got %d, %d)", head_dim,
+                    n_rot);
+    if (tokens < 0 || pos0 < 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "pos0 %d / tokens %d", pos0, tokens);
+    if ((pos || step) && tokens != 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "device positions describe one token, got %d", tokens);
+    if ((k_cache == nullptr) != (v_cache == nullptr))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "give both caches or neither");
+    if (k_cache && (stride <= 0 || (!step && pos0 + tokens > stride)))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "position %d beyond KV cache %d", pos0 + tokens, stride);
+    const size_t align = reinterpret_cast<size_t>(qg) | reinterpret_cast<size_t>(k) |
+                         reinterpret_cast<size_t>(v) | reinterpret_cast<size_t>(q) |
+                         reinterpret_cast<size_t>(gate) | reinterpret_cast<size_t>(k_out) |
+                         reinterpret_cast<size_t>(q_norm) | reinterpret_cast<size_t>(k_norm);
+    if (align & 15) return fail(HIPML_ERR_INVALID_ARGUMENT, "fused front end: 16-byte aligned rows");
+    if (tokens == 0) return 0;
+    return launch_front_rows_q8(as_stream(stream), qg, k, v, q, gate, k_out, q_norm, k_norm, k_cache,
+                                v_cache, n_heads, n_kv, n_rot, sections, pos, step, pos0, tokens,
+                                stride, theta_base, eps);
 }
 
 int hipml_attn_decode_cols_f32(hipml_stream_t stream, const float *q, const float *k_cache,

@@ -35,12 +35,14 @@ struct FoldParams {
     long long acc_head_stride, acc_split_stride, ml_head_stride, ml_split_stride;
     long long acc_slot, ml_slot, out_slot, out_head_stride;
     int normalize;     // 1: out = acc/sum; 0: out row = [acc (unnormalised) | max | sum]
+    const float *gate; // optional, normalize only: out *= sigmoid(gate), laid out as out
 };
 int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots);
 // Folds the partials into out[slot][h][d] (slot strides in floats).
 int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int splits, int slots,
-                         long long acc_slot, long long ml_slot, long long out_slot);
+                         long long acc_slot, long long ml_slot, long long out_slot,
+                         const float *gate = nullptr);
 
 // Scalar chunk attention (attn_chunk_scalar.cu).
 struct ChunkScalarParams {
@@ -59,7 +61,8 @@ struct ChunkScalarParams {
 };
 int launch_chunk_scalar(cudaStream_t stream, const ChunkScalarParams &p);
 int launch_chunk_combine(cudaStream_t stream, const float *part_acc, const float *part_ml,
-                         float *out, int n_heads, int head_dim, int tokens, int qslots, int splits);
+                         float *out, int n_heads, int head_dim, int tokens, int qslots, int splits,
+                         const float *gate = nullptr);
 
 // Throughput form of the q8_0 bulk append, head_dim 256 and 16-byte-aligned sources (kv_encode.cu).
 int launch_kv_encode_bulk_rows(cudaStream_t stream, const float *k, const float *v,
@@ -73,7 +76,8 @@ int launch_chunk_stage(cudaStream_t stream, const void *k_cache, const void *v_c
                        void *workspace);
 int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part_acc,
                     float *part_ml, int n_heads, int n_kv, int pos0, int tokens, int cap,
-                    int splits, int variant, void *workspace, int *status);
+                    int splits, int variant, void *workspace, int *status,
+                    const float *gate = nullptr);
 
 // Fold + peer-memory exchange + final fold of a sequence-split decode (decode_exchange.cu).
 size_t decode_exchange_bytes(int n_heads, int head_dim, int shards);
@@ -81,6 +85,14 @@ int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, cons
                                 float *out, int n_heads, int head_dim, int splits,
                                 void *const *peer_ws, int shards, int rank, int phases,
                                 unsigned wait_limit_us, int *status);
+
+// Attention front end and tail (attn_front.cu).
+int launch_q_gate(cudaStream_t stream, const float *q, const float *gate, float *y, long long n);
+int launch_front_rows_q8(cudaStream_t stream, const float *qg, const float *k, const float *v,
+                         float *q, float *gate, float *k_out, const float *q_norm,
+                         const float *k_norm, void *k_cache, void *v_cache, int n_heads, int n_kv,
+                         int n_rot, const int *sections, const int *pos4, const int *step, int pos0,
+                         int tokens, int stride, float theta_base, float eps);
 
 // f32-cache decode for `rows` consecutive columns (attn_decode_f32.cu): split pass + fold.
 int launch_decode_cols_f32(cudaStream_t stream, const float *q, const float *k, const float *v,

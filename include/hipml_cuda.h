@@ -191,6 +191,54 @@ int hipml_attn_decode_cols_f32(hipml_stream_t stream, const float *q, const floa
 int hipml_kv_append_cols_f32(hipml_stream_t stream, float *k_cache, float *v_cache,
                              const float *k, const float *v, int pos0, int rows, int width);
 
+/* hipml_attn_decode_kv with the layer's output gate applied where the output row is produced:
+ * out = attention * sigmoid(gate), gate f32 [n_heads][head_dim] (no counterpart as one call in
+ * the reference, which launches q_gate_f32 after the reduce, attn_gpu.rs:798-830). */
+int hipml_attn_decode_kv_gated(hipml_stream_t stream, const int *step, int selector, const float *q,
+                               const void *k, const void *v, float *part_acc, float *part_ml,
+                               float *out, const float *gate, int n_heads, int n_kv, int head_dim,
+                               int stride, float scale, int splits, size_t k_off, size_t v_off);
+
+/* ---- Attention front end and tail (the callers either side of the attention kernels) ----
+ * CPU definition: crates/hipml-core/src/ops.rs:181-187, 260-360, composed as in
+ * attention.rs:117-143. q|gate rows are [n_heads][2*head_dim] (q half first), q / gate rows
+ * [n_heads][head_dim], k rows [n_kv][head_dim]; M-RoPE rotates the first n_rot channels (NeoX
+ * pairs c, c + n_rot/2; frequency theta_base^(-2c/n_rot); f64 angles); sections[4] chooses
+ * which of the four position ids feeds pair c (NULL or all 0: id 0 for every pair). */
+
+/* AttnLayer::front (crates/hipml-kernels/src/attn_gpu.rs:552-600; kernel attn_front_f32.hip:
+ * 34-135): one token. q|gate split, RMS norm of q (weights q_norm) and of k in place
+ * (k_norm), M-RoPE of both; pos = device int[4]. */
+int hipml_attn_front(hipml_stream_t stream, const float *qg, float *q, float *gate, float *k,
+                     const float *q_norm, const float *k_norm, int n_heads, int n_kv, int head_dim,
+                     int n_rot, const int *sections, const int *pos, float theta_base, float eps);
+
+/* The chunk forms (crates/hipml-kernels/src/attn_gpu/imp/attn_chunk.rs:145-199; kernels
+ * attn_chunk_f32.hip:22-98): rows of `tokens` tokens, text positions pos0 + t. */
+int hipml_qg_split_chunk(hipml_stream_t stream, const float *qg, float *q, float *gate, int n_heads,
+                         int head_dim, int tokens);
+int hipml_norm_rope_chunk(hipml_stream_t stream, float *q, float *k, const float *q_norm,
+                          const float *k_norm, int n_heads, int n_kv, int head_dim, int n_rot,
+                          float theta_base, float eps, int pos0, int tokens);
+
+/* The output gate, y = q * sigmoid(gate) over n elements, y may alias q (attn_chunk.rs:345-362;
+ * kernel q_gate_f32.hip). */
+int hipml_q_gate(hipml_stream_t stream, const float *q, const float *gate, float *y, long long n);
+
+/* All of the front end in one pass, with the q8_0 append (no counterpart in the reference,
+ * which runs split, norm+rope and kv_encode as separate launches): for every token t the q|gate
+ * row is split, q and k are normalised and rotated, and the rotated k row and the v row are
+ * quantised straight into cache row pos0 + t. head_dim 256, n_rot a multiple of 16.
+ * k_out (optional) receives the rotated k rows as f32; k_cache / v_cache may both be NULL (no
+ * append). For one decode token give pos (device int[4], M-RoPE ids) and / or step (device,
+ * step[0] = cache row) instead of pos0. */
+int hipml_attn_front_append_q8(hipml_stream_t stream, const float *qg, const float *k,
+                               const float *v, float *q, float *gate, float *k_out,
+                               const float *q_norm, const float *k_norm, void *k_cache,
+                               void *v_cache, int n_heads, int n_kv, int head_dim, int n_rot,
+                               const int *sections, const int *pos, const int *step, int pos0,
+                               int tokens, int stride, float theta_base, float eps);
+
 /* Sequence-split decode across GPUs (no counterpart in the reference, which is single-GPU; the
  * algebra is its split-K reduce, crates/hipml-kernels/kernels/attn_decode_kv.hip:491-532, lifted
  * from thread blocks to devices). Each GPU holds a contiguous range of every KV head's positions
@@ -311,6 +359,15 @@ int hipml_attn_chunk_staged(hipml_stream_t stream, const float *q, float *out, i
                             int n_kv, int head_dim, int pos0, int tokens, float *part_acc,
                             float *part_ml, int splits, int mode, int key_capacity,
                             void *workspace, size_t workspace_bytes);
+
+/* hipml_attn_chunk_staged with the layer's output gate applied where the rows are produced
+ * (the attention epilogue, or the combine pass when splits >= 2): out = attention *
+ * sigmoid(gate), gate f32 [tokens][n_heads*head_dim]. The reference launches q_gate_f32 over
+ * the chunk afterwards (attn_chunk.rs:345-362). */
+int hipml_attn_chunk_staged_gated(hipml_stream_t stream, const float *q, float *out,
+                                  const float *gate, int n_heads, int n_kv, int head_dim, int pos0,
+                                  int tokens, float *part_acc, float *part_ml, int splits, int mode,
+                                  int key_capacity, void *workspace, size_t workspace_bytes);
 
 /* Reads and clears the device status word that kernels with bounded waits set when a wait
  * ran out (0 = none). Synchronises `stream`. Returns HIPML_ERR_DEVICE_STATUS if it was set. */

@@ -68,6 +68,13 @@ def lib() -> C.CDLL:
                                                    C.c_int, C.c_float, f32p]
         L.hipml_oracle_kv_append_f32.argtypes = [f32p, f32p, f32p, f32p, C.c_size_t, C.c_size_t]
         L.hipml_oracle_compare.argtypes = [f32p, f32p, C.c_size_t, f32p, f32p]
+        i4 = C.POINTER(C.c_int)
+        L.hipml_oracle_head_rmsnorm_f32.argtypes = [f32p, f32p, C.c_int, C.c_int, C.c_float, f32p]
+        L.hipml_oracle_rope_multi_f32.argtypes = [f32p, C.c_int, C.c_int, C.c_int, i4, i4, C.c_float,
+                                                  f32p]
+        L.hipml_oracle_rope_neox_f32.argtypes = [f32p, C.c_int, C.c_int, C.c_int, C.c_float, f32p]
+        L.hipml_oracle_qg_split_f32.argtypes = [f32p, C.c_int, C.c_int, f32p, f32p]
+        L.hipml_oracle_q_gate_f32.argtypes = [f32p, f32p, C.c_size_t, f32p]
     return _lib
 
 
@@ -210,3 +217,60 @@ def max_abs(expected, actual) -> float:
     e = np.asarray(expected, dtype=np.float64).ravel()
     a = np.asarray(actual, dtype=np.float64).ravel()
     return float(np.max(np.abs(e - a))) if e.size else 0.0
+
+
+# ---- attention front end and tail (ops.rs:181-187, 195-224, 260-360) ----------------------
+
+def head_rmsnorm_f32(x, w, n_heads, head_dim, eps) -> np.ndarray:
+    x, w = _f32(x), _f32(w)
+    out = np.empty(n_heads * head_dim, dtype=np.float32)
+    lib().hipml_oracle_head_rmsnorm_f32(_p(x, C.c_float), _p(w, C.c_float), n_heads, head_dim, eps,
+                                        _p(out, C.c_float))
+    return out
+
+
+def rope_multi_f32(x, n_heads, head_dim, n_rot, sections, pos, theta_base) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty(n_heads * head_dim, dtype=np.float32)
+    sec = (C.c_int * 4)(*[int(v) for v in sections])
+    ps = (C.c_int * 4)(*[int(v) for v in pos])
+    lib().hipml_oracle_rope_multi_f32(_p(x, C.c_float), n_heads, head_dim, n_rot, sec, ps,
+                                      theta_base, _p(out, C.c_float))
+    return out
+
+
+def rope_neox_f32(x, n_heads, head_dim, pos, theta_base) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty(n_heads * head_dim, dtype=np.float32)
+    lib().hipml_oracle_rope_neox_f32(_p(x, C.c_float), n_heads, head_dim, pos, theta_base,
+                                     _p(out, C.c_float))
+    return out
+
+
+def qg_split_f32(qg, n_heads, head_dim):
+    """Returns (q, gate), each [n_heads * head_dim]."""
+    qg = _f32(qg)
+    q = np.empty(n_heads * head_dim, dtype=np.float32)
+    gate = np.empty(n_heads * head_dim, dtype=np.float32)
+    lib().hipml_oracle_qg_split_f32(_p(qg, C.c_float), n_heads, head_dim, _p(q, C.c_float),
+                                    _p(gate, C.c_float))
+    return q, gate
+
+
+def q_gate_f32(q, gate) -> np.ndarray:
+    q, gate = _f32(q), _f32(gate)
+    out = np.empty(q.size, dtype=np.float32)
+    lib().hipml_oracle_q_gate_f32(_p(q, C.c_float), _p(gate, C.c_float), q.size, _p(out, C.c_float))
+    return out
+
+
+def attn_front(qg, k, q_norm, k_norm, n_heads, n_kv, head_dim, n_rot, sections, pos, theta_base,
+               eps):
+    """The decode front end of attention.rs:117-143 for one token: q|gate split, per-head RMS
+    norm of q and k, M-RoPE of both. Returns (q, gate, k)."""
+    q, gate = qg_split_f32(qg, n_heads, head_dim)
+    q = rope_multi_f32(head_rmsnorm_f32(q, q_norm, n_heads, head_dim, eps), n_heads, head_dim, n_rot,
+                       sections, pos, theta_base)
+    k = rope_multi_f32(head_rmsnorm_f32(k, k_norm, n_kv, head_dim, eps), n_kv, head_dim, n_rot,
+                       sections, pos, theta_base)
+    return q, gate, k

@@ -351,3 +351,75 @@ void hipml_oracle_compare(const float *expected, const float *actual, size_t n, 
     *max_abs = ma;
     *max_rel = mr;
 }
+
+/* ---- attention front end and tail ------------------------------------------------------ */
+
+/* crates/hipml-core/src/ops.rs:181-187: y = x * (1 / sqrt(mean(x^2) + eps)) * w, the sum in
+ * f32 in index order. */
+void hipml_oracle_rmsnorm_f32(const float *x, const float *w, int n, float eps, float *out) {
+    float sum = 0.0f;
+    for (int i = 0; i < n; i++) sum += x[i] * x[i];
+    float mean_sq = sum / (float)n;
+    float scale = 1.0f / sqrtf(mean_sq + eps);
+    for (int i = 0; i < n; i++) out[i] = x[i] * scale * w[i];
+}
+
+/* crates/hipml-core/src/ops.rs:334-350: every head row normalised with the shared w. */
+void hipml_oracle_head_rmsnorm_f32(const float *x, const float *w, int n_heads, int head_dim,
+                                   float eps, float *out) {
+    for (int h = 0; h < n_heads; h++)
+        hipml_oracle_rmsnorm_f32(x + (size_t)h * head_dim, w, head_dim, eps,
+                                 out + (size_t)h * head_dim);
+}
+
+/* crates/hipml-core/src/ops.rs:260-309: M-RoPE. Only the first n_rot channels rotate, NeoX
+ * pair k against k + n_rot/2, frequency theta_base^(-2k/n_rot), the angle in f64; the section
+ * table picks which of the four position ids feeds pair k. */
+void hipml_oracle_rope_multi_f32(const float *x, int n_heads, int head_dim, int n_rot,
+                                 const int sections[4], const int pos[4], float theta_base,
+                                 float *out) {
+    const int half = n_rot / 2;
+    const int sect = sections[0] + sections[1] + sections[2] + sections[3];
+    memcpy(out, x, (size_t)n_heads * head_dim * sizeof(float));
+    for (int h = 0; h < n_heads; h++) {
+        const size_t base = (size_t)h * head_dim;
+        for (int k = 0; k < half; k++) {
+            int p = pos[0];
+            if (sect != 0) {
+                const int s = k % sect;
+                if (s < sections[0]) p = pos[0];
+                else if (s < sections[0] + sections[1]) p = pos[1];
+                else if (s < sections[0] + sections[1] + sections[2]) p = pos[2];
+                else p = pos[3];
+            }
+            const double freq = pow((double)theta_base, -2.0 * (double)k / (double)n_rot);
+            const double ang = (double)p * freq;
+            const float sn = (float)sin(ang), cs = (float)cos(ang);
+            const float x1 = x[base + k], x2 = x[base + half + k];
+            out[base + k] = x1 * cs - x2 * sn;
+            out[base + half + k] = x1 * sn + x2 * cs;
+        }
+    }
+}
+
+/* crates/hipml-core/src/ops.rs:195-224: plain NeoX rope over the whole head. */
+void hipml_oracle_rope_neox_f32(const float *x, int n_heads, int head_dim, int pos,
+                                float theta_base, float *out) {
+    const int sections[4] = {0, 0, 0, 0};
+    const int p[4] = {pos, pos, pos, pos};
+    hipml_oracle_rope_multi_f32(x, n_heads, head_dim, head_dim, sections, p, theta_base, out);
+}
+
+/* crates/hipml-core/src/ops.rs:315-329: joint [n_heads][2*head_dim] -> q then gate. */
+void hipml_oracle_qg_split_f32(const float *qg, int n_heads, int head_dim, float *q, float *gate) {
+    for (int h = 0; h < n_heads; h++) {
+        memcpy(q + (size_t)h * head_dim, qg + (size_t)h * 2 * head_dim, head_dim * sizeof(float));
+        memcpy(gate + (size_t)h * head_dim, qg + (size_t)h * 2 * head_dim + head_dim,
+               head_dim * sizeof(float));
+    }
+}
+
+/* crates/hipml-core/src/ops.rs:354-360: y = q * (1 / (1 + exp(-gate))). */
+void hipml_oracle_q_gate_f32(const float *q, const float *gate, size_t n, float *out) {
+    for (size_t i = 0; i < n; i++) out[i] = q[i] * (1.0f / (1.0f + expf(-gate[i])));
+}

@@ -92,6 +92,18 @@ void hipml_oracle_kv_append_f32(float *k_cache, float *v_cache, const float *k, 
 void hipml_oracle_compare(const float *expected, const float *actual, size_t n, float *max_abs,
                           float *max_rel);
 
+/* Attention front end and tail (crates/hipml-core/src/ops.rs:181-187, 195-224, 260-360). */
+void hipml_oracle_rmsnorm_f32(const float *x, const float *w, int n, float eps, float *out);
+void hipml_oracle_head_rmsnorm_f32(const float *x, const float *w, int n_heads, int head_dim,
+                                   float eps, float *out);
+void hipml_oracle_rope_multi_f32(const float *x, int n_heads, int head_dim, int n_rot,
+                                 const int sections[4], const int pos[4], float theta_base,
+                                 float *out);
+void hipml_oracle_rope_neox_f32(const float *x, int n_heads, int head_dim, int pos,
+                                float theta_base, float *out);
+void hipml_oracle_qg_split_f32(const float *qg, int n_heads, int head_dim, float *q, float *gate);
+void hipml_oracle_q_gate_f32(const float *q, const float *gate, size_t n, float *out);
+
 #ifdef __cplusplus
 }
 #endif
