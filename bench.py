@@ -384,6 +384,67 @@ def decode_bench(torch, api, depths, steps, layers, hbm_gbs, reps=3):
     return results
 
 
+def front_end_bench(torch, api, hbm_gbs, tokens=CHUNK, reps=5):
+    """The attention front end of one 2048-token chunk (q|gate split, head RMS norm, M-RoPE,
+    q8_0 append): the one-pass fused kernel against the separate launches the reference makes
+    (split, norm + rope, kv_encode_bulk), plus the output gate as its own pass. HBM-bound:
+    algorithmic bytes per token = q|gate 48 KB in + q 24 KB + gate 24 KB out + k, v 8 KB in +
+    2,176 B of cache rows out = 108.7 KB (the separate form re-reads q and k: +56 KB)."""
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(5)
+    qg = torch.randn(tokens, H * 2 * D, device=dev, generator=g)
+    k = torch.randn(tokens, W, device=dev, generator=g)
+    v = torch.randn(tokens, W, device=dev, generator=g)
+    qn = 1.0 + 0.1 * torch.randn(D, device=dev, generator=g)
+    kn = 1.0 + 0.1 * torch.randn(D, device=dev, generator=g)
+    q = torch.empty(tokens, QW, device=dev)
+    gate = torch.empty(tokens, QW, device=dev)
+    stride = tokens + 8
+    kc = torch.zeros(KV * stride * ROW, dtype=torch.uint8, device=dev)
+    vc = torch.zeros_like(kc)
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)   # larger than L2
+
+    def fused():
+        api.attn_front_append_q8(qg, k, v, q, gate, qn, kn, kc, vc, H, KV, D, 64, 1e7, 1e-6, pos0=0,
+                                 tokens=tokens, stride=stride)
+
+    k2 = torch.empty_like(k)
+
+    def separate():
+        k2.copy_(k)
+        api.qg_split_chunk(qg, q, gate, H, D, tokens)
+        api.norm_rope_chunk(q, k2, qn, kn, H, KV, D, 64, 1e7, 1e-6, 0, tokens)
+        api.kv_encode_bulk(k2, v, kc, vc, KV, D, stride, 0, 0, tokens)
+
+    def gate_pass():
+        api.q_gate(q, gate, q, tokens * QW)
+
+    def timed(fn):
+        best = float("inf")
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return best
+
+    fused()
+    want_k = kc.clone()
+    separate()
+    same = bool(torch.equal(want_k, kc))
+    ms_fused, ms_sep, ms_gate = timed(fused), timed(separate), timed(gate_pass)
+    bytes_fused = tokens * (H * 2 * D * 4 + 2 * QW * 4 + 2 * W * 4 + 2 * KV * ROW)
+    bytes_gate = tokens * QW * 4 * 3
+    return {"tokens": tokens, "fused_ms": ms_fused, "separate_launches_ms": ms_sep,
+            "fused_gbs": bytes_fused / ms_fused / 1e6, "frac_hbm": bytes_fused / ms_fused / 1e6 / hbm_gbs,
+            "gate_pass_ms": ms_gate, "gate_pass_gbs": bytes_gate / ms_gate / 1e6,
+            "cache_rows_match_separate_form": same,
+            "l2": "a 192 MB buffer is rewritten between repetitions"}
+
+
 def decode_batched(torch, api, slots_list, layers, hbm_gbs, steps=32, reps=3):
     """BASELINE configs[3]: multi-slot decode, B = 8 and 16, per-slot depth uniform in
     [512, 8192] from seed 3, one q8_0 region per slot in a contiguous cache (stride 8448).
@@ -740,6 +801,7 @@ def gpu_main(args):
                                           pk["hbm_gbs"])
             line["decode_peak_hbm_gbs"] = pk["hbm_gbs"]
             line["decode_batched"] = decode_batched(torch, api, (8, 16), LAYERS, pk["hbm_gbs"])
+            line["front_end"] = front_end_bench(torch, api, pk["hbm_gbs"])
     if not args.no_decode:
         # BASELINE configs[4], prefill phase: 100,000 tokens, one layer timed, same partition
         pf = None
@@ -843,6 +905,10 @@ def profile_case(args):
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(7)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.reps)]
+    if args.case == "front":
+        r = front_end_bench(torch, api, peaks()["hbm_gbs"], reps=args.reps)
+        print(json.dumps({"case": "front end of a 2048-token chunk", **r}))
+        return
     if args.case == "chunk":
         # --kv-heads < 4 stands for one rank's share of a KV-head-sharded job
         pos0, n, stride = 6144, 2048, 8200
@@ -911,7 +977,7 @@ def profile_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["chunk", "decode"], default=None,
+    ap.add_argument("--case", choices=["chunk", "decode", "front"], default=None,
                     help="run one small profiling case instead of the benchmark")
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--mode", type=int, default=0)
