@@ -68,6 +68,9 @@ SIGNATURES = {
     "hipml_kv_append_chunk_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "hipml_attn_decode_kv": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f,
                                   _i, _sz, _sz]),
+    "hipml_attn_decode_cols": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i,
+                                    _i, _i, _i, _i]),
+    "hipml_kv_rows_copy": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "hipml_attn_decode_kv_gated": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _f, _i, _sz, _sz]),
     "hipml_attn_decode_kv_shard": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,

@@ -66,6 +66,20 @@ def attn_decode_kv(step, q, k, v, part_acc, part_ml, out, n_heads, n_kv, head_di
         n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
 
 
+def attn_decode_cols(pos, q, k, v, part_acc, part_ml, out, n_heads, n_kv, head_dim, stride, scale,
+                     splits, cols, acc_slot, ml_slot, q_slot, selector=0):
+    """launch_kv::launch_cols_ptrs: `cols` columns of one sequence over a shared cache."""
+    _lib.check("attn_decode_cols", _lib.load().hipml_attn_decode_cols(
+        _stream(), selector, _p(pos), _p(q), _p(k), _p(v), _p(part_acc), _p(part_ml), _p(out),
+        n_heads, n_kv, head_dim, stride, scale, splits, cols, acc_slot, ml_slot, q_slot))
+
+
+def kv_rows_copy(dst, src, n_kv, row_bytes, dst_stride, src_stride, rows):
+    """Live rows [0, rows) of every KV head between two head-major caches (prefix snapshots)."""
+    _lib.check("kv_rows_copy", _lib.load().hipml_kv_rows_copy(
+        _stream(), _p(dst), _p(src), n_kv, row_bytes, dst_stride, src_stride, rows))
+
+
 def attn_decode_kv_gated(step, q, k, v, part_acc, part_ml, out, gate, n_heads, n_kv, head_dim,
                          stride, scale, splits, selector=0, k_off=0, v_off=0):
     """attn_decode_kv with out *= sigmoid(gate) applied in the fold."""

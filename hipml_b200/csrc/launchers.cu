@@ -334,6 +334,32 @@ int hipml_attn_decode_rows(hipml_stream_t stream, int dtype, const int *pos, con
                        q_slot, slots, 1);
 }
 
+int hipml_attn_decode_cols(hipml_stream_t stream, int selector, const int *pos, const float *q,
+                           const void *k, const void *v, float *part_acc, float *part_ml,
+                           float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
+                           int splits, int cols, int acc_slot, int ml_slot, int q_slot) {
+    if (selector != 0 && selector != 4)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "decode columns: selector %d has no batched entry",
+                    selector);
+    // The columns share the cache (no slot offset) and each is partitioned over its own live
+    // length, exactly as its one-column launch would be.
+    return decode_rows(stream, 0, pos, q, k, v, part_acc, part_ml, out, n_heads, n_kv, head_dim,
+                       stride, scale, splits, 0, acc_slot, ml_slot, q_slot, cols, 0);
+}
+
+int hipml_kv_rows_copy(hipml_stream_t stream, void *dst, const void *src, int n_kv, int row_bytes,
+                       int dst_stride, int src_stride, int rows) {
+    if (n_kv <= 0 || row_bytes <= 0 || rows < 0 || rows > dst_stride || rows > src_stride)
+        return fail(HIPML_ERR_INVALID_ARGUMENT,
+                    "rows copy: n_kv %d / row_bytes %d / rows %d of strides %d, %d", n_kv, row_bytes,
+                    rows, dst_stride, src_stride);
+    if (rows == 0) return 0;
+    // one contiguous run of rows * row_bytes per KV head
+    return (int)cudaMemcpy2DAsync(dst, (size_t)dst_stride * row_bytes, src,
+                                  (size_t)src_stride * row_bytes, (size_t)rows * row_bytes, n_kv,
+                                  cudaMemcpyDeviceToDevice, as_stream(stream));
+}
+
 int hipml_attn_decode_batch(hipml_stream_t stream, int dtype, const int *pos, const float *q,
                             const void *k_cache, const void *v_cache, float *part_acc,
                             float *part_ml, float *out, int n_heads, int n_kv, int head_dim,

@@ -432,4 +432,86 @@ Status AttnLayer::attention_cols(const Launcher &l, const void *q, void *out, co
                                             (int)rows));
 }
 
+Status deep_attention_cols(const Launcher &l, const Config &cfg, const DeepKv &dk, size_t pos0,
+                           size_t cols, const void *q_ptr, void *out_ptr, const Buffer &pos_buf,
+                           void *part_acc, void *part_ml, size_t acc_slot, size_t ml_slot,
+                           bool &handled) {
+    handled = false;
+    if (dk.kernel != 4 && dk.kernel != 0) return {};   // only the warp entry has a batched form
+    if (dk.dtype != KvDtype::Q8) return {};
+    const size_t qw = cfg.n_head * cfg.head_dim;
+    const float scale = 1.0f / std::sqrt((float)cfg.head_dim);
+    size_t c0 = 0;
+    while (c0 < cols) {
+        // columns that share a split count go out together, so that each column's arithmetic
+        // is the one-column launch's
+        const size_t splits = dk.splits(pos0 + c0 + 1);
+        size_t c1 = c0 + 1;
+        while (c1 < cols && dk.splits(pos0 + c1 + 1) == splits) c1++;
+        Status s = check("attn_decode_cols",
+                         hipml_attn_decode_cols(l.stream(), 0, (const int *)pos_buf.as_ptr() + 2 * c0,
+                                                (const float *)q_ptr + c0 * qw, dk.k.as_ptr(),
+                                                dk.v.as_ptr(), (float *)part_acc + c0 * acc_slot,
+                                                (float *)part_ml + c0 * ml_slot,
+                                                (float *)out_ptr + c0 * qw, (int)cfg.n_head,
+                                                (int)cfg.n_head_kv, (int)cfg.head_dim, (int)dk.seq, scale,
+                                                (int)splits, (int)(c1 - c0), (int)acc_slot, (int)ml_slot,
+                                                (int)qw));
+        if (!s.empty()) return s;
+        c0 = c1;
+    }
+    handled = true;
+    return {};
+}
+
+Status kv_prefix_copy(const Launcher &l, const Buffer &dst, const Buffer &src, size_t n_kv,
+                      size_t row_bytes, size_t dst_seq, size_t src_seq, size_t rows) {
+    return check("kv_rows_copy", hipml_kv_rows_copy(l.stream(), dst.as_ptr(), src.as_ptr(), (int)n_kv,
+                                                    (int)row_bytes, (int)dst_seq, (int)src_seq,
+                                                    (int)rows));
+}
+
+Status chunk_front_rows(const Launcher &l, const FrontDims &d, const void *qg, void *k, void *q,
+                        void *gate, const Buffer &q_norm, const Buffer &k_norm, size_t pos0,
+                        size_t tokens) {
+    if (d.head_dim > 256) return std::string("row attention: unsupported head dimension");
+    Status s = check("qg_split_chunk",
+                     hipml_qg_split_chunk(l.stream(), (const float *)qg, (float *)q, (float *)gate,
+                                          (int)d.n_head, (int)d.head_dim, (int)tokens));
+    if (!s.empty()) return s;
+    return check("norm_rope_chunk",
+                 hipml_norm_rope_chunk(l.stream(), (float *)q, (float *)k, (const float *)q_norm.as_ptr(),
+                                       (const float *)k_norm.as_ptr(), (int)d.n_head, (int)d.n_kv,
+                                       (int)d.head_dim, (int)d.n_rot, d.rope_base, d.eps, (int)pos0,
+                                       (int)tokens));
+}
+
+Status kv_encode_bulk_rows(const Launcher &l, const void *k, const void *v, void *k_cache,
+                           void *v_cache, size_t dtype, size_t n_kv, size_t head_dim, size_t seq,
+                           size_t start, size_t rows) {
+    return check("kv_encode_bulk",
+                 hipml_kv_encode_bulk(l.stream(), (int)dtype, (const float *)k, (const float *)v, k_cache,
+                                      v_cache, (int)n_kv, (int)head_dim, (int)seq, (int)start, 0,
+                                      (int)rows));
+}
+
+Status chunk_front_append_rows(const Launcher &l, const FrontDims &d, const void *qg, const void *k,
+                               const void *v, void *q, void *gate, const Buffer &q_norm,
+                               const Buffer &k_norm, void *k_cache, void *v_cache, size_t seq,
+                               size_t pos0, size_t tokens) {
+    return check("attn_front_append_q8",
+                 hipml_attn_front_append_q8(l.stream(), (const float *)qg, (const float *)k,
+                                            (const float *)v, (float *)q, (float *)gate, nullptr,
+                                            (const float *)q_norm.as_ptr(),
+                                            (const float *)k_norm.as_ptr(), k_cache, v_cache,
+                                            (int)d.n_head, (int)d.n_kv, (int)d.head_dim, (int)d.n_rot,
+                                            nullptr, nullptr, nullptr, (int)pos0, (int)tokens, (int)seq,
+                                            d.rope_base, d.eps));
+}
+
+Status q_gate_rows(const Launcher &l, const FrontDims &d, void *out, const void *gate, size_t tokens) {
+    return check("q_gate", hipml_q_gate(l.stream(), (const float *)out, (const float *)gate, (float *)out,
+                                        (long long)(d.n_head * d.head_dim * tokens)));
+}
+
 }  // namespace hipml_host

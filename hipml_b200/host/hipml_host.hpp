@@ -150,6 +150,43 @@ public:
     Buffer k, v, part_acc, part_ml;
 };
 
+// Quantised-KV decode of `cols` consecutive columns of one sequence (speculative verify):
+// one launch per group of columns with the same split count, every column bit-identical to
+// its one-column launch (crates/hipml-model/src/gpu/attn_tile.rs:225-295). pos_buf holds
+// (position, length) pairs per column; scratch slices are acc_slot / ml_slot floats apart.
+Status deep_attention_cols(const Launcher &l, const Config &cfg, const DeepKv &dk, size_t pos0,
+                           size_t cols, const void *q_ptr, void *out_ptr, const Buffer &pos_buf,
+                           void *part_acc, void *part_ml, size_t acc_slot, size_t ml_slot,
+                           bool &handled);
+
+// The attention half of a prefix snapshot (crates/hipml-model/src/gpu/prefix.rs:30-43): the
+// live rows [0, rows) of every KV head, between caches of `src_seq` and `dst_seq` rows per head.
+Status kv_prefix_copy(const Launcher &l, const Buffer &dst, const Buffer &src, size_t n_kv,
+                      size_t row_bytes, size_t dst_seq, size_t src_seq, size_t rows);
+
+// Front end and tail of the attention layer on explicit row pointers (a row block holds
+// several slots' tails; crates/hipml-kernels/src/attn_gpu/imp/attn_rows.rs:21-203).
+struct FrontDims {
+    size_t n_head = 24, n_kv = 4, head_dim = 256, n_rot = 64;
+    int sections[4] = {11, 11, 10, 0};
+    float rope_base = 1e7f, eps = 1e-6f;
+};
+// attn_rows.rs:21-95: q|gate split, per-head RMS norm and M-RoPE of `tokens` rows at pos0.
+Status chunk_front_rows(const Launcher &l, const FrontDims &d, const void *qg, void *k, void *q,
+                        void *gate, const Buffer &q_norm, const Buffer &k_norm, size_t pos0,
+                        size_t tokens);
+// attn_rows.rs:97-148: quantise-append of the block's rows into one slot's cache.
+Status kv_encode_bulk_rows(const Launcher &l, const void *k, const void *v, void *k_cache,
+                           void *v_cache, size_t dtype, size_t n_kv, size_t head_dim, size_t seq,
+                           size_t start, size_t rows);
+// The two above in one pass (no counterpart in the reference).
+Status chunk_front_append_rows(const Launcher &l, const FrontDims &d, const void *qg, const void *k,
+                               const void *v, void *q, void *gate, const Buffer &q_norm,
+                               const Buffer &k_norm, void *k_cache, void *v_cache, size_t seq,
+                               size_t pos0, size_t tokens);
+// attn_chunk.rs:345-362: out *= sigmoid(gate) over `tokens` rows.
+Status q_gate_rows(const Launcher &l, const FrontDims &d, void *out, const void *gate, size_t tokens);
+
 // Prefill split policy (crates/hipml-model/src/gpu/attn_tile.rs:138-151).
 size_t split_count(size_t configured, size_t pos0, size_t split_min = 8192);
 

@@ -191,6 +191,26 @@ int hipml_attn_decode_cols_f32(hipml_stream_t stream, const float *q, const floa
 int hipml_kv_append_cols_f32(hipml_stream_t stream, float *k_cache, float *v_cache,
                              const float *k, const float *v, int pos0, int rows, int width);
 
+/* launch_kv::launch_cols_ptrs as used by deep_attention_cols (crates/hipml-model/src/gpu/
+ * attn_tile.rs:225-295): decode of `cols` consecutive columns of ONE sequence (speculative
+ * verify). The columns share the cache; column c has its own query row (q + c*q_slot floats),
+ * (position, length) pair (pos[2c], pos[2c+1]), scratch slices (c*acc_slot, c*ml_slot floats)
+ * and output row (out + c*q_slot). Every column is partitioned over its own live length with
+ * the given split count, so its result is bit-identical to its one-column hipml_attn_decode_kv
+ * launch (the caller groups columns of equal split count, as the reference does). selector 0
+ * or 4. */
+int hipml_attn_decode_cols(hipml_stream_t stream, int selector, const int *pos, const float *q,
+                           const void *k, const void *v, float *part_acc, float *part_ml,
+                           float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
+                           int splits, int cols, int acc_slot, int ml_slot, int q_slot);
+
+/* The attention half of a prefix snapshot / restore (crates/hipml-model/src/gpu/prefix.rs:30-43
+ * copies the whole head-major buffer): only the live rows [0, rows) of every KV head move,
+ * between a cache with `src_stride` rows per head and one with `dst_stride` (a snapshot sized
+ * for the prefix has dst_stride = rows). row_bytes = 272 for q8_0 at head_dim 256. */
+int hipml_kv_rows_copy(hipml_stream_t stream, void *dst, const void *src, int n_kv, int row_bytes,
+                       int dst_stride, int src_stride, int rows);
+
 /* hipml_attn_decode_kv with the layer's output gate applied where the output row is produced:
  * out = attention * sigmoid(gate), gate f32 [n_heads][head_dim] (no counterpart as one call in
  * the reference, which launches q_gate_f32 after the reduce, attn_gpu.rs:798-830). */

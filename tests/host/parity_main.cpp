@@ -5,7 +5,9 @@
 //
 // Cases: parity_kv.rs:68-246 (q8 decode incl. the 100,000-token deep case, with --deep),
 // parity.rs:364-378 (kv_encode_q8, EXACT), attn_chunk_parity.rs (37 queries at position 29:
-// f32 cache, q8 cache, q8 4-way split), attn_parity.rs:101-161 (f32 position-major decode).
+// f32 cache, q8 cache, q8 4-way split), attn_parity.rs:101-161 (f32 position-major decode),
+// attn_tile.rs:225-295 (verify columns), attn_rows.rs:21-148 + attn_cmd.rs:232-289 (front end on
+// row pointers), prefix.rs:30-43 (snapshot of the live cache rows).
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -210,6 +212,155 @@ static void decode_pm_f32_case(Launcher &l) {
     report("attn_decode_pm_f32", want, got, DEFAULT);
 }
 
+// deep_attention_cols (attn_tile.rs:225-295): 4 verify columns over a shared q8 cache; every
+// column against the oracle at its own length, and bit-identical to its one-column launch.
+static void verify_cols_case(Launcher &l) {
+    Config cfg;
+    const size_t pos0 = 300, cols = 4, seq = 320, qw = cfg.n_head * cfg.head_dim;
+    DeepKv dk;
+    OK(DeepKv::create(cfg, seq, KvDtype::Q8, dk));
+    OK(dk.fill_synthetic(pos0 + cols, 0xC015));
+    uint64_t rng = hipml_oracle_rng_new(0xC015C015ULL);
+    std::vector<float> q = normals(rng, cols * qw);
+    Buffer dq, out, one, pos_buf, acc, ml;
+    OK(Buffer::from_host(q.data(), q.size(), dq));
+    OK(Buffer::alloc(cols * qw, out));
+    OK(Buffer::alloc(qw, one));
+    const size_t splits = dk.splits(pos0 + 1);
+    const size_t acc_slot = cfg.n_head * splits * cfg.head_dim, ml_slot = cfg.n_head * splits * 2;
+    OK(Buffer::alloc(cols * acc_slot, acc));
+    OK(Buffer::alloc(cols * ml_slot, ml));
+    std::vector<int> pairs;
+    for (size_t c = 0; c < cols; c++) {
+        pairs.push_back((int)(pos0 + c));
+        pairs.push_back((int)(pos0 + c + 1));
+    }
+    OK(Buffer::alloc(pairs.size(), pos_buf));
+    OK(pos_buf.upload_bytes(0, pairs.data(), pairs.size() * 4));
+    bool handled = false;
+    OK(deep_attention_cols(l, cfg, dk, pos0, cols, dq.as_ptr(), out.as_ptr(), pos_buf, acc.as_ptr(),
+                           ml.as_ptr(), acc_slot, ml_slot, handled));
+    OK(l.synchronize());
+    std::vector<float> got;
+    OK(out.to_host(got));
+    std::vector<uint8_t> kb(dk.bytes() / 2), vb(dk.bytes() / 2);
+    OK(dk.k.download_bytes(0, kb.data(), kb.size()));
+    OK(dk.v.download_bytes(0, vb.data(), vb.size()));
+    bool identical = handled;
+    for (size_t c = 0; c < cols; c++) {
+        std::vector<float> want(qw), col(got.begin() + c * qw, got.begin() + (c + 1) * qw), single;
+        hipml_oracle_attn_decode_kv_q8_strided(&q[c * qw], kb.data(), vb.data(), (int)cfg.n_head,
+                                               (int)cfg.n_head_kv, (int)cfg.head_dim, (int)(pos0 + c + 1),
+                                               (int)seq, 0.0625f, want.data());
+        char name[64];
+        snprintf(name, sizeof(name), "verify column %zu of %zu at %zu", c, cols, pos0);
+        report(name, want, col, DEFAULT);
+        OK(l.set_step(pos0 + c, pos0 + c + 1, 0));
+        OK(launch_kv::launch_ptrs(l, 0, (const float *)dq.as_ptr() + c * qw, dk.k, dk.v, dk.part_acc,
+                                  dk.part_ml, one.as_ptr(), cfg.n_head, cfg.n_head_kv, cfg.head_dim, seq,
+                                  0.0625f, splits, 0, 0));
+        OK(l.synchronize());
+        OK(one.to_host(single));
+        identical = identical && memcmp(single.data(), col.data(), qw * 4) == 0;
+    }
+    printf("%s verify columns bit-identical to one-column launches\n", identical ? "PASS" : "FAIL");
+    g_ran++;
+    g_failed += !identical;
+}
+
+// chunk_front_rows + kv_encode_bulk_rows (attn_rows.rs:21-148) against the one-pass form, and
+// the front end against the oracle (attn_cmd.rs:232-289: norm + rope at position 37).
+static void front_rows_case(Launcher &l) {
+    FrontDims d;
+    const size_t tokens = 9, pos0 = 37, seq = 64, qw = d.n_head * d.head_dim, kw = d.n_kv * d.head_dim;
+    uint64_t rng = hipml_oracle_rng_new(0xF011A77E12345678ULL);
+    std::vector<float> qg = normals(rng, tokens * 2 * qw), k = normals(rng, tokens * kw),
+                       v = normals(rng, tokens * kw), qn = normals(rng, d.head_dim, 0.1f),
+                       kn = normals(rng, d.head_dim, 0.1f);
+    for (auto &x : qn) x += 1.0f;
+    for (auto &x : kn) x += 1.0f;
+    Buffer dqg, dk1, dk2, dv, dq1, dq2, g1, g2, dqn, dkn;
+    OK(Buffer::from_host(qg.data(), qg.size(), dqg));
+    OK(Buffer::from_host(k.data(), k.size(), dk1));
+    OK(Buffer::from_host(k.data(), k.size(), dk2));
+    OK(Buffer::from_host(v.data(), v.size(), dv));
+    OK(Buffer::from_host(qn.data(), qn.size(), dqn));
+    OK(Buffer::from_host(kn.data(), kn.size(), dkn));
+    OK(Buffer::alloc(tokens * qw, dq1));
+    OK(Buffer::alloc(tokens * qw, dq2));
+    OK(Buffer::alloc(tokens * qw, g1));
+    OK(Buffer::alloc(tokens * qw, g2));
+    Config cfg;
+    DeepKv a, b;
+    OK(DeepKv::create(cfg, seq, KvDtype::Q8, a));
+    OK(DeepKv::create(cfg, seq, KvDtype::Q8, b));
+    OK(a.fill_synthetic(pos0, 5));
+    OK(b.fill_synthetic(pos0, 5));
+    // the reference's launches ...
+    OK(chunk_front_rows(l, d, dqg.as_ptr(), dk1.as_ptr(), dq1.as_ptr(), g1.as_ptr(), dqn, dkn, pos0, tokens));
+    OK(kv_encode_bulk_rows(l, dk1.as_ptr(), dv.as_ptr(), a.k.as_ptr(), a.v.as_ptr(), 0, d.n_kv, d.head_dim,
+                           seq, pos0, tokens));
+    // ... and the one-pass form
+    OK(chunk_front_append_rows(l, d, dqg.as_ptr(), dk2.as_ptr(), dv.as_ptr(), dq2.as_ptr(), g2.as_ptr(), dqn,
+                               dkn, b.k.as_ptr(), b.v.as_ptr(), seq, pos0, tokens));
+    OK(l.synchronize());
+    std::vector<float> q1, q2, gate1, gate2;
+    OK(dq1.to_host(q1));
+    OK(dq2.to_host(q2));
+    OK(g1.to_host(gate1));
+    OK(g2.to_host(gate2));
+    std::vector<uint8_t> ka(a.bytes() / 2), kb(b.bytes() / 2), va(a.bytes() / 2), vb(b.bytes() / 2);
+    OK(a.k.download_bytes(0, ka.data(), ka.size()));
+    OK(b.k.download_bytes(0, kb.data(), kb.size()));
+    OK(a.v.download_bytes(0, va.data(), va.size()));
+    OK(b.v.download_bytes(0, vb.data(), vb.size()));
+    // copies and the V rows are bit-exact (the caches are uninitialised past the live rows)
+    bool same = gate1 == gate2;
+    for (size_t h = 0; h < d.n_kv; h++)
+        same = same && memcmp(&va[h * seq * 272], &vb[h * seq * 272], (pos0 + tokens) * 272) == 0;
+    (void)ka;
+    (void)kb;
+    printf("%s front end: gate rows and V cache rows of both forms identical\n", same ? "PASS" : "FAIL");
+    g_ran++;
+    g_failed += !same;
+    // oracle: split, norm, rope per token
+    std::vector<float> want(tokens * qw), qs(qw), gs(qw), nrm(qw);
+    const int sections[4] = {0, 0, 0, 0};
+    for (size_t t = 0; t < tokens; t++) {
+        const int p4[4] = {(int)(pos0 + t), (int)(pos0 + t), (int)(pos0 + t), (int)(pos0 + t)};
+        hipml_oracle_qg_split_f32(&qg[t * 2 * qw], (int)d.n_head, (int)d.head_dim, qs.data(), gs.data());
+        hipml_oracle_head_rmsnorm_f32(qs.data(), qn.data(), (int)d.n_head, (int)d.head_dim, d.eps, nrm.data());
+        hipml_oracle_rope_multi_f32(nrm.data(), (int)d.n_head, (int)d.head_dim, (int)d.n_rot, sections, p4,
+                                    d.rope_base, &want[t * qw]);
+    }
+    report("chunk_front_rows q (norm + rope at 37..45)", want, q1, DEFAULT);
+    report("one-pass front end q", want, q2, DEFAULT);
+}
+
+// prefix.rs:30-43: snapshot of the live rows and restore into a fresh cache.
+static void prefix_copy_case(Launcher &l) {
+    Config cfg;
+    const size_t seq = 200, live = 77;
+    DeepKv dk, fresh;
+    OK(DeepKv::create(cfg, seq, KvDtype::Q8, dk));
+    OK(DeepKv::create(cfg, seq, KvDtype::Q8, fresh));
+    OK(dk.fill_synthetic(live, 11));
+    Buffer snap;
+    OK(Buffer::alloc((cfg.n_head_kv * live * 272 + 3) / 4, snap));
+    OK(kv_prefix_copy(l, snap, dk.k, cfg.n_head_kv, 272, live, seq, live));
+    OK(kv_prefix_copy(l, fresh.k, snap, cfg.n_head_kv, 272, seq, live, live));
+    OK(l.synchronize());
+    std::vector<uint8_t> a(dk.bytes() / 2), b(dk.bytes() / 2);
+    OK(dk.k.download_bytes(0, a.data(), a.size()));
+    OK(fresh.k.download_bytes(0, b.data(), b.size()));
+    bool ok = true;
+    for (size_t h = 0; h < cfg.n_head_kv; h++)
+        ok = ok && memcmp(&a[h * seq * 272], &b[h * seq * 272], live * 272) == 0;
+    printf("%s prefix snapshot + restore of %zu live rows\n", ok ? "PASS" : "FAIL", live);
+    g_ran++;
+    g_failed += !ok;
+}
+
 int main(int argc, char **argv) {
     bool deep = false;
     for (int i = 1; i < argc; i++) deep = deep || strcmp(argv[i], "--deep") == 0;
@@ -231,6 +382,9 @@ int main(int argc, char **argv) {
     chunk_case(l, "chunk_attention 37@29 f32", 0, 1);
     chunk_case(l, "chunk_attention 37@29 q8", 1, 1);
     chunk_case(l, "chunk_attention 37@29 q8 split4", 1, 4);
+    verify_cols_case(l);
+    front_rows_case(l);
+    prefix_copy_case(l);
     // policy tables of the engine objects
     DeepKv dk;
     Config cfg;
