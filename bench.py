@@ -894,7 +894,8 @@ def profile_case(args):
     chunk  -- one 2048-token chunk at position 6144 of one layer (the largest chunk of the
               headline workload): kv_encode_bulk, stage, attn_chunk_tc, `--reps` times;
     decode -- one layer's decode at depth 100000 (217.6 MB of q8 K/V, larger than L2):
-              kv_encode_q8, attn_decode_kv_tc, attn_decode_kv_reduce, `--reps` times.
+              kv_encode_q8, attn_decode_kv_tc, attn_decode_kv_reduce, `--reps` times
+              (`--selector 1`: the same over a q4_0 cache, 115.2 MB).
     Prints the CUDA-event time per repetition so the capture has an un-profiled number."""
     import torch
 
@@ -944,13 +945,16 @@ def profile_case(args):
     else:
         depth = args.depth
         stride = depth + 136
-        kc = torch.zeros(KV * stride * ROW, dtype=torch.uint8, device=dev)
+        # --selector 1 runs the same case over a q4_0 cache (144-byte rows)
+        kvd = 1 if args.selector == 1 else 0
+        row = 144 if kvd else ROW
+        kc = torch.zeros(KV * stride * row, dtype=torch.uint8, device=dev)
         vc = torch.zeros_like(kc)
         for p0 in range(0, depth, 8192):
             n = min(8192, depth - p0)
             api.kv_encode_bulk(torch.randn(n, W, device=dev, generator=g),
                                torch.randn(n, W, device=dev, generator=g), kc, vc, KV, D, stride,
-                               p0, 0, n)
+                               p0, 0, n, dtype=kvd)
         q = torch.randn(args.reps, QW, device=dev, generator=g)
         kn = torch.randn(args.reps, W, device=dev, generator=g)
         vn = torch.randn(args.reps, W, device=dev, generator=g)
@@ -962,7 +966,7 @@ def profile_case(args):
         steps[:, 1] = steps[:, 0] + 1
         torch.cuda.synchronize()
         for r in range(args.reps):
-            api.kv_encode(steps[r], kn[r], vn[r], kc, vc, KV, D, stride)
+            api.kv_encode(steps[r], kn[r], vn[r], kc, vc, KV, D, stride, dtype=kvd)
             ev[2 * r].record()
             api.attn_decode_kv(steps[r], q[r], kc, vc, acc, ml, out[r], H, KV, D, stride, SCALE,
                                api.decode_splits(depth + r + 1), selector=args.selector)
@@ -970,7 +974,7 @@ def profile_case(args):
         torch.cuda.synchronize()
         for r in range(args.reps):
             ms = ev[2 * r].elapsed_time(ev[2 * r + 1])
-            nbytes = 2 * KV * (depth + r + 1) * ROW
+            nbytes = 2 * KV * (depth + r + 1) * row
             print(json.dumps({"case": f"decode depth {depth}", "selector": args.selector, "ms": ms,
                               "kv_gbs": nbytes / ms / 1e6}))
 

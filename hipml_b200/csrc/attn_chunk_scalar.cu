@@ -10,6 +10,7 @@
 // attn_chunk_combine_f32 replaces crates/hipml-kernels/kernels/attn_chunk_split.hip:343-376
 // and keeps its name, parameter list and launch shape.
 #include "params.cuh"
+#include "q8_pack.cuh"
 
 namespace hipml {
 
@@ -58,6 +59,25 @@ __global__ void __launch_bounds__(128) attn_chunk_scalar(ChunkScalarParams p) {
                 for (int j = 0; j < 8; j++) {
                     kx[j] = kr[j];
                     vx[j] = vr[j];
+                }
+            } else if (p.kv_dtype == 2) {
+                // q4_0: this lane's dims are the low (sub < 2) or high nibbles of 8 bytes
+                const size_t row = q4_row_offset(kvh, p.stride, pos, p.head_dim) +
+                                   (size_t)blk * kQ4BlockBytes;
+                const unsigned char *kb = (const unsigned char *)p.k + row;
+                const unsigned char *vb = (const unsigned char *)p.v + row;
+                const float dk = half_bits_to_float(*(const unsigned short *)kb);
+                const float dv = half_bits_to_float(*(const unsigned short *)vb);
+                const unsigned short *kc = (const unsigned short *)(kb + 2 + (sub & 1) * 8);
+                const unsigned short *vc = (const unsigned short *)(vb + 2 + (sub & 1) * 8);
+                const int shift = (sub >> 1) * 4;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const unsigned short a = kc[j], b = vc[j];
+                    kx[2 * j] = dk * ((float)((a >> shift) & 0xf) - 8.0f);
+                    kx[2 * j + 1] = dk * ((float)((a >> (8 + shift)) & 0xf) - 8.0f);
+                    vx[2 * j] = dv * ((float)((b >> shift) & 0xf) - 8.0f);
+                    vx[2 * j + 1] = dv * ((float)((b >> (8 + shift)) & 0xf) - 8.0f);
                 }
             } else {
                 const size_t row = q8_row_offset(kvh, p.stride, pos, p.head_dim) +

@@ -54,6 +54,7 @@
 #include <cuda.h>
 
 #include "params.cuh"
+#include "q8_pack.cuh"
 
 namespace hipml {
 
@@ -356,6 +357,21 @@ __device__ __forceinline__ void stage_fetch(const StageParams &p, const void *ca
         const float4 a = r[0], b = r[1];
         x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
         x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else if (p.kv_dtype == 2) {
+        // q4_0: dims 8*sub .. 8*sub+7 of the block are the low (sub < 2) or high nibbles of
+        // bytes 8*(sub & 1) .. +7
+        const int blk = d0 >> 5, sub = (d0 >> 3) & 3;
+        const unsigned char *b = (const unsigned char *)cache +
+                                 q4_row_offset(kvh, p.stride, key, kD) + (size_t)blk * kQ4BlockBytes;
+        const float d = half_bits_to_float(*(const unsigned short *)b);
+        const unsigned short *c = (const unsigned short *)(b + 2 + (sub & 1) * 8);
+        const int shift = (sub >> 1) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const unsigned short w = c[j];
+            x[2 * j] = d * ((float)((w >> shift) & 0xf) - 8.0f);
+            x[2 * j + 1] = d * ((float)((w >> (8 + shift)) & 0xf) - 8.0f);
+        }
     } else {
         const int blk = d0 >> 5, sub = (d0 >> 3) & 3;
         const unsigned char *b = (const unsigned char *)cache +

@@ -24,6 +24,7 @@
 //  * attn_decode_kv_scalar -- any head_dim in 32..256 step 32, one warp per
 //    (query head, split), plain f32. Kept as the A/B kernel (selector 6).
 #include "params.cuh"
+#include "q8_pack.cuh"
 
 namespace hipml {
 
@@ -41,6 +42,31 @@ __device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int
 }
 
 // ------------------------------------------------------------ scalar body
+
+// The eight dequantised values (dims 8*sub .. 8*sub+7 of block blk) of one cache row.
+__device__ __forceinline__ void load8_quant(const unsigned char *blk_ptr, int sub, bool q4,
+                                            float (&x)[8]) {
+    const float d = half_bits_to_float(*reinterpret_cast<const unsigned short *>(blk_ptr));
+    if (q4) {
+        // low (sub < 2) or high nibbles of bytes 8*(sub & 1) .. +7
+        const unsigned short *c = reinterpret_cast<const unsigned short *>(blk_ptr + 2 + (sub & 1) * 8);
+        const int shift = (sub >> 1) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const unsigned short w = c[j];
+            x[2 * j] = d * ((float)((w >> shift) & 0xf) - 8.0f);
+            x[2 * j + 1] = d * ((float)((w >> (8 + shift)) & 0xf) - 8.0f);
+        }
+    } else {
+        const unsigned short *c = reinterpret_cast<const unsigned short *>(blk_ptr + 2 + sub * 8);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const unsigned short w = c[j];
+            x[2 * j] = d * (float)(signed char)(w & 0xff);
+            x[2 * j + 1] = d * (float)(signed char)(w >> 8);
+        }
+    }
+}
 
 __global__ void __launch_bounds__(128) attn_decode_kv_scalar(DecodeParams p) {
     griddep_launch();
@@ -69,19 +95,16 @@ __global__ void __launch_bounds__(128) attn_decode_kv_scalar(DecodeParams p) {
     float m = -INFINITY, l = 0.0f;
     const size_t head_off = (size_t)slot * p.kv_slot_bytes;
     for (int pos = lo; pos < hi; pos++) {
-        const size_t row = head_off + q8_row_offset(kvh, p.stride, pos, p.head_dim) +
-                           (size_t)blk * kQ8BlockBytes;
+        const size_t row = head_off + (p.q4 ? q4_row_offset(kvh, p.stride, pos, p.head_dim) +
+                                                  (size_t)blk * kQ4BlockBytes
+                                            : q8_row_offset(kvh, p.stride, pos, p.head_dim) +
+                                                  (size_t)blk * kQ8BlockBytes);
         float part = 0.0f;
         if (live) {
-            const unsigned char *kb = p.k + row;
-            const float d = half_bits_to_float(*reinterpret_cast<const unsigned short *>(kb));
-            const unsigned short *c = reinterpret_cast<const unsigned short *>(kb + 2 + sub * 8);
+            float kx[8];
+            load8_quant(p.k + row, sub, p.q4 != 0, kx);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const unsigned short w = c[j];
-                part += qv[2 * j] * (d * (float)(signed char)(w & 0xff));
-                part += qv[2 * j + 1] * (d * (float)(signed char)(w >> 8));
-            }
+            for (int j = 0; j < 8; j++) part += qv[j] * kx[j];
         }
         const float s = warp_sum(part);
         const float m_new = fmaxf(m, s);
@@ -90,15 +113,10 @@ __global__ void __launch_bounds__(128) attn_decode_kv_scalar(DecodeParams p) {
         l = l * corr + w;
         m = m_new;
         if (live) {
-            const unsigned char *vb = p.v + row;
-            const float d = half_bits_to_float(*reinterpret_cast<const unsigned short *>(vb));
-            const unsigned short *c = reinterpret_cast<const unsigned short *>(vb + 2 + sub * 8);
+            float vx[8];
+            load8_quant(p.v + row, sub, p.q4 != 0, vx);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const unsigned short cw = c[j];
-                acc[2 * j] = acc[2 * j] * corr + w * (d * (float)(signed char)(cw & 0xff));
-                acc[2 * j + 1] = acc[2 * j + 1] * corr + w * (d * (float)(signed char)(cw >> 8));
-            }
+            for (int j = 0; j < 8; j++) acc[j] = acc[j] * corr + w * vx[j];
         }
     }
     float *pa = p.part_acc + (size_t)slot * p.acc_slot +

@@ -24,6 +24,7 @@
 // 449-518; kernel replaced: crates/hipml-kernels/kernels/attn_decode_kv_w.hip:92-285 and
 // attn_decode_kv.hip:251-374,427-484.
 #include "params.cuh"
+#include "q8_pack.cuh"
 
 namespace hipml {
 
@@ -177,6 +178,14 @@ __device__ __forceinline__ void score_block(const unsigned char *ktile, int key_
     }
 }
 
+// kQ4: the cache is q4_0 (144-byte rows). A tile's raw rows are copied into the upper part of
+// its stage and expanded in place into the q8_0 row image (scale + 32 signed codes = nibble
+// - 8) that the three phases read, through registers: every thread first loads its blocks,
+// the CTA synchronises, then the expanded blocks are written (the two regions overlap).
+constexpr int kQ4RowBytes = 8 * kQ4BlockBytes;                 // 144
+constexpr int kQ4RawOffset = kTileBytes - kTile * kQ4RowBytes; // 8192: raw tile at the stage's end
+
+template <bool kQ4>
 __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int *status) {
     extern __shared__ __align__(16) unsigned char smem[];
     griddep_launch();
@@ -218,7 +227,8 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         return;
     }
 
-    const size_t head_byte = (size_t)slot * p.kv_slot_bytes + q8_row_offset(kvh, p.stride, 0, 256);
+    constexpr int kSrcRow = kQ4 ? kQ4RowBytes : kRowBytes;   // bytes of a cache row
+    const size_t head_byte = (size_t)slot * p.kv_slot_bytes + (size_t)kvh * p.stride * kSrcRow;
     const unsigned char *kbase = p.k + head_byte;
     const unsigned char *vbase = p.v + head_byte;
 
@@ -229,13 +239,14 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     auto fetch = [&](int tile) {
         const int stage = tile % kStages;
         const int r0 = lo + tile * kTile;
-        const unsigned bytes = (unsigned)(min(kTile, hi - r0) * kRowBytes);
-        const size_t off = (size_t)r0 * kRowBytes;
+        const unsigned bytes = (unsigned)(min(kTile, hi - r0) * kSrcRow);
+        const size_t off = (size_t)r0 * kSrcRow;
+        constexpr int kDst = kQ4 ? kQ4RawOffset : 0;
         // earlier generic-proxy writes to the stage (zero fill, query staging) come first
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * bytes);
-        bulk_load(smem_u32(ktile[stage]), kbase + off, bytes, bar_full + 8 * stage);
-        bulk_load(smem_u32(vtile[stage]), vbase + off, bytes, bar_full + 8 * stage);
+        bulk_load(smem_u32(ktile[stage]) + kDst, kbase + off, bytes, bar_full + 8 * stage);
+        bulk_load(smem_u32(vtile[stage]) + kDst, vbase + off, bytes, bar_full + 8 * stage);
     };
     if (tid == 0) {
 #pragma unroll
@@ -302,7 +313,41 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
             }
         }
         const int nvalid = min(kTile, hi - (lo + tile * kTile));
-        // (no barrier here: every thread has seen the copy land for itself)
+        if constexpr (kQ4) {
+            // expand the raw q4_0 rows into the q8_0 row image: 64 rows x 8 blocks x {K, V} =
+            // 1024 blocks, four per thread; rows past the split's end are left alone
+            unsigned short raw[4][9];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int item = tid + kThreads * i, row = (item & 511) >> 3, blk = item & 7;
+                const unsigned char *src = (item < 512 ? ktile[buf] : vtile[buf]) + kQ4RawOffset +
+                                           row * kQ4RowBytes + blk * kQ4BlockBytes;
+#pragma unroll
+                for (int w = 0; w < 9; w++) raw[i][w] = reinterpret_cast<const unsigned short *>(src)[w];
+            }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int item = tid + kThreads * i, row = (item & 511) >> 3, blk = item & 7;
+                if (row >= nvalid) continue;
+                unsigned short *dst = reinterpret_cast<unsigned short *>(
+                    (item < 512 ? ktile[buf] : vtile[buf]) + row * kRowBytes + blk * kQ8BlockBytes);
+                dst[0] = raw[i][0];
+#pragma unroll
+                for (int w = 0; w < 8; w += 2) {
+                    // bytes 2w..2w+3 of the block: low nibbles are values 2w.., high nibbles 16+2w..
+                    const unsigned pair = raw[i][1 + w] | ((unsigned)raw[i][2 + w] << 16);
+                    const unsigned lo = __vsub4(pair & 0x0f0f0f0fu, 0x08080808u);
+                    const unsigned hi4 = __vsub4((pair >> 4) & 0x0f0f0f0fu, 0x08080808u);
+                    dst[1 + w] = (unsigned short)lo;
+                    dst[2 + w] = (unsigned short)(lo >> 16);
+                    dst[9 + w] = (unsigned short)hi4;
+                    dst[10 + w] = (unsigned short)(hi4 >> 16);
+                }
+            }
+            __syncthreads();
+        }
+        // (no barrier here for q8_0: every thread has seen the copy land for itself)
         if (nvalid < kTile) {
             // Rows past the split's end hold stale bytes; their V scales must read as zero.
             for (int i = tid; i < (kTile - nvalid) * (kRowBytes / 16); i += kThreads)
@@ -436,14 +481,20 @@ int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (status_word[dev] == nullptr) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kv_tc,
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kv_tc<false>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_decode_kv_tc<true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         status_word[dev] = device_status_word();
         if (status_word[dev] == nullptr) return launch_status();
     }
     dim3 grid(p.n_kv * p.splits, slots);
-    return launch_pdl(attn_decode_kv_tc, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, p,
+    if (p.q4)
+        return launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, p,
+                          status_word[dev]);
+    return launch_pdl(attn_decode_kv_tc<false>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, p,
                       status_word[dev]);
 }
 

@@ -36,6 +36,7 @@ __device__ __forceinline__ void q8_put(float x, int blk, int lane, unsigned char
 }
 
 // One (K row, V row) pair of one KV head. All threads of the CTA must call it.
+template <bool kQ4 = false>
 __device__ __forceinline__ void encode_pair(const float *ksrc, const float *vsrc,
                                             unsigned char *kdst, unsigned char *vdst,
                                             int head_dim, unsigned char *krow,
@@ -43,11 +44,16 @@ __device__ __forceinline__ void encode_pair(const float *ksrc, const float *vsrc
     const int tid = threadIdx.x;
     const int blk = tid >> 5, lane = tid & 31;
     if (tid < head_dim) {
-        q8_put(ksrc[tid], blk, lane, krow);
-        q8_put(vsrc[tid], blk, lane, vrow);
+        if constexpr (kQ4) {
+            q4_put(ksrc[tid], blk, lane, krow);
+            q4_put(vsrc[tid], blk, lane, vrow);
+        } else {
+            q8_put(ksrc[tid], blk, lane, krow);
+            q8_put(vsrc[tid], blk, lane, vrow);
+        }
     }
     __syncthreads();
-    const int row_bytes = (head_dim >> 5) * kQ8BlockBytes;
+    const int row_bytes = (head_dim >> 5) * (kQ4 ? kQ4BlockBytes : kQ8BlockBytes);
     row_store(kdst, krow, row_bytes, tid, blockDim.x);
     row_store(vdst, vrow, row_bytes, tid, blockDim.x);
     __syncthreads();
@@ -152,6 +158,95 @@ extern "C" __global__ void kv_encode_q8_b(const float *__restrict__ k, const flo
     encode_pair(k + src, v + src, kc + off, vc + off, head_dim, krow, vrow);
 }
 
+// ---- q4_0 forms of the three entries (crates/hipml-kernels/kernels/kv_encode.hip:150-238,
+// 286-320): same parameter lists and launch shapes, 18-byte blocks.
+extern "C" __global__ void kv_encode_q4(const float *__restrict__ k, const float *__restrict__ v,
+                                        unsigned char *__restrict__ kc,
+                                        unsigned char *__restrict__ vc, int head_dim, int stride,
+                                        const int *__restrict__ step) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ __align__(16) unsigned char krow[kMaxRowBytes];
+    __shared__ __align__(16) unsigned char vrow[kMaxRowBytes];
+    const int h = blockIdx.x;
+    const size_t off = q4_row_offset(h, stride, step[0], head_dim);
+    encode_pair<true>(k + (size_t)h * head_dim, v + (size_t)h * head_dim, kc + off, vc + off, head_dim,
+                      krow, vrow);
+}
+
+extern "C" __global__ void kv_encode_bulk_q4(const float *__restrict__ k,
+                                             const float *__restrict__ v,
+                                             unsigned char *__restrict__ kc,
+                                             unsigned char *__restrict__ vc, int n_kv,
+                                             int head_dim, int stride, int start, int rows,
+                                             int src0) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ __align__(16) unsigned char krow[kMaxRowBytes];
+    __shared__ __align__(16) unsigned char vrow[kMaxRowBytes];
+    const long long total = (long long)n_kv * rows;
+    for (long long idx = blockIdx.x; idx < total; idx += gridDim.x) {
+        const int r = (int)(idx / n_kv);
+        const int h = (int)(idx - (long long)r * n_kv);
+        const size_t src = ((size_t)(src0 + r) * n_kv + h) * (size_t)head_dim;
+        const size_t off = q4_row_offset(h, stride, start + r, head_dim);
+        encode_pair<true>(k + src, v + src, kc + off, vc + off, head_dim, krow, vrow);
+    }
+}
+
+extern "C" __global__ void kv_encode_q4_b(const float *__restrict__ k, const float *__restrict__ v,
+                                          unsigned char *__restrict__ kc,
+                                          unsigned char *__restrict__ vc, int n_kv, int head_dim,
+                                          int stride, const int *__restrict__ pos,
+                                          int slot_bytes) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ __align__(16) unsigned char krow[kMaxRowBytes];
+    __shared__ __align__(16) unsigned char vrow[kMaxRowBytes];
+    const int h = blockIdx.x, slot = blockIdx.y;
+    const size_t src = ((size_t)slot * n_kv + h) * (size_t)head_dim;
+    const size_t off =
+        (size_t)slot * (size_t)slot_bytes + q4_row_offset(h, stride, pos[slot * 2], head_dim);
+    encode_pair<true>(k + src, v + src, kc + off, vc + off, head_dim, krow, vrow);
+}
+
+// Throughput form of the q4_0 bulk append (head_dim 256, 16-byte-aligned sources): one warp
+// per (row, KV head), as kv_encode_bulk_q8_w.
+__global__ void __launch_bounds__(256) kv_encode_bulk_q4_w(const float *__restrict__ k,
+                                                           const float *__restrict__ v,
+                                                           unsigned char *__restrict__ kc,
+                                                           unsigned char *__restrict__ vc, int n_kv,
+                                                           int stride, int start, int rows,
+                                                           int src0) {
+    __shared__ __align__(16) unsigned char img[8][2][8 * kQ4BlockBytes];
+    griddep_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * 8 + warp;
+    if (idx >= (long long)n_kv * rows) return;
+    const int r = (int)(idx / n_kv);
+    const int h = (int)(idx - (long long)r * n_kv);
+    const size_t src = ((size_t)(src0 + r) * n_kv + h) * 256 + (size_t)lane * 8;
+    const float4 ka = __ldg(reinterpret_cast<const float4 *>(k + src));
+    const float4 kb = __ldg(reinterpret_cast<const float4 *>(k + src) + 1);
+    const float4 va = __ldg(reinterpret_cast<const float4 *>(v + src));
+    const float4 vb = __ldg(reinterpret_cast<const float4 *>(v + src) + 1);
+    q4_put8(ka, kb, lane, img[warp][0]);
+    q4_put8(va, vb, lane, img[warp][1]);
+    __syncwarp();
+    griddep_wait();
+    const size_t off = q4_row_offset(h, stride, start + r, 256);
+    row_store(kc + off, img[warp][0], 8 * kQ4BlockBytes, lane, 32);
+    row_store(vc + off, img[warp][1], 8 * kQ4BlockBytes, lane, 32);
+}
+
+int launch_kv_encode_bulk_rows_q4(cudaStream_t stream, const float *k, const float *v,
+                                  unsigned char *kc, unsigned char *vc, int n_kv, int stride,
+                                  int start, int src0, int rows) {
+    const long long pairs = (long long)n_kv * rows;
+    return launch_pdl(kv_encode_bulk_q4_w, dim3((unsigned)((pairs + 7) / 8)), dim3(256), 0, stream, 1, k, v,
+                      kc, vc, n_kv, stride, start, rows, src0);
+}
+
 // Threads [0,width) copy K, [width,2*width) copy V, into cache row step[0].
 extern "C" __global__ void kv_append_f32(float *__restrict__ k_cache, float *__restrict__ v_cache,
                                          const float *__restrict__ k, const float *__restrict__ v,
@@ -203,6 +298,9 @@ const void *lookup_kv_kernel(const char *name) {
     if (strcmp(name, "kv_encode_q8") == 0) return (const void *)kv_encode_q8;
     if (strcmp(name, "kv_encode_bulk_q8") == 0) return (const void *)kv_encode_bulk_q8;
     if (strcmp(name, "kv_encode_q8_b") == 0) return (const void *)kv_encode_q8_b;
+    if (strcmp(name, "kv_encode_q4") == 0) return (const void *)kv_encode_q4;
+    if (strcmp(name, "kv_encode_bulk_q4") == 0) return (const void *)kv_encode_bulk_q4;
+    if (strcmp(name, "kv_encode_q4_b") == 0) return (const void *)kv_encode_q4_b;
     if (strcmp(name, "kv_append_f32") == 0) return (const void *)kv_append_f32;
     if (strcmp(name, "kv_append_chunk_f32") == 0) return (const void *)kv_append_chunk_f32;
     return nullptr;

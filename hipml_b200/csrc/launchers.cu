@@ -13,9 +13,8 @@ namespace {
 constexpr float kLog2e = 1.4426950408889634f;
 
 int check_encode(int dtype, int n_kv, int head_dim, int stride) {
-    if (dtype == 1)
-        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 1 (q4_0) is not built in this library");
-    if (dtype != 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", dtype);
+    if (dtype != 0 && dtype != 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", dtype);
     if (n_kv <= 0 || stride <= 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "n_kv %d / stride %d must be positive", n_kv, stride);
     if (head_dim % 32 != 0 || head_dim < 32 || head_dim > 256)
@@ -47,8 +46,8 @@ int hipml_kv_encode(hipml_stream_t stream, const int *step, int dtype, const flo
                     int stride) {
     if (int e = check_encode(dtype, n_kv, head_dim, stride)) return e;
     void *args[] = {&k_row, &v_row, &k_cache, &v_cache, &head_dim, &stride, &step};
-    return launch_pdl_args(lookup_kv_kernel("kv_encode_q8"), dim3(n_kv), dim3(head_dim), args, 0,
-                           as_stream(stream));
+    return launch_pdl_args(lookup_kv_kernel(dtype == 1 ? "kv_encode_q4" : "kv_encode_q8"), dim3(n_kv),
+                           dim3(head_dim), args, 0, as_stream(stream));
 }
 
 int hipml_kv_encode_bulk(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
@@ -60,16 +59,17 @@ int hipml_kv_encode_bulk(hipml_stream_t stream, int dtype, const float *k_f32, c
                     start + rows, stride);
     if (rows == 0) return 0;
     if (head_dim == 256 && ((reinterpret_cast<size_t>(k_f32) | reinterpret_cast<size_t>(v_f32)) & 15) == 0)
-        return launch_kv_encode_bulk_rows(as_stream(stream), k_f32, v_f32, (unsigned char *)k_cache,
-                                          (unsigned char *)v_cache, n_kv, stride, start, src0, rows);
+        return (dtype == 1 ? launch_kv_encode_bulk_rows_q4 : launch_kv_encode_bulk_rows)(
+            as_stream(stream), k_f32, v_f32, (unsigned char *)k_cache, (unsigned char *)v_cache, n_kv,
+            stride, start, src0, rows);
     // Any other head_dim or alignment: the kernel with the reference's launch shape, one CTA
     // per (row, head) pair up to a few waves of the device; the kernel strides.
     const long long pairs = (long long)n_kv * rows;
     const unsigned grid = (unsigned)(pairs < 148LL * 64 ? pairs : 148LL * 64);
     void *args[] = {&k_f32, &v_f32, &k_cache, &v_cache, &n_kv, &head_dim, &stride, &start, &rows,
                     &src0};
-    return launch_pdl_args(lookup_kv_kernel("kv_encode_bulk_q8"), dim3(grid), dim3(head_dim), args, 0,
-                           as_stream(stream));
+    return launch_pdl_args(lookup_kv_kernel(dtype == 1 ? "kv_encode_bulk_q4" : "kv_encode_bulk_q8"),
+                           dim3(grid), dim3(head_dim), args, 0, as_stream(stream));
 }
 
 int hipml_kv_encode_rows(hipml_stream_t stream, int dtype, const float *k_f32, const float *v_f32,
@@ -79,8 +79,8 @@ int hipml_kv_encode_rows(hipml_stream_t stream, int dtype, const float *k_f32, c
     if (slots <= 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "slots %d must be positive", slots);
     void *args[] = {&k_f32, &v_f32, &k_cache, &v_cache, &n_kv, &head_dim, &stride, &pos,
                     &slot_bytes};
-    return launch_pdl_args(lookup_kv_kernel("kv_encode_q8_b"), dim3(n_kv, slots), dim3(head_dim), args,
-                           0, as_stream(stream));
+    return launch_pdl_args(lookup_kv_kernel(dtype == 1 ? "kv_encode_q4_b" : "kv_encode_q8_b"),
+                           dim3(n_kv, slots), dim3(head_dim), args, 0, as_stream(stream));
 }
 
 int hipml_kv_append_f32(hipml_stream_t stream, const int *step, float *k_cache, float *v_cache,
@@ -138,7 +138,8 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     } else if (selector == 6) {
         tensor_core = false;
     } else if (selector == 1) {
-        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 1 (q4_0) is not built in this library");
+        // q4_0: the same tile kernel, expanding the raw rows in shared memory, at head_dim 256
+        tensor_core = head_dim == 256;
     } else {
         return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", selector);
     }
@@ -162,6 +163,7 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     p.scale_log2 = scale * kLog2e;
     p.splits = splits;
     p.by_stride = 0;
+    p.q4 = selector == 1;
     p.kv_slot_bytes = p.acc_slot = p.ml_slot = p.q_slot = 0;
     if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
@@ -289,9 +291,8 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
                        int splits, int kv_slot_bytes, int acc_slot, int ml_slot, int q_slot,
                        int slots, int by_stride) {
     if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
-    if (dtype == 1)
-        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 1 (q4_0) is not built in this library");
-    if (dtype != 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", dtype);
+    if (dtype != 0 && dtype != 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", dtype);
     if (slots <= 0 || splits < 1 || stride <= 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "slots %d / splits %d / stride %d", slots, splits,
                     stride);
@@ -311,6 +312,7 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
     p.scale_log2 = scale * kLog2e;
     p.splits = splits;
     p.by_stride = by_stride;
+    p.q4 = dtype == 1;
     p.kv_slot_bytes = kv_slot_bytes;
     p.acc_slot = acc_slot;
     p.ml_slot = ml_slot;
@@ -398,9 +400,7 @@ int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
         return fail(HIPML_ERR_INVALID_ARGUMENT, "n_heads %d is not a multiple of n_kv %d", n_heads,
                     n_kv);
     const int group = n_heads / n_kv;
-    if (kv_dtype == 2)
-        return fail(HIPML_ERR_INVALID_ARGUMENT, "KV dtype 2 (q4_0) is not built in this library");
-    if (kv_dtype != 0 && kv_dtype != 1)
+    if (kv_dtype < 0 || kv_dtype > 2)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", kv_dtype);
     if (kv_dtype != 0 && !(head_dim == 256 && group <= 8))
         return fail(HIPML_ERR_INVALID_ARGUMENT, "quantized chunk attention: unsupported shape");
@@ -409,7 +409,7 @@ int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
                     head_dim);
     if (pos0 < 0 || tokens < 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "pos0 %d / tokens %d", pos0, tokens);
-    if (kv_dtype == 1 && pos0 + tokens > stride)
+    if (kv_dtype != 0 && pos0 + tokens > stride)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "position %d beyond KV cache %d", pos0 + tokens,
                     stride);
     if (mode < 0 || mode > 3) return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown mode %d", mode);
@@ -464,12 +464,12 @@ int hipml_attn_chunk_stage(hipml_stream_t stream, const void *k_cache, const voi
     if (head_dim != 256 || n_kv <= 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT,
                     "tensor-core chunk attention: only head_dim 256 with a GQA group <= 8");
-    if (kv_dtype != 0 && kv_dtype != 1)
+    if (kv_dtype < 0 || kv_dtype > 2)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", kv_dtype);
     if (key_from < 0 || key_to < key_from || key_capacity % 128 != 0 || key_to > key_capacity)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "stage rows [%d, %d) with capacity %d", key_from,
                     key_to, key_capacity);
-    if (kv_dtype == 1 && key_to > stride)
+    if (kv_dtype != 0 && key_to > stride)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "position %d beyond KV cache %d", key_to, stride);
     const size_t need = chunk_tc_workspace_bytes(n_kv, key_capacity);
     if (!workspace || workspace_bytes < need)

@@ -20,6 +20,7 @@ struct DecodeParams {
     float scale_log2;     // scale * log2(e): scores are kept in log2 units
     int splits;
     int by_stride;        // 1: runs of ceil(stride/splits) cache rows; 0: ceil(len/splits)
+    int q4;               // 1: the cache is q4_0 (18-byte blocks), 0: q8_0
     long long kv_slot_bytes, acc_slot, ml_slot, q_slot;
 };
 // Launches the split pass (the caller launches the reduce).
@@ -68,6 +69,10 @@ int launch_chunk_combine(cudaStream_t stream, const float *part_acc, const float
 int launch_kv_encode_bulk_rows(cudaStream_t stream, const float *k, const float *v,
                                unsigned char *kc, unsigned char *vc, int n_kv, int stride,
                                int start, int src0, int rows);
+
+int launch_kv_encode_bulk_rows_q4(cudaStream_t stream, const float *k, const float *v,
+                                  unsigned char *kc, unsigned char *vc, int n_kv, int stride,
+                                  int start, int src0, int rows);
 
 // Tensor-core chunk attention (attn_chunk_tc.cu).
 size_t chunk_tc_workspace_bytes(int n_kv, int n_keys);

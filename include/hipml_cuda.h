@@ -127,8 +127,8 @@ int hipml_module_launch_kernel(hipml_function_t function, unsigned grid_x, unsig
                                void **kernel_params, void **extra);       /* ffi.rs:91-104 */
 
 /* --------------------------------------------------------------- B. launchers
- * `dtype` for encode/decode is KvDtype::id(): 0 = q8_0 (1 = q4_0 is rejected:
- * not built). `step` is the device-resident i32[8] step buffer
+ * `dtype` for encode/decode is KvDtype::id(): 0 = q8_0 (34-byte blocks), 1 = q4_0
+ * (18-byte blocks, crates/hipml-core/src/kv.rs:36-90). `step` is the device-resident i32[8] step buffer
  * [pos, seq, token, 0, p0..p3] (crates/hipml-kernels/src/launch.rs:105-154):
  * step[0] = append position, step[1] = live length. */
 
@@ -344,7 +344,7 @@ size_t hipml_attn_chunk_workspace_bytes(int n_kv, int head_dim, int pos0, int to
  * causal GQA attention of `tokens` query rows at positions pos0..pos0+tokens-1 over cache rows
  * [0, pos0+tokens); row t sees cache rows 0..pos0+t. q and out are f32 [tokens][n_heads*head_dim].
  * kv_dtype: 0 = f32 position-major cache [n_ctx][n_kv*head_dim] (stride unused), 1 = q8_0
- * head-major cache with `stride` rows per KV head (2 = q4_0 is rejected: not built).
+ * head-major cache with `stride` rows per KV head, 2 = q4_0 in the same head-major layout.
  * scale is 1/sqrt(head_dim), computed here as the reference does.
  * splits < 2: one pass. splits >= 2: the key axis of every query tile is cut into `splits`
  * slices, partials go to part_acc f32 [splits][qslots][n_heads][head_dim] and part_ml f32

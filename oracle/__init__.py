@@ -18,6 +18,7 @@ _SO = os.path.join(_HERE, "_build", "libhipml_oracle.so")
 
 BLOCK = 32
 Q8_BLOCK_BYTES = 34
+Q4_BLOCK_BYTES = 18
 
 
 def build(force: bool = False) -> str:
@@ -69,6 +70,11 @@ def lib() -> C.CDLL:
         L.hipml_oracle_kv_append_f32.argtypes = [f32p, f32p, f32p, f32p, C.c_size_t, C.c_size_t]
         L.hipml_oracle_compare.argtypes = [f32p, f32p, C.c_size_t, f32p, f32p]
         i4 = C.POINTER(C.c_int)
+        L.hipml_oracle_quantize_q4.argtypes = [f32p, C.c_size_t, u8p]
+        L.hipml_oracle_dequantize_q4.argtypes = [u8p, C.c_size_t, f32p]
+        L.hipml_oracle_synthetic_blocks_q4.argtypes = [C.c_size_t, C.c_uint64, u8p]
+        L.hipml_oracle_attn_decode_kv_strided.argtypes = [f32p, u8p, u8p, C.c_int, C.c_int, C.c_int,
+                                                          C.c_int, C.c_int, C.c_int, C.c_float, f32p]
         L.hipml_oracle_head_rmsnorm_f32.argtypes = [f32p, f32p, C.c_int, C.c_int, C.c_float, f32p]
         L.hipml_oracle_rope_multi_f32.argtypes = [f32p, C.c_int, C.c_int, C.c_int, i4, i4, C.c_float,
                                                   f32p]
@@ -274,3 +280,41 @@ def attn_front(qg, k, q_norm, k_norm, n_heads, n_kv, head_dim, n_rot, sections, 
     k = rope_multi_f32(head_rmsnorm_f32(k, k_norm, n_kv, head_dim, eps), n_kv, head_dim, n_rot,
                        sections, pos, theta_base)
     return q, gate, k
+
+
+# ---- q4_0 (kv.rs:201-218, 238-290, 306-320) -------------------------------------------------
+
+def quantize_q4(values) -> np.ndarray:
+    v = _f32(values).ravel()
+    assert v.size % BLOCK == 0
+    out = np.empty(v.size // BLOCK * Q4_BLOCK_BYTES, dtype=np.uint8)
+    lib().hipml_oracle_quantize_q4(_p(v, C.c_float), v.size, _p(out, C.c_uint8))
+    return out
+
+
+def dequantize_q4(data) -> np.ndarray:
+    b = _u8(data).ravel()
+    assert b.size % Q4_BLOCK_BYTES == 0
+    out = np.empty(b.size // Q4_BLOCK_BYTES * BLOCK, dtype=np.float32)
+    lib().hipml_oracle_dequantize_q4(_p(b, C.c_uint8), b.size, _p(out, C.c_float))
+    return out
+
+
+def synthetic_blocks_q4(n_blocks: int, seed: int) -> np.ndarray:
+    out = np.empty(n_blocks * Q4_BLOCK_BYTES, dtype=np.uint8)
+    lib().hipml_oracle_synthetic_blocks_q4(n_blocks, C.c_uint64(seed), _p(out, C.c_uint8))
+    return out
+
+
+def attn_decode_kv(q, k_bytes, v_bytes, dtype, n_heads, n_kv, head_dim, seq, scale,
+                   stride: int | None = None) -> np.ndarray:
+    """ops::attn_decode_kv over either quantised cache (dtype 0 = q8_0, 1 = q4_0)."""
+    q, k, v = _f32(q).ravel(), _u8(k_bytes).ravel(), _u8(v_bytes).ravel()
+    stride = seq if stride is None else stride
+    row = head_dim // BLOCK * (Q4_BLOCK_BYTES if dtype == 1 else Q8_BLOCK_BYTES)
+    assert k.size >= n_kv * stride * row and v.size >= n_kv * stride * row
+    out = np.empty(n_heads * head_dim, dtype=np.float32)
+    lib().hipml_oracle_attn_decode_kv_strided(_p(q, C.c_float), _p(k, C.c_uint8), _p(v, C.c_uint8),
+                                              dtype, n_heads, n_kv, head_dim, seq, stride,
+                                              C.c_float(scale), _p(out, C.c_float))
+    return out

@@ -246,11 +246,15 @@ void hipml_oracle_attn_chunk_f32(const float *q, const float *k_cache, const flo
 /* ------------------------------------------------- decode over a q8_0 cache
  * crates/hipml-core/src/ops.rs:449-518. */
 
-void hipml_oracle_attn_decode_kv_q8_strided(const float *q, const uint8_t *k, const uint8_t *v,
-                                            int n_heads, int n_kv, int head_dim, int seq,
-                                            int stride, float scale, float *out) {
+static void block_f32_q4(const uint8_t *src, float *out);
+
+/* dtype 0 = q8_0 (34-byte blocks), 1 = q4_0 (18-byte blocks). */
+void hipml_oracle_attn_decode_kv_strided(const float *q, const uint8_t *k, const uint8_t *v, int dtype,
+                                         int n_heads, int n_kv, int head_dim, int seq, int stride,
+                                         float scale, float *out) {
     const int nb = head_dim / HIPML_KV_BLOCK;
-    const size_t row = (size_t)nb * HIPML_Q8_BLOCK_BYTES;
+    const size_t bb = dtype == 1 ? HIPML_Q4_BLOCK_BYTES : HIPML_Q8_BLOCK_BYTES;
+    const size_t row = (size_t)nb * bb;
     const int group = n_heads / n_kv;
     float *acc = (float *)malloc(sizeof(float) * (size_t)head_dim);
     float blk[HIPML_KV_BLOCK];
@@ -265,7 +269,8 @@ void hipml_oracle_attn_decode_kv_q8_strided(const float *q, const uint8_t *k, co
             const uint8_t *kr = k + base + (size_t)pos * row;
             float dot = 0.0f;
             for (int c = 0; c < nb; c++) {
-                block_f32_q8(kr + (size_t)c * HIPML_Q8_BLOCK_BYTES, blk);
+                if (dtype == 1) block_f32_q4(kr + (size_t)c * bb, blk);
+                else block_f32_q8(kr + (size_t)c * bb, blk);
                 const float *qc = qh + c * HIPML_KV_BLOCK;
                 for (int j = 0; j < HIPML_KV_BLOCK; j++) dot += qc[j] * blk[j];
             }
@@ -277,7 +282,8 @@ void hipml_oracle_attn_decode_kv_q8_strided(const float *q, const uint8_t *k, co
             m = m_new;
             const uint8_t *vr = v + base + (size_t)pos * row;
             for (int c = 0; c < nb; c++) {
-                block_f32_q8(vr + (size_t)c * HIPML_Q8_BLOCK_BYTES, blk);
+                if (dtype == 1) block_f32_q4(vr + (size_t)c * bb, blk);
+                else block_f32_q8(vr + (size_t)c * bb, blk);
                 float *a = acc + c * HIPML_KV_BLOCK;
                 for (int j = 0; j < HIPML_KV_BLOCK; j++) a[j] = a[j] * corr + p * blk[j];
             }
@@ -286,6 +292,12 @@ void hipml_oracle_attn_decode_kv_q8_strided(const float *q, const uint8_t *k, co
         for (int d = 0; d < head_dim; d++) out[(size_t)h * head_dim + d] = acc[d] * inv;
     }
     free(acc);
+}
+
+void hipml_oracle_attn_decode_kv_q8_strided(const float *q, const uint8_t *k, const uint8_t *v,
+                                            int n_heads, int n_kv, int head_dim, int seq,
+                                            int stride, float scale, float *out) {
+    hipml_oracle_attn_decode_kv_strided(q, k, v, 0, n_heads, n_kv, head_dim, seq, stride, scale, out);
 }
 
 void hipml_oracle_attn_decode_kv_q8(const float *q, const uint8_t *k, const uint8_t *v,
@@ -422,4 +434,61 @@ void hipml_oracle_qg_split_f32(const float *qg, int n_heads, int head_dim, float
 /* crates/hipml-core/src/ops.rs:354-360: y = q * (1 / (1 + exp(-gate))). */
 void hipml_oracle_q_gate_f32(const float *q, const float *gate, size_t n, float *out) {
     for (size_t i = 0; i < n; i++) out[i] = q[i] * (1.0f / (1.0f + expf(-gate[i])));
+}
+
+/* ---- q4_0 (crates/hipml-core/src/kv.rs:201-218, 238-290, 306-320) ---------------------------
+ * Block = f16 scale + 16 bytes; byte j holds value j in its low nibble and value j + 16 in its
+ * high nibble; value = d * (nibble - 8). ggml's convention: the scale takes the sign of the
+ * element of largest magnitude (the first one on ties), d = -vmax / 8, so that element lands
+ * exactly on nibble 0 or 15. */
+
+void hipml_oracle_quantize_block_q4(const float *xs, uint8_t *out) {
+    float vmax = 0.0f;
+    for (int j = 0; j < HIPML_KV_BLOCK; j++)
+        if (fabsf(xs[j]) > fabsf(vmax)) vmax = xs[j];
+    float d = -vmax / 8.0f;
+    float id = d != 0.0f ? 1.0f / d : 0.0f;
+    uint16_t hs = hipml_oracle_f32_to_f16(d);
+    out[0] = (uint8_t)(hs & 0xff);
+    out[1] = (uint8_t)(hs >> 8);
+    uint8_t q[HIPML_KV_BLOCK];
+    for (int j = 0; j < HIPML_KV_BLOCK; j++) {
+        float r = roundf(xs[j] * id) + 8.0f; /* f32::round: half away from zero */
+        if (r < 0.0f) r = 0.0f;
+        if (r > 15.0f) r = 15.0f;
+        q[j] = (r != r) ? 0 : (uint8_t)r;    /* `as u8` of a NaN is 0 in Rust */
+    }
+    for (int j = 0; j < HIPML_KV_BLOCK / 2; j++)
+        out[2 + j] = (uint8_t)(q[j] | (q[j + HIPML_KV_BLOCK / 2] << 4));
+}
+
+void hipml_oracle_quantize_q4(const float *values, size_t n, uint8_t *out) {
+    for (size_t b = 0; b < n / HIPML_KV_BLOCK; b++)
+        hipml_oracle_quantize_block_q4(values + b * HIPML_KV_BLOCK, out + b * HIPML_Q4_BLOCK_BYTES);
+}
+
+static void block_f32_q4(const uint8_t *src, float *out) {
+    const float d = hipml_oracle_f16_to_f32((uint16_t)(src[0] | (src[1] << 8)));
+    for (int j = 0; j < HIPML_KV_BLOCK / 2; j++) {
+        const uint8_t byte = src[2 + j];
+        out[j] = d * ((float)(byte & 0x0f) - 8.0f);
+        out[j + HIPML_KV_BLOCK / 2] = d * ((float)(byte >> 4) - 8.0f);
+    }
+}
+
+void hipml_oracle_dequantize_q4(const uint8_t *bytes, size_t n_bytes, float *out) {
+    for (size_t b = 0; b < n_bytes / HIPML_Q4_BLOCK_BYTES; b++)
+        block_f32_q4(bytes + b * HIPML_Q4_BLOCK_BYTES, out + b * HIPML_KV_BLOCK);
+}
+
+void hipml_oracle_synthetic_blocks_q4(size_t n_blocks, uint64_t seed, uint8_t *out) {
+    uint64_t s = seed | 1;
+    for (size_t b = 0; b < n_blocks; b++) {
+        uint8_t *blk = out + b * HIPML_Q4_BLOCK_BYTES;
+        float d = 0.01f + (float)(xorshift64star(&s) % 1000) * 0.00004f;
+        uint16_t hs = hipml_oracle_f32_to_f16(d);
+        blk[0] = (uint8_t)(hs & 0xff);
+        blk[1] = (uint8_t)(hs >> 8);
+        for (int j = 0; j < HIPML_Q4_BLOCK_BYTES - 2; j++) blk[2 + j] = (uint8_t)(xorshift64star(&s) >> 24);
+    }
 }

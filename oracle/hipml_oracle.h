@@ -29,6 +29,7 @@ extern "C" {
 
 #define HIPML_KV_BLOCK 32
 #define HIPML_Q8_BLOCK_BYTES 34
+#define HIPML_Q4_BLOCK_BYTES 18
 
 /* crates/hipml-core/src/kv.rs:94-116 */
 float hipml_oracle_f16_to_f32(uint16_t h);
@@ -91,6 +92,16 @@ void hipml_oracle_kv_append_f32(float *k_cache, float *v_cache, const float *k, 
 /* crates/hipml-core/src/parity.rs:58-80: max_abs and max_rel (denominator max(|e|,1e-12)). */
 void hipml_oracle_compare(const float *expected, const float *actual, size_t n, float *max_abs,
                           float *max_rel);
+
+/* q4_0 (crates/hipml-core/src/kv.rs:201-218, 238-290, 306-320) and the decode over either
+ * quantised format (ops.rs:449-518; dtype 0 = q8_0, 1 = q4_0). */
+void hipml_oracle_quantize_block_q4(const float *xs, uint8_t *out);
+void hipml_oracle_quantize_q4(const float *values, size_t n, uint8_t *out);
+void hipml_oracle_dequantize_q4(const uint8_t *bytes, size_t n_bytes, float *out);
+void hipml_oracle_synthetic_blocks_q4(size_t n_blocks, uint64_t seed, uint8_t *out);
+void hipml_oracle_attn_decode_kv_strided(const float *q, const uint8_t *k, const uint8_t *v, int dtype,
+                                         int n_heads, int n_kv, int head_dim, int seq, int stride,
+                                         float scale, float *out);
 
 /* Attention front end and tail (crates/hipml-core/src/ops.rs:181-187, 195-224, 260-360). */
 void hipml_oracle_rmsnorm_f32(const float *x, const float *w, int n, float eps, float *out);

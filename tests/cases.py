@@ -29,9 +29,10 @@ class KvCase:
     splits: int
     scale: float
     seed: int
+    dtype: int = 0      # KvDtype::id(): 0 = q8_0, 1 = q4_0
 
 
-# parity_kv.rs:68-215, q8 rows only (q4 is not built)
+# parity_kv.rs:68-215, the q8 rows
 KV_CASES = [
     KvCase("attn_decode_kv_q8_hd256_s1", 6, 1, 256, 1, 1, 0.0625, 0x9E00_0001),
     KvCase("attn_decode_kv_q8_hd256_s37", 6, 1, 256, 37, 1, 0.0625, 0x9E00_0002),
@@ -41,8 +42,19 @@ KV_CASES = [
     KvCase("attn_decode_kv_q8_hd64_s1000", 8, 2, 64, 1000, 7, 0.125, 0x9E00_000A),
 ]
 
+# parity_kv.rs:68-215, the q4 rows
+KV_CASES_Q4 = [
+    KvCase("attn_decode_kv_q4_hd256_s1", 6, 1, 256, 1, 1, 0.0625, 0x9E00_0005, 1),
+    KvCase("attn_decode_kv_q4_hd256_s37", 6, 1, 256, 37, 1, 0.0625, 0x9E00_0006, 1),
+    KvCase("attn_decode_kv_q4_hd256_s1000", 6, 1, 256, 1000, 7, 0.0625, 0x9E00_0007, 1),
+    KvCase("attn_decode_kv_q4_hd256_s4096", 6, 1, 256, 4096, 16, 0.0625, 0x9E00_0008, 1),
+    KvCase("attn_decode_kv_q4_hd64_s37", 8, 2, 64, 37, 1, 0.125, 0x9E00_000B, 1),
+    KvCase("attn_decode_kv_q4_hd64_s1000", 8, 2, 64, 1000, 7, 0.125, 0x9E00_000C, 1),
+]
+
 # parity_kv.rs:219-246
 DEEP_CASE = KvCase("attn_decode_kv_q8_hd256_s100000", 1, 1, 256, 100000, 256, 0.0625, 0x9E00_1001)
+DEEP_CASE_Q4 = KvCase("attn_decode_kv_q4_hd256_s100000", 1, 1, 256, 100000, 64, 0.0625, 0x9E00_1002, 1)
 
 
 def kv_case_inputs(c: KvCase):
@@ -51,11 +63,12 @@ def kv_case_inputs(c: KvCase):
     q = rng.normals(c.heads * c.dim)
     kf = rng.normals(c.n_kv * c.seq * c.dim, 0.3)
     vf = rng.normals(c.n_kv * c.seq * c.dim)
-    return q, O.quantize_q8(kf), O.quantize_q8(vf)
+    quantize = O.quantize_q4 if c.dtype == 1 else O.quantize_q8
+    return q, quantize(kf), quantize(vf)
 
 
 def kv_case_expected(c: KvCase, q, kb, vb):
-    return O.attn_decode_kv_q8(q, kb, vb, c.heads, c.n_kv, c.dim, c.seq, c.scale)
+    return O.attn_decode_kv(q, kb, vb, c.dtype, c.heads, c.n_kv, c.dim, c.seq, c.scale)
 
 
 # parity.rs:364-378
@@ -116,19 +129,21 @@ def chunk_case_f32(heads=24, n_kv=4, hd=256, tok=37, pos0=29, seed=0xC4A0_1234_5
 
 
 def chunk_case_q8(heads=24, n_kv=4, hd=256, tok=37, pos0=29, pad=0,
-                  seed=0xC4A0_9876_5432) -> ChunkCase:
+                  seed=0xC4A0_9876_5432, q4=False) -> ChunkCase:
     """attn_chunk_parity.rs:124-207: the cache has stride = pos0 + tok + pad rows per head and
-    is drawn and quantised over the whole stride; the oracle reads the dequantised values."""
+    is drawn and quantised over the whole stride; the oracle reads the dequantised values.
+    `q4` quantises the same draws as q4_0 instead."""
+    quantize, dequantize = (O.quantize_q4, O.dequantize_q4) if q4 else (O.quantize_q8, O.dequantize_q8)
     stride = pos0 + tok + pad
     width, nhd = n_kv * hd, heads * hd
     rng = O.Rng(seed)
     q = rng.normals(tok * nhd).reshape(tok, nhd)
     kc = rng.normals(stride * width).reshape(stride, width)
     vc = rng.normals(stride * width).reshape(stride, width)
-    kb = O.quantize_q8(pack_head_major(kc, n_kv, stride, hd))
-    vb = O.quantize_q8(pack_head_major(vc, n_kv, stride, hd))
-    kq = unpack_head_major(O.dequantize_q8(kb), n_kv, stride, hd)
-    vq = unpack_head_major(O.dequantize_q8(vb), n_kv, stride, hd)
+    kb = quantize(pack_head_major(kc, n_kv, stride, hd))
+    vb = quantize(pack_head_major(vc, n_kv, stride, hd))
+    kq = unpack_head_major(dequantize(kb), n_kv, stride, hd)
+    vq = unpack_head_major(dequantize(vb), n_kv, stride, hd)
     return ChunkCase(q, kq, vq, kb, vb, heads, n_kv, hd, pos0, tok, stride)
 
 

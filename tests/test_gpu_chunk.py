@@ -167,7 +167,7 @@ def test_chunk_argument_errors():
         api.attn_chunk(z, c, c, z, 8, 2, 64, 0, 4, 1, 66, mode=2)
     with pytest.raises(_lib.HipmlError, match="workspace"):
         api.attn_chunk(z, c, c, z, 24, 4, 256, 29, 37, 1, 66, mode=0, workspace=None)
-    with pytest.raises(_lib.HipmlError, match="q4_0"):
-        api.attn_chunk(z, c, c, z, 24, 4, 256, 29, 37, 2, 66, mode=2)
+    with pytest.raises(_lib.HipmlError, match="unknown KV dtype 3"):
+        api.attn_chunk(z, c, c, z, 24, 4, 256, 29, 37, 3, 66, mode=2)
     with pytest.raises(_lib.HipmlError, match="beyond KV cache"):
         api.attn_chunk(z, c, c, z, 24, 4, 256, 40, 37, 1, 66, mode=2)

@@ -198,7 +198,7 @@ def test_argument_errors_use_the_reference_messages():
     c = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     with pytest.raises(_lib.HipmlError, match="unknown KV dtype 7"):
         api.kv_encode(_step(0), z, z, c, c, 4, 64, 8, dtype=7)
-    with pytest.raises(_lib.HipmlError, match="q4_0"):
-        api.kv_encode(_step(0), z, z, c, c, 4, 64, 8, dtype=1)
+    with pytest.raises(_lib.HipmlError, match="unknown KV dtype -1"):
+        api.kv_encode(_step(0), z, z, c, c, 4, 64, 8, dtype=-1)
     with pytest.raises(_lib.HipmlError, match="head_dim 48"):
         api.kv_encode(_step(0), z, z, c, c, 4, 48, 8)
