@@ -8,9 +8,16 @@
 // consumed, so two tiles (70 KB per CTA, two CTAs per SM) are always in flight while the
 // third is being computed on. Both contractions run on the tensor cores
 // (mma.sync m16n8k16, f16 operands, f32 accumulate) with operands built in registers:
-//   * int8 codes are exact in f16 (0x6400 | (code ^ 0x80) is 1152 + code);
-//   * the query and the softmax weights are split into f16 high + low parts stacked along
-//     M (rows 0..7 high, rows 8..15 low of the same head), so one MMA carries both;
+//   * int8 codes are exact in f16. Scores: one byte permute per two codes -- the byte
+//     code + 128 under a zero high byte is the f16 subnormal (code + 128) * 2^-24; the offset
+//     leaves through the accumulators, which start at -2^-17 * (sum of the query over the
+//     block), and the factor 2^-24 when the scores are read. Values: 0x6400 | (code + 128) is
+//     1152 + code, minus 1152 (the weights are all positive, so an offset left in the
+//     accumulators would cost precision there);
+//   * scores: the codes are the A operand (16 keys x 16 dims), the query the B operand as an
+//     f16 high and a low part in two chained MMAs, so the block scale multiplies whole
+//     accumulator rows; values: the softmax weights are split into f16 high + low parts
+//     stacked along M (rows 0..7 high, rows 8..15 low of the same head);
 //   * the per-block f16 scales are applied in f32: on the K side to the 32-wide partial dot
 //     products, on the V side folded into the weight operand (weight * scale kept as an
 //     exact f16 high + low pair).
@@ -34,7 +41,7 @@ constexpr int kTile = 64;                        // keys per shared-memory tile
 constexpr int kRowBytes = 8 * kQ8BlockBytes;     // 272
 constexpr int kTileBytes = kTile * kRowBytes;    // 17408
 constexpr int kThreads = 256;
-constexpr int kSsStride = 72;                    // padded row of the score tile (floats)
+constexpr int kSsStride = 68;                    // padded row of the score tile (floats)
 constexpr int kPStride = 72;                     // padded row of the weight tile (halves)
 constexpr float kPScale = 1024.0f;               // keeps weight*scale in f16's normal range
 
@@ -127,13 +134,24 @@ __device__ __forceinline__ unsigned v_word(const unsigned *row, int blk, int j) 
     return __byte_perm(row[17 * m + j], row[17 * m + j + 1], 0x5432);
 }
 
-// Bytes lo/hi of `biased` (code ^ 0x80) as an exact half2: 0x64xx is 1024 + xx, minus 1152.
+// Two bytes of `biased` (code ^ 0x80 = code + 128) as a half2 of f16 subnormals: 0x00xx is
+// xx * 2^-24 exactly, so one permute converts two codes. The offset of 128 is taken out
+// again through the accumulators (see score_block and the values phase), the factor 2^-24
+// when the scores / partials are written.
 __device__ __forceinline__ unsigned codes_to_half2(unsigned biased, unsigned selector) {
+    return __byte_perm(biased, 0u, selector);
+}
+// Value side: bytes of `biased` as an exact half2 through 0x64xx = 1024 + xx, minus 1152. The
+// weights are all positive there, so an offset carried in the accumulators would cost
+// several bits (measured: 4e-5 relative on a flat 256-key run); this form is exact.
+__device__ __forceinline__ unsigned codes_to_half2_exact(unsigned biased, unsigned selector) {
     const unsigned h = __byte_perm(biased, 0x64646464u, selector);
     const __half2 r =
         __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half(0x6480)));
     return *reinterpret_cast<const unsigned *>(&r);
 }
+constexpr float kCodeUnit = 16777216.0f;          // 2^24
+constexpr float kCodeBias = 128.0f / 16777216.0f; // the offset in the operand's units: 2^-17
 
 __device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
     const __half2 r = __halves2half2(lo, hi);
@@ -150,32 +168,58 @@ __device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
 __device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int &lo,
                                             int &hi) {
     const int len = p.len[slot * p.len_stride + p.len_offset];
+    if (!p.by_stride && p.run_cap > 0) {
+        const int tiles = (len + kTile - 1) / kTile;
+        const int runs = min(min(p.splits, tiles), p.run_cap);
+        if (split >= runs) {
+            lo = hi = len;
+            return;
+        }
+        lo = (int)((long long)split * tiles / runs) * kTile;
+        hi = min((int)((long long)(split + 1) * tiles / runs) * kTile, len);
+        return;
+    }
     const int span = p.by_stride ? p.stride : len;
     const int per = ((span + p.splits - 1) / p.splits + kTile - 1) / kTile * kTile;
     lo = min(split * per, len);
     hi = min(lo + per, len);
 }
 
-// Scores of one block for this warp's 16 keys (two n-tiles), added into s.
+// Scores of one block for this warp's 16 keys, added into s. The codes are the A operand
+// (rows = keys g and g + 8 of the 16, contraction slots in k_word's order), the query the B
+// operand (columns = heads), so the block scale is one factor per accumulator row:
+// s[0], s[1] = key g, heads 2t and 2t + 1; s[2], s[3] = key g + 8. The accumulators start at
+// -2^-17 * (sum of the head's query over the block), which removes the codes' offset of 128.
 template <int BLK>
 __device__ __forceinline__ void score_block(const unsigned char *ktile, int key_base, int g, int t,
-                                            const unsigned (&qa0)[4], const unsigned (&qa1)[4],
-                                            float (&s)[2][2]) {
-#pragma unroll
-    for (int nt = 0; nt < 2; nt++) {
-        const unsigned *row =
-            reinterpret_cast<const unsigned *>(ktile + (key_base + nt * 8 + g) * kRowBytes);
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        const unsigned w0 = k_word<BLK, 0>(row, t) ^ 0x80808080u;
-        mma_16816(c, qa0, codes_to_half2(w0, 0x4140), codes_to_half2(w0, 0x4342));
-        const unsigned w1 = k_word<BLK, 1>(row, t) ^ 0x80808080u;
-        mma_16816(c, qa1, codes_to_half2(w1, 0x4140), codes_to_half2(w1, 0x4342));
-        const unsigned char *r0 = ktile + (key_base + nt * 8 + 2 * t) * kRowBytes + BLK * kQ8BlockBytes;
-        const float d0 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(r0));
-        const float d1 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(r0 + kRowBytes));
-        s[nt][0] += d0 * (c[0] + c[2]);
-        s[nt][1] += d1 * (c[1] + c[3]);
+                                            const unsigned (&qb0)[4], const unsigned (&qb1)[4],
+                                            const float (&bias)[2], float (&s)[4]) {
+    const unsigned *row0 = reinterpret_cast<const unsigned *>(ktile + (key_base + g) * kRowBytes);
+    const unsigned *row1 = row0 + 8 * (kRowBytes / 4);
+    float c[4] = {bias[0], bias[1], bias[0], bias[1]};
+    {
+        const unsigned w0 = k_word<BLK, 0>(row0, t) ^ 0x80808080u;
+        const unsigned w1 = k_word<BLK, 0>(row1, t) ^ 0x80808080u;
+        const unsigned a[4] = {codes_to_half2(w0, 0x4140), codes_to_half2(w1, 0x4140),
+                               codes_to_half2(w0, 0x4342), codes_to_half2(w1, 0x4342)};
+        mma_16816(c, a, qb0[0], qb0[1]);
+        mma_16816(c, a, qb0[2], qb0[3]);
     }
+    {
+        const unsigned w0 = k_word<BLK, 1>(row0, t) ^ 0x80808080u;
+        const unsigned w1 = k_word<BLK, 1>(row1, t) ^ 0x80808080u;
+        const unsigned a[4] = {codes_to_half2(w0, 0x4140), codes_to_half2(w1, 0x4140),
+                               codes_to_half2(w0, 0x4342), codes_to_half2(w1, 0x4342)};
+        mma_16816(c, a, qb1[0], qb1[1]);
+        mma_16816(c, a, qb1[2], qb1[3]);
+    }
+    const unsigned char *sc = ktile + (key_base + g) * kRowBytes + BLK * kQ8BlockBytes;
+    const float d0 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(sc));
+    const float d1 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(sc + 8 * kRowBytes));
+    s[0] += d0 * c[0];
+    s[1] += d0 * c[1];
+    s[2] += d1 * c[2];
+    s[3] += d1 * c[3];
 }
 
 // kQ4: the cache is q4_0 (144-byte rows). A tile's raw rows are copied into the upper part of
@@ -189,17 +233,14 @@ template <bool kQ4>
 __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int *status) {
     extern __shared__ __align__(16) unsigned char smem[];
     griddep_launch();
-    unsigned char *ktile[kStages], *vtile[kStages];
-#pragma unroll
-    for (int s = 0; s < kStages; s++) {
-        ktile[s] = smem + 2 * s * kTileBytes;
-        vtile[s] = ktile[s] + kTileBytes;
-    }
-    float *qs = reinterpret_cast<float *>(ktile[2]);                 // set-up only
+    auto ktile_at = [&](int stage) { return smem + 2 * stage * kTileBytes; };
+    auto vtile_at = [&](int stage) { return smem + (2 * stage + 1) * kTileBytes; };
+    float *qs = reinterpret_cast<float *>(ktile_at(2));              // set-up only
     float *ss = reinterpret_cast<float *>(smem + kOffSs);            // [2][8][kSsStride]
     __half *ph = reinterpret_cast<__half *>(smem + kOffPh);          // [8][kPStride]
     __half *pl = reinterpret_cast<__half *>(smem + kOffPl);
     float *corr_s = reinterpret_cast<float *>(smem + kOffCorr);      // [8]
+    float *qsum_s = ss;                                              // [8][8], set-up only
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -245,8 +286,8 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         // earlier generic-proxy writes to the stage (zero fill, query staging) come first
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * bytes);
-        bulk_load(smem_u32(ktile[stage]) + kDst, kbase + off, bytes, bar_full + 8 * stage);
-        bulk_load(smem_u32(vtile[stage]) + kDst, vbase + off, bytes, bar_full + 8 * stage);
+        bulk_load(smem_u32(ktile_at(stage)) + kDst, kbase + off, bytes, bar_full + 8 * stage);
+        bulk_load(smem_u32(vtile_at(stage)) + kDst, vbase + off, bytes, bar_full + 8 * stage);
     };
     if (tid == 0) {
 #pragma unroll
@@ -267,9 +308,11 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         qs[i] = (i >> 8) < group ? q[i] * p.scale_log2 : 0.0f;
     __syncthreads();
 
-    // A fragments of the query for this warp's four blocks: rows 0..7 carry the f16 high
-    // part of head g, rows 8..15 the low part; contraction slots follow k_word's order.
-    unsigned qa[8][4];
+    // B fragments of the query for this warp's four blocks and both 16-slot steps of each:
+    // column g = head g, as an f16 high and low part ({hi b0, hi b1, lo b0, lo b1}); the
+    // contraction slots follow k_word's order (slots 2t, 2t+1 = bytes 0, 1 of word t, slots
+    // 2t+8, 2t+9 = bytes 2, 3).
+    unsigned qb[8][4];
 #pragma unroll
     for (int ks = 0; ks < 8; ks++) {
         const int blk = dh * 4 + (ks >> 1), j = (ks & 1) * 4 + t;
@@ -280,10 +323,29 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
             xh[i] = __float2half_rn(x);
             xl[i] = __float2half_rn(x - __half2float(xh[i]));
         }
-        qa[ks][0] = pack_half2(xh[0], xh[1]);
-        qa[ks][1] = pack_half2(xl[0], xl[1]);
-        qa[ks][2] = pack_half2(xh[2], xh[3]);
-        qa[ks][3] = pack_half2(xl[2], xl[3]);
+        qb[ks][0] = pack_half2(xh[0], xh[1]);
+        qb[ks][1] = pack_half2(xh[2], xh[3]);
+        qb[ks][2] = pack_half2(xl[0], xl[1]);
+        qb[ks][3] = pack_half2(xl[2], xl[3]);
+    }
+    // Per (head, block) sums of the query as the tensor cores see it (high + low part), times
+    // -2^-17: the starting value of the score accumulators. 64 threads sum one pair each.
+    if (tid < 64) {
+        const int h = tid >> 3, blk = tid & 7;
+        float sum = 0.0f;
+        for (int d = 0; d < 32; d++) {
+            const float x = qs[h * 256 + blk * 32 + d];
+            const float xh = __half2float(__float2half_rn(x));
+            sum += xh + __half2float(__float2half_rn(x - xh));
+        }
+        qsum_s[tid] = -kCodeBias * sum;
+    }
+    __syncthreads();
+    float qbias[4][2];
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+        qbias[b][0] = qsum_s[(2 * t) * 8 + dh * 4 + b];
+        qbias[b][1] = qsum_s[(2 * t + 1) * 8 + dh * 4 + b];
     }
     // qs aliases stage 2: every warp is done with it (and its generic-proxy writes are ordered
     // before the bulk copy's) before tile 2 is fetched
@@ -313,6 +375,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
             }
         }
         const int nvalid = min(kTile, hi - (lo + tile * kTile));
+        unsigned char *const ktile_b = ktile_at(buf), *const vtile_b = vtile_at(buf);
         if constexpr (kQ4) {
             // expand the raw q4_0 rows into the q8_0 row image: 64 rows x 8 blocks x {K, V} =
             // 1024 blocks, four per thread; rows past the split's end are left alone
@@ -320,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int item = tid + kThreads * i, row = (item & 511) >> 3, blk = item & 7;
-                const unsigned char *src = (item < 512 ? ktile[buf] : vtile[buf]) + kQ4RawOffset +
+                const unsigned char *src = (item < 512 ? ktile_b : vtile_b) + kQ4RawOffset +
                                            row * kQ4RowBytes + blk * kQ4BlockBytes;
 #pragma unroll
                 for (int w = 0; w < 9; w++) raw[i][w] = reinterpret_cast<const unsigned short *>(src)[w];
@@ -331,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
                 const int item = tid + kThreads * i, row = (item & 511) >> 3, blk = item & 7;
                 if (row >= nvalid) continue;
                 unsigned short *dst = reinterpret_cast<unsigned short *>(
-                    (item < 512 ? ktile[buf] : vtile[buf]) + row * kRowBytes + blk * kQ8BlockBytes);
+                    (item < 512 ? ktile_b : vtile_b) + row * kRowBytes + blk * kQ8BlockBytes);
                 dst[0] = raw[i][0];
 #pragma unroll
                 for (int w = 0; w < 8; w += 2) {
@@ -351,26 +414,28 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         if (nvalid < kTile) {
             // Rows past the split's end hold stale bytes; their V scales must read as zero.
             for (int i = tid; i < (kTile - nvalid) * (kRowBytes / 16); i += kThreads)
-                reinterpret_cast<uint4 *>(vtile[buf] + nvalid * kRowBytes)[i] = make_uint4(0, 0, 0, 0);
+                reinterpret_cast<uint4 *>(vtile_b + nvalid * kRowBytes)[i] = make_uint4(0, 0, 0, 0);
         }
 
         // ---- (1) scores
         {
-            float s[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (dh == 0) {
-                score_block<0>(ktile[buf], kg * 16, g, t, qa[0], qa[1], s);
-                score_block<1>(ktile[buf], kg * 16, g, t, qa[2], qa[3], s);
-                score_block<2>(ktile[buf], kg * 16, g, t, qa[4], qa[5], s);
-                score_block<3>(ktile[buf], kg * 16, g, t, qa[6], qa[7], s);
+                score_block<0>(ktile_b, kg * 16, g, t, qb[0], qb[1], qbias[0], s);
+                score_block<1>(ktile_b, kg * 16, g, t, qb[2], qb[3], qbias[1], s);
+                score_block<2>(ktile_b, kg * 16, g, t, qb[4], qb[5], qbias[2], s);
+                score_block<3>(ktile_b, kg * 16, g, t, qb[6], qb[7], qbias[3], s);
             } else {
-                score_block<4>(ktile[buf], kg * 16, g, t, qa[0], qa[1], s);
-                score_block<5>(ktile[buf], kg * 16, g, t, qa[2], qa[3], s);
-                score_block<6>(ktile[buf], kg * 16, g, t, qa[4], qa[5], s);
-                score_block<7>(ktile[buf], kg * 16, g, t, qa[6], qa[7], s);
+                score_block<4>(ktile_b, kg * 16, g, t, qb[0], qb[1], qbias[0], s);
+                score_block<5>(ktile_b, kg * 16, g, t, qb[2], qb[3], qbias[1], s);
+                score_block<6>(ktile_b, kg * 16, g, t, qb[4], qb[5], qbias[2], s);
+                score_block<7>(ktile_b, kg * 16, g, t, qb[6], qb[7], qbias[3], s);
             }
-            float *dst = ss + (dh * 8 + g) * kSsStride + kg * 16 + 2 * t;
-            *reinterpret_cast<float2 *>(dst) = make_float2(s[0][0], s[0][1]);
-            *reinterpret_cast<float2 *>(dst + 8) = make_float2(s[1][0], s[1][1]);
+            float *dst = ss + (dh * 8 + 2 * t) * kSsStride + kg * 16 + g;
+            dst[0] = s[0];
+            dst[kSsStride] = s[1];
+            dst[8] = s[2];
+            dst[kSsStride + 8] = s[3];
         }
         __syncthreads();
 
@@ -378,8 +443,8 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         {
             const float2 a = *reinterpret_cast<const float2 *>(ss + warp * kSsStride + 2 * lane);
             const float2 b = *reinterpret_cast<const float2 *>(ss + (8 + warp) * kSsStride + 2 * lane);
-            const float s0 = 2 * lane < nvalid ? a.x + b.x : -INFINITY;
-            const float s1 = 2 * lane + 1 < nvalid ? a.y + b.y : -INFINITY;
+            const float s0 = 2 * lane < nvalid ? (a.x + b.x) * kCodeUnit : -INFINITY;
+            const float s1 = 2 * lane + 1 < nvalid ? (a.y + b.y) * kCodeUnit : -INFINITY;
             const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
             // m_new is -inf only while every key so far was masked: nothing to scale then.
             const float corr = (m_new == -INFINITY) ? 1.0f : exp2f(m_run - m_new);
@@ -408,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
 #pragma unroll
             for (int ks = 0; ks < 4; ks++) {
                 const int k0 = ks * 16 + 2 * t;  // keys k0, k0+1, k0+8, k0+9
-                const unsigned char *r0 = vtile[buf] + k0 * kRowBytes;
+                const unsigned char *r0 = vtile_b + k0 * kRowBytes;
                 const unsigned char *r[4] = {r0, r0 + kRowBytes, r0 + 8 * kRowBytes, r0 + 9 * kRowBytes};
                 // A = weight * block scale, kept as an exact f16 high + low pair
                 __half dv[4];
@@ -438,10 +503,10 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
                 const unsigned ab23 = __byte_perm(w[0], w[1], 0x7362);  // [a2 b2 a3 b3]
                 const unsigned cd01 = __byte_perm(w[2], w[3], 0x5140);
                 const unsigned cd23 = __byte_perm(w[2], w[3], 0x7362);
-                mma_16816(acc[0], afrag, codes_to_half2(ab01, 0x4140), codes_to_half2(cd01, 0x4140));
-                mma_16816(acc[1], afrag, codes_to_half2(ab01, 0x4342), codes_to_half2(cd01, 0x4342));
-                mma_16816(acc[2], afrag, codes_to_half2(ab23, 0x4140), codes_to_half2(cd23, 0x4140));
-                mma_16816(acc[3], afrag, codes_to_half2(ab23, 0x4342), codes_to_half2(cd23, 0x4342));
+                mma_16816(acc[0], afrag, codes_to_half2_exact(ab01, 0x4140), codes_to_half2_exact(cd01, 0x4140));
+                mma_16816(acc[1], afrag, codes_to_half2_exact(ab01, 0x4342), codes_to_half2_exact(cd01, 0x4342));
+                mma_16816(acc[2], afrag, codes_to_half2_exact(ab23, 0x4140), codes_to_half2_exact(cd23, 0x4140));
+                mma_16816(acc[3], afrag, codes_to_half2_exact(ab23, 0x4342), codes_to_half2_exact(cd23, 0x4342));
             }
         }
         __syncthreads();  // tile buffers, ss and the weight tile are reused by the next tile

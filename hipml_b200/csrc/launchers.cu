@@ -23,6 +23,21 @@ int check_encode(int dtype, int n_kv, int head_dim, int stride) {
     return 0;
 }
 
+// Live runs per KV head of the single-stream split pass: one round of the device's CTA slots
+// (two CTAs per SM), so that every CTA streams one long run instead of several short ones.
+int decode_run_cap(int n_kv) {
+    static int slots = 0;
+    if (slots == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+        slots = 2 * sms;
+    }
+    const int cap = slots / (n_kv > 0 ? n_kv : 1);
+    return cap < 1 ? 1 : cap;
+}
+
 int check_heads(int n_heads, int n_kv, int head_dim) {
     if (n_kv <= 0 || n_heads % n_kv != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "n_heads %d is not a multiple of n_kv %d", n_heads,
@@ -164,6 +179,7 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     p.splits = splits;
     p.by_stride = 0;
     p.q4 = selector == 1;
+    p.run_cap = decode_run_cap(n_kv);
     p.kv_slot_bytes = p.acc_slot = p.ml_slot = p.q_slot = 0;
     if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
@@ -313,6 +329,7 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
     p.splits = splits;
     p.by_stride = by_stride;
     p.q4 = dtype == 1;
+    p.run_cap = by_stride ? 0 : decode_run_cap(n_kv);
     p.kv_slot_bytes = kv_slot_bytes;
     p.acc_slot = acc_slot;
     p.ml_slot = ml_slot;
