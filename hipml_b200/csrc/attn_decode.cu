@@ -150,14 +150,19 @@ __global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
     const int dl = threadIdx.x & 31, sg = threadIdx.x >> 5;
     const float *pa = p.acc + (size_t)slot * p.acc_slot + (size_t)h * p.acc_head_stride + chunk * 32 + dl;
     const float *ml = p.ml + (size_t)slot * p.ml_slot + (size_t)h * p.ml_head_stride;
+    int nsplit = p.splits;
+    if (p.len) {
+        const int tiles = (p.len[slot * p.len_stride + p.len_offset] + 63) >> 6;
+        nsplit = min(min(nsplit, tiles), p.run_cap);
+    }
     float big = -INFINITY;
-    for (int s = sg; s < p.splits; s += 8) big = fmaxf(big, ml[(size_t)s * p.ml_split_stride]);
+    for (int s = sg; s < nsplit; s += 8) big = fmaxf(big, ml[(size_t)s * p.ml_split_stride]);
     if (dl == 0) s_max[sg] = big;
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < 8; i++) big = fmaxf(big, s_max[i]);
     float num = 0.0f, den = 0.0f;
-    for (int s = sg; s < p.splits; s += 8) {
+    for (int s = sg; s < nsplit; s += 8) {
         const float m = ml[(size_t)s * p.ml_split_stride];
         const float w = (m == -INFINITY) ? 0.0f : exp2f(m - big);
         num += pa[(size_t)s * p.acc_split_stride] * w;
@@ -261,8 +266,14 @@ int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, in
 int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int splits, int slots,
                          long long acc_slot, long long ml_slot, long long out_slot,
-                         const float *gate) {
+                         const float *gate, const DecodeParams *live_runs) {
     FoldParams p;
+    if (live_runs && live_runs->run_cap > 0 && !live_runs->by_stride) {
+        p.len = live_runs->len;
+        p.len_stride = live_runs->len_stride;
+        p.len_offset = live_runs->len_offset;
+        p.run_cap = live_runs->run_cap;
+    }
     p.acc = part_acc;
     p.ml = part_ml;
     p.out = out;

@@ -126,12 +126,13 @@ __device__ __forceinline__ int k_word_dim(int blk, int j, int i) {
     return blk * 32 + (i < 2 ? i : 28 + i);
 }
 
-// V side: codes 4j..4j+3 of block blk in natural order (two loads and a permute for even
-// blocks, whose codes straddle word boundaries).
-__device__ __forceinline__ unsigned v_word(const unsigned *row, int blk, int j) {
-    const int m = blk >> 1;
-    if (blk & 1) return row[17 * m + 9 + j];
-    return __byte_perm(row[17 * m + j], row[17 * m + j + 1], 0x5432);
+// V side: codes 4j..4j+3 of a block in natural order; `blk_row` points at the block's first
+// aligned word (odd blocks: its first code word; even blocks: the word that starts with the
+// scale, so the codes straddle word boundaries: two loads and a permute).
+template <bool kOdd>
+__device__ __forceinline__ unsigned v_word(const unsigned *blk_row, int j) {
+    if constexpr (kOdd) return blk_row[j];
+    return __byte_perm(blk_row[j], blk_row[j + 1], 0x5432);
 }
 
 // Two bytes of `biased` (code ^ 0x80 = code + 128) as a half2 of f16 subnormals: 0x00xx is
@@ -220,6 +221,60 @@ __device__ __forceinline__ void score_block(const unsigned char *ktile, int key_
     s[1] += d0 * c[1];
     s[2] += d1 * c[2];
     s[3] += d1 * c[3];
+}
+
+// Values of one tile for block `blk` (32 dims): acc = acc * corr + weights * scale * codes over
+// the 64 keys. A = weight * block scale as an exact f16 high + low pair (rows 0..7 high part of
+// head g, rows 8..15 low part), B = the block's codes, four n-tiles: output column n of MMA i
+// is dim 32*blk + 4n + i. All shared-memory offsets inside the unrolled loop are immediates
+// off three per-thread base pointers.
+template <bool kOdd>
+__device__ __forceinline__ void values_block(const unsigned char *vtile, int blk, int g, int t,
+                                             const __half *ph, const __half *pl, float corr,
+                                             float (&acc)[4][4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[i][c] *= corr;
+    // keys k0 = 16*ks + 2t, k0 + 1, k0 + 8, k0 + 9 of every 16-key step
+    const unsigned char *scale0 = vtile + 2 * t * kRowBytes + blk * kQ8BlockBytes;
+    const unsigned *code0 =
+        reinterpret_cast<const unsigned *>(scale0 + (kOdd ? 2 : 0)) + g;
+    const __half *ph0 = ph + g * kPStride + 2 * t, *pl0 = pl + g * kPStride + 2 * t;
+    constexpr int kRowWords = kRowBytes / 4;
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++) {
+        constexpr int kOff[4] = {0, 1, 8, 9};
+        __half dv[4];
+        unsigned w[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            dv[e] = __ushort_as_half(*reinterpret_cast<const unsigned short *>(
+                scale0 + (ks * 16 + kOff[e]) * kRowBytes));
+            w[e] = v_word<kOdd>(code0 + (ks * 16 + kOff[e]) * kRowWords, 0) ^ 0x80808080u;
+        }
+        const __half2 d01 = __halves2half2(dv[0], dv[1]), d23 = __halves2half2(dv[2], dv[3]);
+        const __half2 ph01 = *reinterpret_cast<const __half2 *>(ph0 + ks * 16);
+        const __half2 ph23 = *reinterpret_cast<const __half2 *>(ph0 + ks * 16 + 8);
+        const __half2 pl01 = *reinterpret_cast<const __half2 *>(pl0 + ks * 16);
+        const __half2 pl23 = *reinterpret_cast<const __half2 *>(pl0 + ks * 16 + 8);
+        const __half2 h01 = __hmul2(ph01, d01), h23 = __hmul2(ph23, d23);
+        const __half2 l01 = __hfma2(pl01, d01, __hfma2(ph01, d01, __hneg2(h01)));
+        const __half2 l23 = __hfma2(pl23, d23, __hfma2(ph23, d23, __hneg2(h23)));
+        unsigned afrag[4];
+        afrag[0] = *reinterpret_cast<const unsigned *>(&h01);
+        afrag[1] = *reinterpret_cast<const unsigned *>(&l01);
+        afrag[2] = *reinterpret_cast<const unsigned *>(&h23);
+        afrag[3] = *reinterpret_cast<const unsigned *>(&l23);
+        const unsigned ab01 = __byte_perm(w[0], w[1], 0x5140);  // [a0 b0 a1 b1]
+        const unsigned ab23 = __byte_perm(w[0], w[1], 0x7362);  // [a2 b2 a3 b3]
+        const unsigned cd01 = __byte_perm(w[2], w[3], 0x5140);
+        const unsigned cd23 = __byte_perm(w[2], w[3], 0x7362);
+        mma_16816(acc[0], afrag, codes_to_half2_exact(ab01, 0x4140), codes_to_half2_exact(cd01, 0x4140));
+        mma_16816(acc[1], afrag, codes_to_half2_exact(ab01, 0x4342), codes_to_half2_exact(cd01, 0x4342));
+        mma_16816(acc[2], afrag, codes_to_half2_exact(ab23, 0x4140), codes_to_half2_exact(cd23, 0x4140));
+        mma_16816(acc[3], afrag, codes_to_half2_exact(ab23, 0x4342), codes_to_half2_exact(cd23, 0x4342));
+    }
 }
 
 // kQ4: the cache is q4_0 (144-byte rows). A tile's raw rows are copied into the upper part of
@@ -463,52 +518,10 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         __syncthreads();
 
         // ---- (3) values: warp = block (32 dims), all 64 keys
-        {
-            const float corr = corr_s[g];
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int c = 0; c < 4; c++) acc[i][c] *= corr;
-            const int blk = warp;
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                const int k0 = ks * 16 + 2 * t;  // keys k0, k0+1, k0+8, k0+9
-                const unsigned char *r0 = vtile_b + k0 * kRowBytes;
-                const unsigned char *r[4] = {r0, r0 + kRowBytes, r0 + 8 * kRowBytes, r0 + 9 * kRowBytes};
-                // A = weight * block scale, kept as an exact f16 high + low pair
-                __half dv[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    dv[e] = __ushort_as_half(
-                        *reinterpret_cast<const unsigned short *>(r[e] + blk * kQ8BlockBytes));
-                const __half2 d01 = __halves2half2(dv[0], dv[1]), d23 = __halves2half2(dv[2], dv[3]);
-                const __half2 ph01 = *reinterpret_cast<const __half2 *>(ph + g * kPStride + k0);
-                const __half2 ph23 = *reinterpret_cast<const __half2 *>(ph + g * kPStride + k0 + 8);
-                const __half2 pl01 = *reinterpret_cast<const __half2 *>(pl + g * kPStride + k0);
-                const __half2 pl23 = *reinterpret_cast<const __half2 *>(pl + g * kPStride + k0 + 8);
-                const __half2 h01 = __hmul2(ph01, d01), h23 = __hmul2(ph23, d23);
-                const __half2 l01 = __hfma2(pl01, d01, __hfma2(ph01, d01, __hneg2(h01)));
-                const __half2 l23 = __hfma2(pl23, d23, __hfma2(ph23, d23, __hneg2(h23)));
-                unsigned afrag[4];
-                afrag[0] = *reinterpret_cast<const unsigned *>(&h01);
-                afrag[1] = *reinterpret_cast<const unsigned *>(&l01);
-                afrag[2] = *reinterpret_cast<const unsigned *>(&h23);
-                afrag[3] = *reinterpret_cast<const unsigned *>(&l23);
-                // B: code word g of the block (dims 32*blk + 4g .. +3) from each of the four keys
-                unsigned w[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    w[e] = v_word(reinterpret_cast<const unsigned *>(r[e]), blk, g) ^ 0x80808080u;
-                const unsigned ab01 = __byte_perm(w[0], w[1], 0x5140);  // [a0 b0 a1 b1]
-                const unsigned ab23 = __byte_perm(w[0], w[1], 0x7362);  // [a2 b2 a3 b3]
-                const unsigned cd01 = __byte_perm(w[2], w[3], 0x5140);
-                const unsigned cd23 = __byte_perm(w[2], w[3], 0x7362);
-                mma_16816(acc[0], afrag, codes_to_half2_exact(ab01, 0x4140), codes_to_half2_exact(cd01, 0x4140));
-                mma_16816(acc[1], afrag, codes_to_half2_exact(ab01, 0x4342), codes_to_half2_exact(cd01, 0x4342));
-                mma_16816(acc[2], afrag, codes_to_half2_exact(ab23, 0x4140), codes_to_half2_exact(cd23, 0x4140));
-                mma_16816(acc[3], afrag, codes_to_half2_exact(ab23, 0x4342), codes_to_half2_exact(cd23, 0x4342));
-            }
-        }
+        if (warp & 1)
+            values_block<true>(vtile_b, warp, g, t, ph, pl, corr_s[g], acc);
+        else
+            values_block<false>(vtile_b, warp, g, t, ph, pl, corr_s[g], acc);
         __syncthreads();  // tile buffers, ss and the weight tile are reused by the next tile
     }
 

@@ -199,7 +199,8 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     }
     if (!shard)
         return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
-                                    splits, 1, 0, 0, 0, gate);
+                                    splits, 1, 0, 0, 0, gate,
+                                    tensor_core && !tcgen05_body ? &p : nullptr);
     FoldParams f;
     f.acc = part_acc;
     f.ml = part_ml;
@@ -214,6 +215,12 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     f.out_head_stride = head_dim + 2;
     f.normalize = 0;
     f.gate = nullptr;
+    if (tensor_core && !tcgen05_body && p.run_cap > 0) {
+        f.len = p.len;
+        f.len_stride = p.len_stride;
+        f.len_offset = p.len_offset;
+        f.run_cap = p.run_cap;
+    }
     return launch_decode_fold(as_stream(stream), f, n_heads, 1);
 }
 
@@ -340,7 +347,7 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
     const bool tensor_core = head_dim == 256 && aligned;
     if (int e = launch_decode_split(as_stream(stream), p, slots, tensor_core)) return e;
     return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim, splits,
-                                slots, acc_slot, ml_slot, q_slot);
+                                slots, acc_slot, ml_slot, q_slot, nullptr, tensor_core ? &p : nullptr);
 }
 
 int hipml_attn_decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,

@@ -39,13 +39,18 @@ struct FoldParams {
     long long acc_slot, ml_slot, out_slot, out_head_stride;
     int normalize;     // 1: out = acc/sum; 0: out row = [acc (unnormalised) | max | sum]
     const float *gate; // optional, normalize only: out *= sigmoid(gate), laid out as out
+    // Optional: the partials come from the tensor-core split pass with balanced runs, which
+    // leaves only min(splits, 64-key tiles of the live length, run_cap) live runs per head;
+    // the rest are neutral and need not be read. len == nullptr: fold all `splits`.
+    const int *len = nullptr;
+    int len_stride = 0, len_offset = 0, run_cap = 0;
 };
 int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots);
 // Folds the partials into out[slot][h][d] (slot strides in floats).
 int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int splits, int slots,
                          long long acc_slot, long long ml_slot, long long out_slot,
-                         const float *gate = nullptr);
+                         const float *gate = nullptr, const DecodeParams *live_runs = nullptr);
 
 // Scalar chunk attention (attn_chunk_scalar.cu).
 struct ChunkScalarParams {
