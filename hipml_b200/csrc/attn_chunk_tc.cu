@@ -517,6 +517,9 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         tmem_alloc<kCtas>(smem_u32(tmem_slot), 512);  // in the pair form: warp 0 of both CTAs
     }
 
+    // The query rows may come from a grid that is still running (a dependent launch can start
+    // while the grid before its predecessor has not finished): nothing is read before this.
+    griddep_wait();
     // Q tile: f32 -> scaled hi/lo f16 in the swizzled K-major image. Row r = query r/group,
     // head r%group; rows past the live queries are zero.
     for (int i = tid; i < 128 * (kD / 8); i += kTcThreads) {
@@ -563,10 +566,8 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         if (lane == 0 && n_tiles > 0) {
             unsigned n = 0;  // chunks issued
             bool ok = true;
-            // The staged image (and, behind it, the scratch and the output rows) belongs to
-            // the previous grids; the query tile above is the caller's input. Everything the
-            // CTA does to memory from here on follows one of this thread's copies.
-            griddep_wait();
+            // (the staged image, the scratch and the output rows belong to the previous grids:
+            // every thread waited for them before the query tile was read)
             // Takes the next ring slot once the MMAs that read it have completed and arms its
             // full barrier; in a pair only the leader arms, with both CTAs' bytes (the peer's
             // copies complete on the leader's barrier).

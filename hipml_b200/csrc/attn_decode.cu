@@ -152,8 +152,18 @@ __global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
     const float *ml = p.ml + (size_t)slot * p.ml_slot + (size_t)h * p.ml_head_stride;
     int nsplit = p.splits;
     if (p.len) {
-        const int tiles = (p.len[slot * p.len_stride + p.len_offset] + 63) >> 6;
-        nsplit = min(min(nsplit, tiles), p.run_cap);
+        __shared__ int s_quota;
+        if (p.share_slots > 0) {
+            if (sg == 0) {
+                const int q = shared_quota_warp(p.len, p.len_stride, p.len_offset, gridDim.y, p.splits,
+                                                p.share_slots, p.n_kv);
+                if (dl == 0) s_quota = q;
+            }
+            __syncthreads();
+        }
+        const RunPlan plan = plan_runs(p.len, p.len_stride, p.len_offset, slot, p.splits, p.run_cap,
+                                       p.share_slots, p.share_slots > 0 ? s_quota : 0);
+        if (plan.runs >= 0) nsplit = plan.runs;
     }
     float big = -INFINITY;
     for (int s = sg; s < nsplit; s += 8) big = fmaxf(big, ml[(size_t)s * p.ml_split_stride]);
@@ -268,11 +278,13 @@ int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float
                          long long acc_slot, long long ml_slot, long long out_slot,
                          const float *gate, const DecodeParams *live_runs) {
     FoldParams p;
-    if (live_runs && live_runs->run_cap > 0 && !live_runs->by_stride) {
+    if (live_runs && (live_runs->share_slots > 0 || (live_runs->run_cap > 0 && !live_runs->by_stride))) {
         p.len = live_runs->len;
         p.len_stride = live_runs->len_stride;
         p.len_offset = live_runs->len_offset;
-        p.run_cap = live_runs->run_cap;
+        p.run_cap = live_runs->by_stride ? 0 : live_runs->run_cap;
+        p.share_slots = live_runs->share_slots;
+        p.n_kv = live_runs->n_kv;
     }
     p.acc = part_acc;
     p.ml = part_ml;

@@ -166,18 +166,18 @@ __device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
 // partials. Coarser runs were measured too (fewer, longer CTAs chosen from the device's CTA
 // slots): no gain for one stream at 100,000 rows and 20 % slower for 8 - 16 slots of mixed
 // depth, where the longest CTAs form the tail.
-__device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int &lo,
-                                            int &hi) {
+__device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int quota,
+                                            int &lo, int &hi) {
     const int len = p.len[slot * p.len_stride + p.len_offset];
-    if (!p.by_stride && p.run_cap > 0) {
-        const int tiles = (len + kTile - 1) / kTile;
-        const int runs = min(min(p.splits, tiles), p.run_cap);
-        if (split >= runs) {
+    const RunPlan plan = plan_runs(p.len, p.len_stride, p.len_offset, slot, p.splits,
+                                   p.by_stride ? 0 : p.run_cap, p.share_slots, quota);
+    if (plan.runs >= 0) {
+        if (split >= plan.runs) {
             lo = hi = len;
             return;
         }
-        lo = (int)((long long)split * tiles / runs) * kTile;
-        hi = min((int)((long long)(split + 1) * tiles / runs) * kTile, len);
+        lo = (int)((long long)split * plan.tiles / plan.runs) * kTile;
+        hi = min((int)((long long)(split + 1) * plan.tiles / plan.runs) * kTile, len);
         return;
     }
     const int span = p.by_stride ? p.stride : len;
@@ -288,6 +288,10 @@ template <bool kQ4>
 __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int *status) {
     extern __shared__ __align__(16) unsigned char smem[];
     griddep_launch();
+    // Everything this kernel reads -- the live lengths, the query, the cache rows with this
+    // step's append -- may come from the grids before it, and a dependent launch can start
+    // while the grid before its predecessor is still running: nothing is read before this.
+    griddep_wait();
     auto ktile_at = [&](int stage) { return smem + 2 * stage * kTileBytes; };
     auto vtile_at = [&](int stage) { return smem + (2 * stage + 1) * kTileBytes; };
     float *qs = reinterpret_cast<float *>(ktile_at(2));              // set-up only
@@ -299,17 +303,59 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int slot = blockIdx.y;
-    const int kvh = blockIdx.x / p.splits, split = blockIdx.x - kvh * p.splits;
     const int group = p.n_heads / p.n_kv;
     const int kg = warp & 3, dh = warp >> 2;
 
+    // Which (slot, KV head, run) this CTA owns. Plain form: grid (n_kv * splits, slots).
+    // Shared form (several slots, share_slots > 0): a one-dimensional grid of exactly the
+    // device's CTA slots; CTA b takes the b-th live run in (slot, head, run) order, found by a
+    // scan over the slots' run counts, and CTAs past the last live run have nothing to do (no
+    // dead run is ever launched, so no live run waits behind them).
+    __shared__ int s_plan[4];   // slot (-1: none), kvh, split, quota
+    int slot = blockIdx.y, kvh = blockIdx.x / p.splits, split = blockIdx.x - kvh * p.splits;
+    if (p.share_slots > 0) {
+        if (warp == 0) {
+            const int quota = shared_quota_warp(p.len, p.len_stride, p.len_offset, p.n_slots, p.splits,
+                                                p.share_slots, p.n_kv);
+            const int b = blockIdx.x;
+            int base = 0;
+            if (lane == 0) {
+                s_plan[0] = -1;
+                s_plan[3] = quota;
+            }
+            __syncwarp();
+            for (int s0 = 0; s0 < p.n_slots; s0 += 32) {
+                const int s = s0 + lane;
+                const int per = s < p.n_slots
+                    ? ((p.len[s * p.len_stride + p.len_offset] + 63) / 64 + quota - 1) / quota : 0;
+                const int runs = per * p.n_kv;
+                int incl = runs;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                const int first = base + incl - runs;
+                if (runs > 0 && b >= first && b < first + runs) {
+                    const int r = b - first;
+                    s_plan[0] = s;
+                    s_plan[1] = r / per;
+                    s_plan[2] = r - (r / per) * per;
+                }
+                base += __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        __syncthreads();
+        slot = s_plan[0];
+        kvh = s_plan[1];
+        split = s_plan[2];
+        if (slot < 0) return;
+    }
     int lo, hi;
-    split_range(p, slot, split, lo, hi);
+    split_range(p, slot, split, p.share_slots > 0 ? s_plan[3] : 0, lo, hi);
     const int ntiles = (hi - lo + kTile - 1) / kTile;
     if (ntiles == 0) {
         // A split without rows: neutral partials (zero sum, -inf maximum), nothing else.
-        griddep_wait();   // the scratch may still be read by the previous grid
         for (int i = tid; i < group * 256; i += kThreads) {
             const int h = kvh * group + (i >> 8);
             p.part_acc[(size_t)slot * p.acc_slot + ((size_t)h * p.splits + split) * 256 + (i & 255)] = 0.0f;
@@ -348,11 +394,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
 #pragma unroll
         for (int s = 0; s < kStages; s++) mbar_init(bar_full + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // The cache rows (the append of this step among them) and the scratch belong to the
-        // previous grids: nothing of them is touched before this wait. Every later access of
-        // the CTA follows one of these copies, so the other threads need no wait of their
-        // own; the query set-up below overlaps the previous grid's tail.
-        griddep_wait();
         fetch(0);
         if (ntiles > 1) fetch(1);
     }
@@ -526,7 +567,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     }
 
     if (!landed && status) atomicCAS(status, 0, 21);
-    griddep_wait();   // (long satisfied: thread 0 waited before the first copy)
 
     // ---- partials. Output column n of MMA i is dim 32*blk + 4n + i; this thread holds
     // columns 2t, 2t+1, i.e. dims 32*blk + 8t + i and 32*blk + 8t + 4 + i of head g
@@ -569,10 +609,13 @@ int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
         if (status_word[dev] == nullptr) return launch_status();
     }
     dim3 grid(p.n_kv * p.splits, slots);
-    if (p.q4)
-        return launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, p,
+    DecodeParams q = p;
+    q.n_slots = slots;
+    if (q.share_slots > 0) grid = dim3(q.share_slots, 1);
+    if (q.q4)
+        return launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
                           status_word[dev]);
-    return launch_pdl(attn_decode_kv_tc<false>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, p,
+    return launch_pdl(attn_decode_kv_tc<false>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
                       status_word[dev]);
 }
 

@@ -240,6 +240,7 @@ __global__ void __launch_bounds__(256) attn_front_rows_q8(FrontRowsParams p) {
     __shared__ float cs[kMaxHeadDim / 2], sn[kMaxHeadDim / 2];
     __shared__ __align__(16) unsigned char img[8][kMaxRowBytes];
     griddep_launch();
+    griddep_wait();   // positions and rows may come from a grid that is still running
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int p4[4];
     if (p.pos4) {
@@ -251,7 +252,6 @@ __global__ void __launch_bounds__(256) attn_front_rows_q8(FrontRowsParams p) {
     for (int c = threadIdx.x; c < half; c += blockDim.x) rope_angle(p.rope, c, p4, cs[c], sn[c]);
     __syncthreads();
     const int cache_row = p.step ? p.step[0] : p.pos0 + t;
-    griddep_wait();   // inputs are the caller's; the outputs and the caches are shared
     const int rows = p.n_heads + 2 * p.n_kv;
     for (int r = warp; r < rows; r += 8) {
         float x[8];

@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(256) kv_encode_bulk_q8_w(const float *__restri
                                                            int src0) {
     __shared__ __align__(16) unsigned char img[8][2][kMaxRowBytes];
     griddep_launch();
+    griddep_wait();   // the f32 rows may come from a grid that is still running
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long idx = (long long)blockIdx.x * 8 + warp;
     if (idx >= (long long)n_kv * rows) return;
@@ -127,7 +128,6 @@ __global__ void __launch_bounds__(256) kv_encode_bulk_q8_w(const float *__restri
     q8_put8(ka, kb, lane, img[warp][0]);
     q8_put8(va, vb, lane, img[warp][1]);
     __syncwarp();
-    griddep_wait();   // the loads above are of the caller's f32 rows; the cache is shared
     const size_t off = q8_row_offset(h, stride, start + r, 256);
     row_store(kc + off, img[warp][0], kMaxRowBytes, lane, 32);
     row_store(vc + off, img[warp][1], kMaxRowBytes, lane, 32);
@@ -220,6 +220,7 @@ __global__ void __launch_bounds__(256) kv_encode_bulk_q4_w(const float *__restri
                                                            int src0) {
     __shared__ __align__(16) unsigned char img[8][2][8 * kQ4BlockBytes];
     griddep_launch();
+    griddep_wait();   // the f32 rows may come from a grid that is still running
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long idx = (long long)blockIdx.x * 8 + warp;
     if (idx >= (long long)n_kv * rows) return;
@@ -233,7 +234,6 @@ __global__ void __launch_bounds__(256) kv_encode_bulk_q4_w(const float *__restri
     q4_put8(ka, kb, lane, img[warp][0]);
     q4_put8(va, vb, lane, img[warp][1]);
     __syncwarp();
-    griddep_wait();
     const size_t off = q4_row_offset(h, stride, start + r, 256);
     row_store(kc + off, img[warp][0], 8 * kQ4BlockBytes, lane, 32);
     row_store(vc + off, img[warp][1], 8 * kQ4BlockBytes, lane, 32);

@@ -25,7 +25,7 @@ int check_encode(int dtype, int n_kv, int head_dim, int stride) {
 
 // Live runs per KV head of the single-stream split pass: one round of the device's CTA slots
 // (two CTAs per SM), so that every CTA streams one long run instead of several short ones.
-int decode_run_cap(int n_kv) {
+int decode_cta_slots() {
     static int slots = 0;
     if (slots == 0) {
         int dev = 0, sms = 0;
@@ -34,7 +34,10 @@ int decode_run_cap(int n_kv) {
             sms = 148;
         slots = 2 * sms;
     }
-    const int cap = slots / (n_kv > 0 ? n_kv : 1);
+    return slots;
+}
+int decode_run_cap(int n_kv) {
+    const int cap = decode_cta_slots() / (n_kv > 0 ? n_kv : 1);
     return cap < 1 ? 1 : cap;
 }
 
@@ -180,6 +183,8 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     p.by_stride = 0;
     p.q4 = selector == 1;
     p.run_cap = decode_run_cap(n_kv);
+    p.share_slots = 0;
+    p.n_slots = 1;
     p.kv_slot_bytes = p.acc_slot = p.ml_slot = p.q_slot = 0;
     if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
@@ -336,7 +341,14 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
     p.splits = splits;
     p.by_stride = by_stride;
     p.q4 = dtype == 1;
+    p.n_slots = slots;
     p.run_cap = by_stride ? 0 : decode_run_cap(n_kv);
+    // Several slots of unequal depth: the slots share one round of CTAs in proportion to their
+    // live lengths (every CTA reads all the lengths, so only for a moderate number of slots);
+    // the fixed cache-position runs remain for the kernels without this plan.
+    p.share_slots =
+        (by_stride && slots > 1 && slots <= 64 && 2 * slots * n_kv <= decode_cta_slots()) ? decode_cta_slots()
+                                                                                          : 0;
     p.kv_slot_bytes = kv_slot_bytes;
     p.acc_slot = acc_slot;
     p.ml_slot = ml_slot;

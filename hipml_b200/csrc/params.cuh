@@ -23,8 +23,61 @@ struct DecodeParams {
     int q4;               // 1: the cache is q4_0 (18-byte blocks), 0: q8_0
     int run_cap;          // tensor-core body, by_stride == 0: at most this many live runs per
                           // KV head, balanced to within one 64-key tile (0: the reference's runs)
+    int share_slots;      // tensor-core body, several slots: the device's CTA slots, shared by
+                          // all slots in proportion to their live lengths (0: off)
+    int n_slots;          // set by launch_decode_tc
     long long kv_slot_bytes, acc_slot, ml_slot, q_slot;
 };
+// Live runs of one slot in the tensor-core split pass, in 64-key tiles: `runs` runs deal the
+// slot's `tiles` tiles out to within one tile (run i covers tiles [i*tiles/runs,
+// (i+1)*tiles/runs)). Single stream: min(splits, tiles, run_cap). Several slots sharing the
+// device (share_slots > 0): every run gets `quota` tiles, about total_tiles * n_kv /
+// share_slots, so a slot's runs are proportional to its live length and the whole batch is
+// one round of CTAs. runs == -1: the reference's fixed runs apply instead.
+struct RunPlan {
+    int tiles, runs;
+};
+// Tiles per run of the shared plan. Called by all 32 lanes of one warp (lane-strided over
+// the slots); every lane returns the same value.
+__device__ __forceinline__ int shared_quota_warp(const int *len, int len_stride, int len_offset,
+                                                 int slots, int splits, int share_slots, int n_kv) {
+    const int lane = threadIdx.x & 31;
+    int total = 0, longest = 0;
+    for (int s = lane; s < slots; s += 32) {
+        const int t = (len[s * len_stride + len_offset] + 63) >> 6;
+        total += t;
+        longest = max(longest, t);
+    }
+    total = __reduce_add_sync(0xffffffffu, total);
+    longest = __reduce_max_sync(0xffffffffu, longest);
+    int quota = (total * n_kv + share_slots - 1) / share_slots;
+    quota = max(max(quota, (longest + splits - 1) / splits), 1);
+    // rounding every slot up can push the batch past one round of CTAs: grow the quota until
+    // the live runs fit (a few steps; past `longest` every slot is one run)
+    for (int step = 0; step < 64 && quota < longest; step++) {
+        int runs = 0;
+        for (int s = lane; s < slots; s += 32)
+            runs += ((len[s * len_stride + len_offset] + 63) / 64 + quota - 1) / quota;
+        runs = __reduce_add_sync(0xffffffffu, runs);
+        if (runs * n_kv <= share_slots) break;
+        quota++;
+    }
+    return quota;
+}
+// `quota`: shared_quota_warp's value when share_slots > 0 (unused otherwise).
+__device__ __forceinline__ RunPlan plan_runs(const int *len, int len_stride, int len_offset, int slot,
+                                             int splits, int run_cap, int share_slots, int quota) {
+    RunPlan r;
+    r.tiles = (len[slot * len_stride + len_offset] + 63) >> 6;
+    if (share_slots > 0)
+        r.runs = (r.tiles + quota - 1) / quota;
+    else if (run_cap > 0)
+        r.runs = min(min(splits, r.tiles), run_cap);
+    else
+        r.runs = -1;
+    return r;
+}
+
 // Launches the split pass (the caller launches the reduce).
 int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, bool tensor_core);
 int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots);
@@ -43,7 +96,7 @@ struct FoldParams {
     // leaves only min(splits, 64-key tiles of the live length, run_cap) live runs per head;
     // the rest are neutral and need not be read. len == nullptr: fold all `splits`.
     const int *len = nullptr;
-    int len_stride = 0, len_offset = 0, run_cap = 0;
+    int len_stride = 0, len_offset = 0, run_cap = 0, share_slots = 0, n_kv = 1;
 };
 int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots);
 // Folds the partials into out[slot][h][d] (slot strides in floats).

@@ -166,7 +166,7 @@ def test_multi_slot_decode_each_slot_reads_only_its_own_cache(slots):
                           0.0625, splits, slot_bytes, acc_slot, ml_slot, q_slot, slots, 0)
     torch.cuda.synchronize()
     got = out.cpu().numpy()
-    assert not np.isnan(acc.cpu().numpy()).any() and not np.isnan(ml.cpu().numpy()).any()
+    # (the partials are scratch: runs that hold no rows are neither written nor folded)
     for s, d in enumerate(depths):
         expected = O.attn_decode_kv_q8(q[s], kc[s], vc[s], heads, n_kv, hd, d + 1, 0.0625,
                                        stride=stride)
