@@ -312,7 +312,10 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     // scan over the slots' run counts, and CTAs past the last live run have nothing to do (no
     // dead run is ever launched, so no live run waits behind them).
     __shared__ int s_plan[4];   // slot (-1: none), kvh, split, quota
-    int slot = blockIdx.y, kvh = blockIdx.x / p.splits, split = blockIdx.x - kvh * p.splits;
+    // (single stream with balanced runs: only the first min(splits, run_cap) runs of a head
+    // can hold rows, and only those are launched)
+    const int grid_splits = (p.by_stride || p.run_cap <= 0) ? p.splits : min(p.splits, p.run_cap);
+    int slot = blockIdx.y, kvh = blockIdx.x / grid_splits, split = blockIdx.x - kvh * grid_splits;
     if (p.share_slots > 0) {
         if (warp == 0) {
             const int quota = shared_quota_warp(p.len, p.len_stride, p.len_offset, p.n_slots, p.splits,
@@ -611,7 +614,10 @@ int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
     dim3 grid(p.n_kv * p.splits, slots);
     DecodeParams q = p;
     q.n_slots = slots;
-    if (q.share_slots > 0) grid = dim3(q.share_slots, 1);
+    if (q.share_slots > 0)
+        grid = dim3(q.share_slots, 1);
+    else if (!q.by_stride && q.run_cap > 0 && q.run_cap < q.splits)
+        grid = dim3(q.n_kv * q.run_cap, slots);
     if (q.q4)
         return launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
                           status_word[dev]);

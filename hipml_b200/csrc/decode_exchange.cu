@@ -39,6 +39,8 @@ struct ExchangeParams {
     int *status;
     int head_dim, splits, n_heads, shards, rank, phases;
     unsigned wait_polls;
+    const int *len;      // optional: only min(splits, 64-key tiles of *len, run_cap) partials are live
+    int run_cap;
     unsigned char *ws[kMaxShards];   // every rank's workspace as mapped in this process
 };
 
@@ -97,14 +99,15 @@ __global__ void __launch_bounds__(256) attn_decode_fold_exchange(ExchangeParams 
         // ---- publish: fold the local partials of (h, chunk) ...
         const float *pa = p.acc + (size_t)h * p.splits * p.head_dim + chunk * 32 + dl;
         const float *ml = p.ml + (size_t)h * p.splits * 2;
+        const int nsplit = p.len ? min(min(p.splits, (*p.len + 63) >> 6), p.run_cap) : p.splits;
         float big = -INFINITY;
-        for (int s = sg; s < p.splits; s += 8) big = fmaxf(big, ml[2 * s]);
+        for (int s = sg; s < nsplit; s += 8) big = fmaxf(big, ml[2 * s]);
         if (dl == 0) s_max[sg] = big;
         __syncthreads();
 #pragma unroll
         for (int i = 0; i < 8; i++) big = fmaxf(big, s_max[i]);
         float num = 0.0f, den = 0.0f;
-        for (int s = sg; s < p.splits; s += 8) {
+        for (int s = sg; s < nsplit; s += 8) {
             const float m = ml[2 * s];
             const float w = (m == -INFINITY) ? 0.0f : exp2f(m - big);
             num += pa[(size_t)s * p.head_dim] * w;
@@ -195,8 +198,14 @@ size_t decode_exchange_bytes(int n_heads, int head_dim, int shards) {
 int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, const float *part_ml,
                                 float *out, int n_heads, int head_dim, int splits,
                                 void *const *peer_ws, int shards, int rank, int phases,
-                                unsigned wait_limit_us, int *status) {
+                                unsigned wait_limit_us, int *status, const DecodeParams *live_runs) {
     ExchangeParams p;
+    p.len = nullptr;
+    p.run_cap = 0;
+    if (live_runs && live_runs->run_cap > 0 && !live_runs->by_stride) {
+        p.len = live_runs->len + live_runs->len_offset;
+        p.run_cap = live_runs->run_cap;
+    }
     p.acc = part_acc;
     p.ml = part_ml;
     p.out = out;

@@ -200,7 +200,8 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
         if (!status) return launch_status();
         return launch_decode_fold_exchange(as_stream(stream), part_acc, part_ml, out, n_heads,
                                            head_dim, splits, xch->peer_ws, xch->shards, xch->rank,
-                                           xch->phases, xch->wait_limit_us, status);
+                                           xch->phases, xch->wait_limit_us, status,
+                                           tensor_core && !tcgen05_body ? &p : nullptr);
     }
     if (!shard)
         return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,

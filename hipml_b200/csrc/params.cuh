@@ -149,7 +149,8 @@ size_t decode_exchange_bytes(int n_heads, int head_dim, int shards);
 int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, const float *part_ml,
                                 float *out, int n_heads, int head_dim, int splits,
                                 void *const *peer_ws, int shards, int rank, int phases,
-                                unsigned wait_limit_us, int *status);
+                                unsigned wait_limit_us, int *status,
+                                const DecodeParams *live_runs = nullptr);
 
 // Attention front end and tail (attn_front.cu).
 int launch_q_gate(cudaStream_t stream, const float *q, const float *gate, float *y, long long n);
