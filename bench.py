@@ -301,8 +301,9 @@ def prefill_parity_and_cpu(torch, pf: Prefill, sample_rows=24, threads=1):
 
 
 def decode_bench(torch, api, depths, steps, layers, hbm_gbs, reps=3):
-    """Single-stream greedy decode: per step and layer, quantise-append the new K/V row, then
-    split-K attention over depth+i+1 rows and the reduce. All steps of one depth are captured
+    """Single-stream greedy decode: per step and layer, quantise-append the new K/V row (inside
+    the split pass: hipml_attn_decode_kv_append), split-K attention over depth+i+1 rows and the
+    reduce: two launches per layer. All steps of one depth are captured
     in one CUDA graph (the reference replays a captured token graph, gpu/graph.rs:43-60), so
     the number is device time, not Python launch time."""
     import numpy as np
@@ -335,9 +336,8 @@ def decode_bench(torch, api, depths, steps, layers, hbm_gbs, reps=3):
         def token(i):
             splits = api.decode_splits(depth + i + 1)
             for l in range(layers):
-                api.kv_encode(step_buf[i], kn[i, l], vn[i, l], kc[l], vc[l], KV, D, stride)
-                api.attn_decode_kv(step_buf[i], q[i, l], kc[l], vc[l], acc, ml, out[i, l], H, KV, D,
-                                   stride, SCALE, splits)
+                api.attn_decode_kv_append(step_buf[i], kn[i, l], vn[i, l], q[i, l], kc[l], vc[l], acc, ml,
+                                          out[i, l], H, KV, D, stride, SCALE, splits)
 
         token(0)  # first-call setup happens outside the capture
         torch.cuda.synchronize()
@@ -377,7 +377,7 @@ def decode_bench(torch, api, depths, steps, layers, hbm_gbs, reps=3):
             "l2_assisted": bool(kv_bytes < 126e6 * 3),
             "parity": {"max_abs": O.max_abs(want, got), "rel_l2": O.rel_l2(want, got)},
             "cpu_tok_s_1core": 1.0 / (cpu_s * layers),
-            "launches_per_step": layers * 3,
+            "launches_per_step": layers * 2,
         })
         del kc, vc, graph
         torch.cuda.empty_cache()

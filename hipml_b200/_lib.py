@@ -73,6 +73,8 @@ SIGNATURES = {
     "hipml_kv_rows_copy": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "hipml_attn_decode_kv_gated": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _f, _i, _sz, _sz]),
+    "hipml_attn_decode_kv_append": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
+                                         _i, _i, _f, _i, _sz, _sz]),
     "hipml_attn_decode_kv_shard": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _f, _i, _sz, _sz]),
     "hipml_attn_decode_combine": (_i, [_vp, _vp, _vp, _i, _i, _i]),

@@ -88,6 +88,15 @@ def attn_decode_kv_gated(step, q, k, v, part_acc, part_ml, out, gate, n_heads, n
         _p(gate), n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
 
 
+def attn_decode_kv_append(step, k_row, v_row, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
+                          head_dim, stride, scale, splits, gate=None, selector=0, k_off=0, v_off=0):
+    """One decode step of a layer: append the K/V rows at step[0] (= step[1] - 1), then
+    attn_decode_kv (the append is fused into the split pass where that form exists)."""
+    _lib.check("attn_decode_kv_append", _lib.load().hipml_attn_decode_kv_append(
+        _stream(), _p(step), selector, _p(k_row), _p(v_row), _p(q), _p(k), _p(v), _p(part_acc),
+        _p(part_ml), _p(out), _p(gate), n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off))
+
+
 def attn_decode_kv_shard(step, q, k, v, part_acc, part_ml, shard_out, n_heads, n_kv, head_dim,
                          stride, scale, splits, selector=0, k_off=0, v_off=0):
     """One GPU's part of a sequence-split decode: writes [n_heads][head_dim+2] =

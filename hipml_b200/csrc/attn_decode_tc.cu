@@ -376,6 +376,14 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     const size_t head_byte = (size_t)slot * p.kv_slot_bytes + (size_t)kvh * p.stride * kSrcRow;
     const unsigned char *kbase = p.k + head_byte;
     const unsigned char *vbase = p.v + head_byte;
+    int append_pos = -1;
+    if (p.k_row != nullptr) {
+        append_pos = p.len[slot * p.len_stride + p.len_offset - 1];
+        // the fused form appends the last live row; anything else is the caller's error
+        if (split == 0 && kvh == 0 && tid == 0 &&
+            append_pos != p.len[slot * p.len_stride + p.len_offset] - 1 && status)
+            atomicCAS(status, 0, 22);
+    }
 
     // Ring: stage tile % 3; thread 0 arms the stage's barrier with the byte count and issues
     // the two copies. A stage is re-filled only after the __syncthreads that ends the tile
@@ -510,6 +518,27 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
             __syncthreads();
         }
         // (no barrier here for q8_0: every thread has seen the copy land for itself)
+        if constexpr (!kQ4) {
+            if (p.k_row != nullptr) {
+                // Fused append: the row at the append position was copied as it was before
+                // this step. Warp 0 (K) and warp 1 (V) quantise the new row into the tile, with
+                // the encoder's own arithmetic, and store the 272 bytes to the cache.
+                const int prow = append_pos - (lo + tile * kTile);
+                if (prow >= 0 && prow < nvalid) {
+                    if (warp < 2) {
+                        const float *src = (warp == 0 ? p.k_row : p.v_row) + (size_t)slot * p.row_slot +
+                                           (size_t)kvh * 256 + lane * 8;
+                        unsigned char *row = (warp == 0 ? ktile_b : vtile_b) + prow * kRowBytes;
+                        q8_put8(__ldg(reinterpret_cast<const float4 *>(src)),
+                                __ldg(reinterpret_cast<const float4 *>(src) + 1), lane, row);
+                        __syncwarp();
+                        row_store((warp == 0 ? p.kw : p.vw) + head_byte + (size_t)append_pos * kRowBytes, row,
+                                  kRowBytes, lane, 32);
+                    }
+                    __syncthreads();
+                }
+            }
+        }
         if (nvalid < kTile) {
             // Rows past the split's end hold stale bytes; their V scales must read as zero.
             for (int i = tid; i < (kTile - nvalid) * (kRowBytes / 16); i += kThreads)

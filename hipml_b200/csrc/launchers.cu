@@ -134,7 +134,8 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
                      const void *k, const void *v, float *part_acc, float *part_ml, float *out,
                      int n_heads, int n_kv, int head_dim, int stride, float scale, int splits,
                      size_t k_off, size_t v_off, bool shard, const ExchangeArgs *xch = nullptr,
-                     const float *gate = nullptr) {
+                     const float *gate = nullptr, const float *k_row = nullptr,
+                     const float *v_row = nullptr) {
     if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
     // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
     // experimental variants have no counterpart here.
@@ -188,6 +189,14 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     p.kv_slot_bytes = p.acc_slot = p.ml_slot = p.q_slot = 0;
     if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
+    if (k_row) {
+        // the caller checked that this combination has the fused form
+        p.k_row = k_row;
+        p.v_row = v_row;
+        p.kw = const_cast<unsigned char *>(p.k);
+        p.vw = const_cast<unsigned char *>(p.v);
+        p.row_slot = 0;
+    }
     if (tcgen05_body) {
         int *status = device_status_word();
         if (!status) return launch_status();
@@ -245,6 +254,33 @@ int hipml_attn_decode_kv_gated(hipml_stream_t stream, const int *step, int selec
     if (!gate) return fail(HIPML_ERR_INVALID_ARGUMENT, "gated decode: no gate row");
     return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
                      head_dim, stride, scale, splits, k_off, v_off, false, nullptr, gate);
+}
+
+int hipml_attn_decode_kv_append(hipml_stream_t stream, const int *step, int selector,
+                                const float *k_row, const float *v_row, const float *q, void *k,
+                                void *v, float *part_acc, float *part_ml, float *out,
+                                const float *gate, int n_heads, int n_kv, int head_dim, int stride,
+                                float scale, int splits, size_t k_off, size_t v_off) {
+    if (!k_row || !v_row) return fail(HIPML_ERR_INVALID_ARGUMENT, "decode with append: no K/V row");
+    if (((k_off | v_off) & 15) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "k_off/v_off must be multiples of 16 bytes");
+    unsigned char *kc = (unsigned char *)k + k_off, *vc = (unsigned char *)v + v_off;
+    const bool fused =
+        (selector == 0 || selector == 4) && head_dim == 256 &&
+        ((reinterpret_cast<size_t>(kc) | reinterpret_cast<size_t>(vc) | reinterpret_cast<size_t>(k_row) |
+          reinterpret_cast<size_t>(v_row)) & 15) == 0;
+    if (!fused) {
+        // any other selector, head size or alignment: the two launches the reference makes
+        const int dtype = selector == 1 ? 1 : 0;
+        if (selector != 0 && selector != 1 && selector != 4 && selector != 5 && selector != 6)
+            return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", selector);
+        if (int e = hipml_kv_encode(stream, step, dtype, k_row, v_row, kc, vc, n_kv, head_dim, stride))
+            return e;
+        return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
+                         head_dim, stride, scale, splits, k_off, v_off, false, nullptr, gate);
+    }
+    return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
+                     head_dim, stride, scale, splits, k_off, v_off, false, nullptr, gate, k_row, v_row);
 }
 
 int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selector,

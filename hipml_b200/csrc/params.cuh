@@ -26,6 +26,13 @@ struct DecodeParams {
     int share_slots;      // tensor-core body, several slots: the device's CTA slots, shared by
                           // all slots in proportion to their live lengths (0: off)
     int n_slots;          // set by launch_decode_tc
+    // Optional fused append (tensor-core body, q8_0): the new K/V rows of every slot, f32
+    // [n_kv][256] at k_row + slot * row_slot. The CTA whose run holds the append position
+    // (the int before the live length in `len`) quantises the row into its tile and stores
+    // it to the cache through kw / vw (the same addresses as k / v).
+    const float *k_row = nullptr, *v_row = nullptr;
+    unsigned char *kw = nullptr, *vw = nullptr;
+    long long row_slot = 0;
     long long kv_slot_bytes, acc_slot, ml_slot, q_slot;
 };
 // Live runs of one slot in the tensor-core split pass, in 64-key tiles: `runs` runs deal the

@@ -219,6 +219,20 @@ int hipml_attn_decode_kv_gated(hipml_stream_t stream, const int *step, int selec
                                float *out, const float *gate, int n_heads, int n_kv, int head_dim,
                                int stride, float scale, int splits, size_t k_off, size_t v_off);
 
+/* One decode step of a layer in one call: append the token's K/V rows (f32 [n_kv][head_dim]) at
+ * step[0], then hipml_attn_decode_kv over the step[1] live rows (the reference makes the two
+ * launches kv_encode_ptr_on + launch_ptrs, crates/hipml-model/src/gpu/attn_tile.rs:150-224).
+ * step[0] must be step[1] - 1 (device status 22 otherwise). With selector 0 / 4, head_dim 256
+ * and 16-byte aligned rows and caches the append happens inside the split pass -- the CTA
+ * whose run ends the sequence quantises the row into its tile and stores it to the cache,
+ * bit-identical to hipml_kv_encode -- otherwise the two launches are made here. `gate` is
+ * optional (NULL: none) and applied as in hipml_attn_decode_kv_gated. */
+int hipml_attn_decode_kv_append(hipml_stream_t stream, const int *step, int selector,
+                                const float *k_row, const float *v_row, const float *q, void *k,
+                                void *v, float *part_acc, float *part_ml, float *out,
+                                const float *gate, int n_heads, int n_kv, int head_dim, int stride,
+                                float scale, int splits, size_t k_off, size_t v_off);
+
 /* ---- Attention front end and tail (the callers either side of the attention kernels) ----
  * CPU definition: crates/hipml-core/src/ops.rs:181-187, 260-360, composed as in
  * attention.rs:117-143. q|gate rows are [n_heads][2*head_dim] (q half first), q / gate rows

@@ -346,3 +346,74 @@ def test_f32_cache_decode_columns(rows, pos0, n_ctx):
         for c in range(rows):
             want = O.attn_causal_f32(q[c], k, v, heads, n_kv, hd, pos0 + c + 1, float(scale))
             _assert_close(want, got[c])
+
+
+@pytest.mark.parametrize("seq", [1, 64, 65, 700, 5000])
+def test_decode_step_with_fused_append_equals_the_two_launches(seq):
+    """hipml_attn_decode_kv_append: the cache row it writes and the output are bit-identical
+    to hipml_kv_encode followed by hipml_attn_decode_kv, and nothing else in the cache moves."""
+    from hipml_b200 import api
+    heads, n_kv, hd, scale = 24, 4, 256, 0.0625
+    stride = seq + 9
+    rng = O.Rng(0xA99E + seq)
+    q = rng.normals(heads * hd)
+    k_row, v_row = rng.normals(n_kv * hd), rng.normals(n_kv * hd, 2.0)
+    kc, vc = _canary_cache(n_kv, stride, 272), _canary_cache(n_kv, stride, 272)
+    kc[:, :seq - 1] = O.quantize_q8(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, 272)
+    vc[:, :seq - 1] = O.quantize_q8(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, 272)
+    splits = api.decode_splits(seq)
+    step = _step(seq - 1, seq)
+
+    def scratch():
+        return (torch.full((heads * splits * hd,), float("nan"), device="cuda"),
+                torch.full((heads * splits * 2,), float("nan"), device="cuda"),
+                torch.full((heads * hd,), float("nan"), device="cuda"))
+
+    k1, v1 = _dev(kc), _dev(vc)
+    acc, ml, out1 = scratch()
+    api.kv_encode(step, _dev(k_row), _dev(v_row), k1, v1, n_kv, hd, stride)
+    api.attn_decode_kv(step, _dev(q), k1, v1, acc, ml, out1, heads, n_kv, hd, stride, scale, splits)
+    k2, v2 = _dev(kc), _dev(vc)
+    acc, ml, out2 = scratch()
+    api.attn_decode_kv_append(step, _dev(k_row), _dev(v_row), _dev(q), k2, v2, acc, ml, out2, heads,
+                              n_kv, hd, stride, scale, splits)
+    torch.cuda.synchronize()
+    assert api.check_device_status() == 0
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.equal(out1, out2)
+    kb, vb = k2.cpu().numpy().reshape(n_kv, stride, 272), v2.cpu().numpy().reshape(n_kv, stride, 272)
+    expected = O.attn_decode_kv_q8(q, kb, vb, heads, n_kv, hd, seq, scale, stride=stride)
+    _assert_close(expected, out2.cpu().numpy())
+
+
+def test_decode_step_with_append_other_shapes_and_misuse():
+    from hipml_b200 import api
+    # head_dim 64 has no fused form: the entry makes the two launches itself
+    heads, n_kv, hd, scale, seq = 8, 2, 64, 0.125, 37
+    rng = O.Rng(0xA99F)
+    q, k_row, v_row = rng.normals(heads * hd), rng.normals(n_kv * hd), rng.normals(n_kv * hd)
+    rowb = hd // 32 * 34
+    kc = np.zeros((n_kv, seq, rowb), dtype=np.uint8)
+    vc = np.zeros((n_kv, seq, rowb), dtype=np.uint8)
+    kc[:, :seq - 1] = O.quantize_q8(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, rowb)
+    vc[:, :seq - 1] = O.quantize_q8(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, rowb)
+    dk, dv = _dev(kc), _dev(vc)
+    out = torch.full((heads * hd,), float("nan"), device="cuda")
+    acc, ml = torch.empty(heads * hd, device="cuda"), torch.empty(heads * 2, device="cuda")
+    api.attn_decode_kv_append(_step(seq - 1, seq), _dev(k_row), _dev(v_row), _dev(q), dk, dv, acc, ml,
+                              out, heads, n_kv, hd, seq, scale, 1)
+    kc[:, seq - 1] = O.quantize_q8(k_row).reshape(n_kv, rowb)
+    vc[:, seq - 1] = O.quantize_q8(v_row).reshape(n_kv, rowb)
+    assert np.array_equal(dk.cpu().numpy().reshape(kc.shape), kc)
+    _assert_close(O.attn_decode_kv_q8(q, kc, vc, heads, n_kv, hd, seq, scale), out.cpu().numpy())
+    # the fused form appends the last live row only: anything else is flagged, not guessed
+    heads, n_kv, hd = 24, 4, 256
+    z = torch.zeros(heads * hd, device="cuda")
+    c = torch.zeros(n_kv * 16 * 272, dtype=torch.uint8, device="cuda")
+    acc, ml = torch.empty(heads * hd, device="cuda"), torch.empty(heads * 2, device="cuda")
+    assert api.check_device_status() == 0
+    api.attn_decode_kv_append(_step(3, 9), z[:n_kv * hd], z[:n_kv * hd], z, c, c.clone(), acc, ml,
+                              torch.empty_like(z), heads, n_kv, hd, 16, 0.0625, 1)
+    with pytest.raises(Exception, match="code 22"):
+        api.check_device_status()          # reports the code and clears the word
+    assert api.check_device_status() == 0
