@@ -448,7 +448,8 @@ def front_end_bench(torch, api, hbm_gbs, tokens=CHUNK, reps=5):
 def decode_batched(torch, api, slots_list, layers, hbm_gbs, steps=32, reps=3):
     """BASELINE configs[3]: multi-slot decode, B = 8 and 16, per-slot depth uniform in
     [512, 8192] from seed 3, one q8_0 region per slot in a contiguous cache (stride 8448).
-    One step = per layer kv_encode_rows + batched split pass + fold; `steps` steps are captured
+    One step = per layer hipml_attn_decode_batch_append (split pass with the slots' appends fused
+    in, then the fold); `steps` steps are captured
     in one CUDA graph. Every slot of the last step is checked against the oracle on layer 0."""
     import numpy as np
 
@@ -481,10 +482,9 @@ def decode_batched(torch, api, slots_list, layers, hbm_gbs, steps=32, reps=3):
 
         def token(i):
             for l in range(layers):
-                api.kv_encode_rows(kn[i, l], vn[i, l], kc[l], vc[l], KV, D, stride, pos[i], slot_bytes,
-                                   slots)
-                api.attn_decode_batch(pos[i], q[i, l], kc[l], vc[l], acc, ml, out[i, l], H, KV, D,
-                                      stride, SCALE, splits, slot_bytes, acc_slot, ml_slot, QW, slots, 0)
+                api.attn_decode_batch_append(pos[i], kn[i, l], vn[i, l], q[i, l], kc[l], vc[l], acc, ml,
+                                             out[i, l], H, KV, D, stride, SCALE, splits, slot_bytes,
+                                             acc_slot, ml_slot, QW, slots)
 
         token(0)
         torch.cuda.synchronize()

@@ -75,6 +75,8 @@ SIGNATURES = {
                                         _f, _i, _sz, _sz]),
     "hipml_attn_decode_kv_append": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                                          _i, _i, _f, _i, _sz, _sz]),
+    "hipml_attn_decode_batch_append": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
+                                            _i, _i, _f, _i, _i, _i, _i, _i, _i]),
     "hipml_attn_decode_kv_shard": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                         _f, _i, _sz, _sz]),
     "hipml_attn_decode_combine": (_i, [_vp, _vp, _vp, _i, _i, _i]),

@@ -177,6 +177,17 @@ def attn_decode_batch(pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads,
         q_slot, slots, live_seq))
 
 
+def attn_decode_batch_append(pos, k_f32, v_f32, q, k_cache, v_cache, part_acc, part_ml, out, n_heads,
+                             n_kv, head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot,
+                             q_slot, slots, dtype=0):
+    """One batched decode step of a layer: kv_encode_rows + attn_decode_rows, the append fused
+    into the split pass where that form exists."""
+    _lib.check("attn_decode_batch_append", _lib.load().hipml_attn_decode_batch_append(
+        _stream(), dtype, _p(pos), _p(k_f32), _p(v_f32), _p(q), _p(k_cache), _p(v_cache),
+        _p(part_acc), _p(part_ml), _p(out), n_heads, n_kv, head_dim, stride, scale, splits,
+        kv_slot_bytes, acc_slot, ml_slot, q_slot, slots))
+
+
 def attn_chunk_workspace_bytes(n_kv, head_dim, pos0, tokens) -> int:
     return int(_lib.load().hipml_attn_chunk_workspace_bytes(n_kv, head_dim, pos0, tokens))
 

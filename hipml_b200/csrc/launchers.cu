@@ -354,7 +354,8 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
                        const void *k_cache, const void *v_cache, float *part_acc, float *part_ml,
                        float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
                        int splits, int kv_slot_bytes, int acc_slot, int ml_slot, int q_slot,
-                       int slots, int by_stride) {
+                       int slots, int by_stride, const float *k_rows = nullptr,
+                       const float *v_rows = nullptr) {
     if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
     if (dtype != 0 && dtype != 1)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", dtype);
@@ -394,6 +395,16 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
         ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v) | (size_t)kv_slot_bytes) &
          15) == 0;
     const bool tensor_core = head_dim == 256 && aligned;
+    if (k_rows) {
+        // fused append (the caller checked that this combination has it)
+        if (!tensor_core || dtype != 0)
+            return fail(HIPML_ERR_INVALID_ARGUMENT, "decode with append: no fused form for this shape");
+        p.k_row = k_rows;
+        p.v_row = v_rows;
+        p.kw = const_cast<unsigned char *>(p.k);
+        p.vw = const_cast<unsigned char *>(p.v);
+        p.row_slot = (long long)n_kv * head_dim;
+    }
     if (int e = launch_decode_split(as_stream(stream), p, slots, tensor_core)) return e;
     return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim, splits,
                                 slots, acc_slot, ml_slot, q_slot, nullptr, tensor_core ? &p : nullptr);
@@ -457,6 +468,30 @@ int hipml_attn_decode_batch(hipml_stream_t stream, int dtype, const int *pos, co
     return decode_rows(stream, dtype, pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads,
                        n_kv, head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot,
                        q_slot, slots, 1);
+}
+
+int hipml_attn_decode_batch_append(hipml_stream_t stream, int dtype, const int *pos,
+                                   const float *k_f32, const float *v_f32, const float *q,
+                                   void *k_cache, void *v_cache, float *part_acc, float *part_ml,
+                                   float *out, int n_heads, int n_kv, int head_dim, int stride,
+                                   float scale, int splits, int kv_slot_bytes, int acc_slot,
+                                   int ml_slot, int q_slot, int slots) {
+    if (!k_f32 || !v_f32) return fail(HIPML_ERR_INVALID_ARGUMENT, "decode with append: no K/V rows");
+    const bool fused =
+        dtype == 0 && head_dim == 256 && slots > 0 &&
+        ((reinterpret_cast<size_t>(k_cache) | reinterpret_cast<size_t>(v_cache) | (size_t)kv_slot_bytes |
+          reinterpret_cast<size_t>(k_f32) | reinterpret_cast<size_t>(v_f32)) & 15) == 0;
+    if (!fused) {
+        if (int e = hipml_kv_encode_rows(stream, dtype, k_f32, v_f32, k_cache, v_cache, n_kv, head_dim,
+                                         stride, pos, kv_slot_bytes, slots))
+            return e;
+        return decode_rows(stream, dtype, pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads,
+                           n_kv, head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot,
+                           q_slot, slots, 1);
+    }
+    return decode_rows(stream, dtype, pos, q, k_cache, v_cache, part_acc, part_ml, out, n_heads, n_kv,
+                       head_dim, stride, scale, splits, kv_slot_bytes, acc_slot, ml_slot, q_slot,
+                       slots, 1, k_f32, v_f32);
 }
 
 size_t hipml_attn_chunk_workspace_bytes(int n_kv, int head_dim, int pos0, int tokens) {

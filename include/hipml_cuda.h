@@ -233,6 +233,17 @@ int hipml_attn_decode_kv_append(hipml_stream_t stream, const int *step, int sele
                                 const float *gate, int n_heads, int n_kv, int head_dim, int stride,
                                 float scale, int splits, size_t k_off, size_t v_off);
 
+/* One batched decode step of a layer in one call: hipml_kv_encode_rows (slot s appends row
+ * k_f32 + s*n_kv*head_dim at pos[2s], which must be pos[2s+1] - 1) then hipml_attn_decode_rows;
+ * with dtype 0, head_dim 256 and 16-byte aligned buffers the append happens inside the split
+ * pass, otherwise the two launches are made here. */
+int hipml_attn_decode_batch_append(hipml_stream_t stream, int dtype, const int *pos,
+                                   const float *k_f32, const float *v_f32, const float *q,
+                                   void *k_cache, void *v_cache, float *part_acc, float *part_ml,
+                                   float *out, int n_heads, int n_kv, int head_dim, int stride,
+                                   float scale, int splits, int kv_slot_bytes, int acc_slot,
+                                   int ml_slot, int q_slot, int slots);
+
 /* ---- Attention front end and tail (the callers either side of the attention kernels) ----
  * CPU definition: crates/hipml-core/src/ops.rs:181-187, 260-360, composed as in
  * attention.rs:117-143. q|gate rows are [n_heads][2*head_dim] (q half first), q / gate rows
@@ -332,9 +343,12 @@ int hipml_attn_decode_kv_static(hipml_stream_t stream, const int *step, int sele
 
 /* Launcher::attn_decode_rows_ptr (batch_launch.rs:213-316): multi-slot decode. Slot s reads
  * q + s*q_slot, caches + s*kv_slot_bytes, pos[2*s+1] as its live length, and writes
- * part_acc + s*acc_slot, part_ml + s*ml_slot, out + s*q_slot. The key axis is cut into
- * `splits` runs of ceil(stride/splits) rows fixed in cache positions; runs that start at or
- * beyond the live length write an empty partial (max = -inf, sum = 0). */
+ * part_acc + s*acc_slot, part_ml + s*ml_slot, out + s*q_slot. The partials are scratch of
+ * `splits` runs per head and slot. The reference cuts every slot's cache into `splits` runs of
+ * ceil(stride/splits) rows fixed in cache positions; at head_dim 256 with up to 64 slots this
+ * library instead reads the live lengths on the device and deals the batch's 64-key tiles out
+ * to one round of CTAs, each slot getting runs in proportion to its live length (still safe to
+ * replay from a captured graph: nothing of the plan is baked into the launch). */
 int hipml_attn_decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,
                            const void *k_cache, const void *v_cache, float *part_acc,
                            float *part_ml, float *out, int n_heads, int n_kv, int head_dim,

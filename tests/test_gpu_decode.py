@@ -417,3 +417,45 @@ def test_decode_step_with_append_other_shapes_and_misuse():
     with pytest.raises(Exception, match="code 22"):
         api.check_device_status()          # reports the code and clears the word
     assert api.check_device_status() == 0
+
+
+@pytest.mark.parametrize("slots", [3, 16])
+def test_batched_step_with_fused_append_equals_the_two_launches(slots):
+    from hipml_b200 import api
+    stride = 1024
+    heads, n_kv, hd, depths, q, kc, vc = _batch_setup(slots, stride, 0xBA + slots, 0, 1000)
+    rng = O.Rng(0xBA99 + slots)
+    k_new = rng.normals(slots * n_kv * hd).reshape(slots, n_kv * hd)
+    v_new = rng.normals(slots * n_kv * hd).reshape(slots, n_kv * hd)
+    splits = api.batch_splits(stride, slots)
+    slot_bytes = n_kv * stride * 272
+    acc_slot, ml_slot, q_slot = heads * splits * hd, heads * splits * 2, heads * hd
+    # the new row goes to position depth + 1 of every slot (rows 0..depth are live already)
+    pos = torch.tensor([[d + 1, d + 2] for d in depths], dtype=torch.int32, device="cuda")
+
+    def run(fused):
+        k, v = _dev(kc), _dev(vc)
+        out = torch.full((slots, q_slot), float("nan"), device="cuda")
+        acc = torch.empty(slots * acc_slot, device="cuda")
+        ml = torch.empty(slots * ml_slot, device="cuda")
+        if fused:
+            api.attn_decode_batch_append(pos, _dev(k_new), _dev(v_new), _dev(q), k, v, acc, ml, out,
+                                         heads, n_kv, hd, stride, 0.0625, splits, slot_bytes, acc_slot,
+                                         ml_slot, q_slot, slots)
+        else:
+            api.kv_encode_rows(_dev(k_new), _dev(v_new), k, v, n_kv, hd, stride, pos, slot_bytes, slots)
+            api.attn_decode_batch(pos, _dev(q), k, v, acc, ml, out, heads, n_kv, hd, stride, 0.0625,
+                                  splits, slot_bytes, acc_slot, ml_slot, q_slot, slots, 0)
+        torch.cuda.synchronize()
+        assert api.check_device_status() == 0
+        return k, v, out
+
+    k1, v1, out1 = run(False)
+    k2, v2, out2 = run(True)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.equal(out1, out2)
+    kb = k2.cpu().numpy().reshape(slots, n_kv, stride, 272)
+    vb = v2.cpu().numpy().reshape(slots, n_kv, stride, 272)
+    for s, d in enumerate(depths):
+        want = O.attn_decode_kv_q8(q[s], kb[s], vb[s], heads, n_kv, hd, d + 2, 0.0625, stride=stride)
+        _assert_close(want, out2.cpu().numpy()[s])
