@@ -243,6 +243,20 @@ Status launch_ptrs(const Launcher &l, size_t dtype, const void *q_ptr, const Buf
                                       (int)seq, scale, (int)std::max<size_t>(splits, 1), k_off, v_off));
 }
 
+Status step_ptrs(const Launcher &l, size_t dtype, const void *k_row, const void *v_row,
+                 const void *q_ptr, const Buffer &k, const Buffer &v, const Buffer &part_acc,
+                 const Buffer &part_ml, void *out_ptr, const void *gate, size_t n_heads, size_t n_kv,
+                 size_t head_dim, size_t seq, float scale, size_t splits, size_t k_off, size_t v_off) {
+    return check("attn_decode_kv_append",
+                 hipml_attn_decode_kv_append(l.stream(), (const int *)l.step_buf().as_ptr(), (int)dtype,
+                                             (const float *)k_row, (const float *)v_row,
+                                             (const float *)q_ptr, k.as_ptr(), v.as_ptr(),
+                                             (float *)part_acc.as_ptr(), (float *)part_ml.as_ptr(),
+                                             (float *)out_ptr, (const float *)gate, (int)n_heads,
+                                             (int)n_kv, (int)head_dim, (int)seq, scale,
+                                             (int)std::max<size_t>(splits, 1), k_off, v_off));
+}
+
 }  // namespace launch_kv
 
 // ---- DeepKv -----------------------------------------------------------------------------

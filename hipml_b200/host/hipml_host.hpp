@@ -113,6 +113,13 @@ Status launch_ptrs(const Launcher &l, size_t dtype, const void *q_ptr, const Buf
                    const Buffer &v, const Buffer &part_acc, const Buffer &part_ml, void *out_ptr,
                    size_t n_heads, size_t n_kv, size_t head_dim, size_t seq, float scale,
                    size_t splits, size_t k_off, size_t v_off);
+// One decode step of a layer: Launcher::kv_encode_ptr_on + launch_ptrs as
+// deep_attention makes them (crates/hipml-model/src/gpu/attn_tile.rs:150-224), in one call;
+// `gate` may be null. The append position step[0] must be step[1] - 1.
+Status step_ptrs(const Launcher &l, size_t dtype, const void *k_row, const void *v_row,
+                 const void *q_ptr, const Buffer &k, const Buffer &v, const Buffer &part_acc,
+                 const Buffer &part_ml, void *out_ptr, const void *gate, size_t n_heads, size_t n_kv,
+                 size_t head_dim, size_t seq, float scale, size_t splits, size_t k_off, size_t v_off);
 }  // namespace launch_kv
 
 // One layer's quantised K/V cache plus the split-K scratch (deep_kv.rs:11-99).

@@ -64,17 +64,23 @@ static void upload_cache(const std::vector<uint8_t> &bytes, Buffer &out, Status 
     if (st.empty()) st = out.upload_bytes(0, bytes.data(), bytes.size());
 }
 
+// dtype: KvDtype::id(), 0 = q8_0, 1 = q4_0 (parity_kv.rs:68-246)
 static void kv_case(Launcher &l, const char *name, size_t heads, size_t n_kv, size_t dim, size_t seq,
-                    size_t splits, float scale, uint64_t seed) {
+                    size_t splits, float scale, uint64_t seed, size_t dtype = 0) {
     uint64_t rng = hipml_oracle_rng_new(seed);
     std::vector<float> q = normals(rng, heads * dim);
     std::vector<float> kf = normals(rng, n_kv * seq * dim, 0.3f), vf = normals(rng, n_kv * seq * dim);
-    std::vector<uint8_t> kb(kf.size() / 32 * 34), vb(kb.size());
-    hipml_oracle_quantize_q8(kf.data(), kf.size(), kb.data());
-    hipml_oracle_quantize_q8(vf.data(), vf.size(), vb.data());
+    std::vector<uint8_t> kb(kf.size() / 32 * (dtype ? 18 : 34)), vb(kb.size());
+    if (dtype) {
+        hipml_oracle_quantize_q4(kf.data(), kf.size(), kb.data());
+        hipml_oracle_quantize_q4(vf.data(), vf.size(), vb.data());
+    } else {
+        hipml_oracle_quantize_q8(kf.data(), kf.size(), kb.data());
+        hipml_oracle_quantize_q8(vf.data(), vf.size(), vb.data());
+    }
     std::vector<float> want(heads * dim);
-    hipml_oracle_attn_decode_kv_q8(q.data(), kb.data(), vb.data(), (int)heads, (int)n_kv, (int)dim,
-                                   (int)seq, scale, want.data());
+    hipml_oracle_attn_decode_kv_strided(q.data(), kb.data(), vb.data(), (int)dtype, (int)heads, (int)n_kv,
+                                        (int)dim, (int)seq, (int)seq, scale, want.data());
     Buffer dq, dk, dv, out, acc, ml;
     Status st;
     OK(Buffer::from_host(q.data(), q.size(), dq));
@@ -86,11 +92,65 @@ static void kv_case(Launcher &l, const char *name, size_t heads, size_t n_kv, si
     OK(Buffer::alloc(heads * splits * dim, acc));
     OK(Buffer::alloc(heads * splits * 2, ml));
     OK(l.set_step(seq - 1, seq, 0));  // launch_kv.rs:35-41: the count comes from the step buffer
-    OK(launch_kv::launch(l, 0, dq, dk, dv, acc, ml, out, heads, n_kv, dim, seq, scale, splits, 0, 0));
+    OK(launch_kv::launch(l, dtype, dq, dk, dv, acc, ml, out, heads, n_kv, dim, seq, scale, splits, 0, 0));
     OK(l.synchronize());
     std::vector<float> got;
     OK(out.to_host(got));
     report(name, want, got, DEFAULT);
+}
+
+// One decode step in one call (append + attention) against the two launches of the
+// reference's deep_attention: the cache row and the output must be identical.
+static void decode_step_case(Launcher &l) {
+    const size_t heads = 24, n_kv = 4, dim = 256, seq = 700, stride = 712, row = 272;
+    const float scale = 0.0625f;
+    uint64_t rng = hipml_oracle_rng_new(0xA99E0001ULL);
+    std::vector<float> q = normals(rng, heads * dim), kr = normals(rng, n_kv * dim), vr = normals(rng, n_kv * dim);
+    std::vector<float> kf = normals(rng, n_kv * stride * dim), vf = normals(rng, n_kv * stride * dim);
+    std::vector<uint8_t> kb(n_kv * stride * row), vb(kb.size());
+    hipml_oracle_quantize_q8(kf.data(), kf.size(), kb.data());
+    hipml_oracle_quantize_q8(vf.data(), vf.size(), vb.data());
+    DeepKv shape;
+    Config cfg;
+    OK(DeepKv::create(cfg, stride, KvDtype::Q8, shape));
+    const size_t splits = shape.splits(seq);
+    Buffer dq, dkr, dvr, acc, ml;
+    OK(Buffer::from_host(q.data(), q.size(), dq));
+    OK(Buffer::from_host(kr.data(), kr.size(), dkr));
+    OK(Buffer::from_host(vr.data(), vr.size(), dvr));
+    OK(Buffer::alloc(heads * splits * dim, acc));
+    OK(Buffer::alloc(heads * splits * 2, ml));
+    OK(l.set_step(seq - 1, seq, 0));
+    std::vector<float> outs[2];
+    std::vector<uint8_t> rows[2];
+    for (int fused = 0; fused < 2; fused++) {
+        Buffer dk, dv, out;
+        Status st;
+        upload_cache(kb, dk, st);
+        OK(st);
+        upload_cache(vb, dv, st);
+        OK(st);
+        OK(Buffer::alloc(heads * dim, out));
+        if (fused) {
+            OK(launch_kv::step_ptrs(l, 0, dkr.as_ptr(), dvr.as_ptr(), dq.as_ptr(), dk, dv, acc, ml,
+                                    out.as_ptr(), nullptr, heads, n_kv, dim, stride, scale, splits, 0, 0));
+        } else {
+            OK(l.kv_encode(0, dkr, dvr, dk, dv, n_kv, dim, stride));
+            OK(launch_kv::launch(l, 0, dq, dk, dv, acc, ml, out, heads, n_kv, dim, stride, scale, splits, 0, 0));
+        }
+        OK(l.synchronize());
+        OK(out.to_host(outs[fused]));
+        rows[fused].resize(2 * n_kv * row);
+        for (size_t h = 0; h < n_kv; h++) {
+            OK(dk.download_bytes((h * stride + seq - 1) * row, rows[fused].data() + h * row, row));
+            OK(dv.download_bytes((h * stride + seq - 1) * row, rows[fused].data() + (n_kv + h) * row, row));
+        }
+    }
+    const bool same_rows = rows[0] == rows[1];
+    printf("%s decode step: appended rows identical\n", same_rows ? "PASS" : "FAIL");
+    g_ran++;
+    g_failed += !same_rows;
+    report("decode step (append fused) vs two launches", outs[0], outs[1], EXACT);
 }
 
 static void kv_encode_case(Launcher &l) {
@@ -377,7 +437,15 @@ int main(int argc, char **argv) {
     kv_case(l, "attn_decode_kv_q8_hd256_s4096", 6, 1, 256, 4096, 16, 0.0625f, 0x9E000004);
     kv_case(l, "attn_decode_kv_q8_hd64_s37", 8, 2, 64, 37, 1, 0.125f, 0x9E000009);
     kv_case(l, "attn_decode_kv_q8_hd64_s1000", 8, 2, 64, 1000, 7, 0.125f, 0x9E00000A);
+    kv_case(l, "attn_decode_kv_q4_hd256_s1", 6, 1, 256, 1, 1, 0.0625f, 0x9E000005, 1);
+    kv_case(l, "attn_decode_kv_q4_hd256_s37", 6, 1, 256, 37, 1, 0.0625f, 0x9E000006, 1);
+    kv_case(l, "attn_decode_kv_q4_hd256_s1000", 6, 1, 256, 1000, 7, 0.0625f, 0x9E000007, 1);
+    kv_case(l, "attn_decode_kv_q4_hd256_s4096", 6, 1, 256, 4096, 16, 0.0625f, 0x9E000008, 1);
+    kv_case(l, "attn_decode_kv_q4_hd64_s37", 8, 2, 64, 37, 1, 0.125f, 0x9E00000B, 1);
+    kv_case(l, "attn_decode_kv_q4_hd64_s1000", 8, 2, 64, 1000, 7, 0.125f, 0x9E00000C, 1);
     if (deep) kv_case(l, "attn_decode_kv_q8_hd256_s100000", 1, 1, 256, 100000, 256, 0.0625f, 0x9E001001);
+    if (deep) kv_case(l, "attn_decode_kv_q4_hd256_s100000", 1, 1, 256, 100000, 64, 0.0625f, 0x9E001002, 1);
+    decode_step_case(l);
     decode_pm_f32_case(l);
     chunk_case(l, "chunk_attention 37@29 f32", 0, 1);
     chunk_case(l, "chunk_attention 37@29 q8", 1, 1);

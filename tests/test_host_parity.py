@@ -46,4 +46,4 @@ def test_parity_table_passes_on_the_device():
     r = subprocess.run([exe, "--deep"], capture_output=True, text=True, timeout=600)
     print(r.stdout)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "FAIL" not in r.stdout and "22 cases, 0 failed" in r.stdout
+    assert "FAIL" not in r.stdout and "31 cases, 0 failed" in r.stdout
