@@ -277,13 +277,126 @@ __device__ __forceinline__ void values_block(const unsigned char *vtile, int blk
     }
 }
 
-// kQ4: the cache is q4_0 (144-byte rows). A tile's raw rows are copied into the upper part of
-// its stage and expanded in place into the q8_0 row image (scale + 32 signed codes = nibble
-// - 8) that the three phases read, through registers: every thread first loads its blocks,
-// the CTA synchronises, then the expanded blocks are written (the two regions overlap).
-constexpr int kQ4RowBytes = 8 * kQ4BlockBytes;                 // 144
-constexpr int kQ4RawOffset = kTileBytes - kTile * kQ4RowBytes; // 8192: raw tile at the stage's end
+// ---- q4_0 rows read in place (144-byte rows of 18-byte blocks: f16 scale, then 16 bytes
+// whose low nibbles are values 0..15 and high nibbles values 16..31, each value + 8).
+constexpr int kQ4RowBytes = 8 * kQ4BlockBytes;   // 144 = 36 words; a block pair is 9 words
 
+// K side: the four "logical words" of block BLK (four code bytes each), aligned loads only.
+// Odd blocks start on a word boundary after their scale's half word; even blocks hold bytes
+// 2..13 in three aligned words and bytes 0, 1, 14, 15 in the two words they share with the
+// scales, stitched into the fourth. The contraction order is free (the query follows it).
+template <int BLK>
+__device__ __forceinline__ unsigned k_word_q4(const unsigned *row, int t) {
+    constexpr int m = BLK >> 1;
+    if constexpr (BLK & 1) {
+        return row[9 * m + 5 + t];
+    } else {
+        const bool last = t == 3;
+        const unsigned a = row[last ? 9 * m : 9 * m + 1 + t];
+        const unsigned b = row[last ? 9 * m + 4 : 9 * m + 1 + t];
+        return __byte_perm(a, b, last ? 0x5432 : 0x3210);
+    }
+}
+// head_dim index of byte i of logical word j (low nibble; the high nibble is 16 further).
+__device__ __forceinline__ int k_word_dim_q4(int blk, int j, int i) {
+    if (blk & 1) return blk * 32 + 4 * j + i;
+    if (j < 3) return blk * 32 + 4 * j + 2 + i;
+    return blk * 32 + (i < 2 ? i : 12 + i);
+}
+
+// Scores of one q4_0 block for this warp's 16 keys: as score_block, with step 0 of the
+// contraction over the low nibbles (values 0..15 of the block) and step 1 over the high ones.
+// A nibble is value + 8, an f16 subnormal as it stands: no XOR, offset 8.
+template <int BLK>
+__device__ __forceinline__ void score_block_q4(const unsigned char *ktile, int key_base, int g, int t,
+                                               const unsigned (&qb0)[4], const unsigned (&qb1)[4],
+                                               const float (&bias)[2], float (&s)[4]) {
+    const unsigned *row0 = reinterpret_cast<const unsigned *>(ktile + (key_base + g) * kQ4RowBytes);
+    const unsigned *row1 = row0 + 8 * (kQ4RowBytes / 4);
+    float c[4] = {bias[0], bias[1], bias[0], bias[1]};
+    const unsigned w0 = k_word_q4<BLK>(row0, t), w1 = k_word_q4<BLK>(row1, t);
+    {
+        const unsigned x0 = w0 & 0x0f0f0f0fu, x1 = w1 & 0x0f0f0f0fu;
+        const unsigned a[4] = {codes_to_half2(x0, 0x4140), codes_to_half2(x1, 0x4140),
+                               codes_to_half2(x0, 0x4342), codes_to_half2(x1, 0x4342)};
+        mma_16816(c, a, qb0[0], qb0[1]);
+        mma_16816(c, a, qb0[2], qb0[3]);
+    }
+    {
+        const unsigned x0 = (w0 >> 4) & 0x0f0f0f0fu, x1 = (w1 >> 4) & 0x0f0f0f0fu;
+        const unsigned a[4] = {codes_to_half2(x0, 0x4140), codes_to_half2(x1, 0x4140),
+                               codes_to_half2(x0, 0x4342), codes_to_half2(x1, 0x4342)};
+        mma_16816(c, a, qb1[0], qb1[1]);
+        mma_16816(c, a, qb1[2], qb1[3]);
+    }
+    const unsigned char *sc = ktile + (key_base + g) * kQ4RowBytes + BLK * kQ4BlockBytes;
+    const float d0 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(sc));
+    const float d1 = half_bits_to_float(*reinterpret_cast<const unsigned short *>(sc + 8 * kQ4RowBytes));
+    s[0] += d0 * c[0];
+    s[1] += d0 * c[1];
+    s[2] += d1 * c[2];
+    s[3] += d1 * c[3];
+}
+
+// Values of one tile for q4_0 block `blk`: as values_block. Lane group g takes code word g & 3
+// (natural order: values 4(g&3) .. +3 in the low nibbles, 16 further in the high ones) and the
+// nibble half g >> 2, so output column n of MMA i is dim 32*blk + 4n + i as for q8_0.
+// 0x6400 | nibble is 1024 + value + 8, minus 1032: exact.
+template <bool kOdd>
+__device__ __forceinline__ void values_block_q4(const unsigned char *vtile, int blk, int g, int t,
+                                                const __half *ph, const __half *pl, float corr,
+                                                float (&acc)[4][4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[i][c] *= corr;
+    const unsigned char *scale0 = vtile + 2 * t * kQ4RowBytes + blk * kQ4BlockBytes;
+    const unsigned *code0 = reinterpret_cast<const unsigned *>(scale0 + (kOdd ? 2 : 0)) + (g & 3);
+    const int shift = (g >> 2) * 4;
+    const __half *ph0 = ph + g * kPStride + 2 * t, *pl0 = pl + g * kPStride + 2 * t;
+    constexpr int kRowWords = kQ4RowBytes / 4;
+    const __half2 off = __half2half2(__ushort_as_half(0x6408));   // 1032
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++) {
+        constexpr int kOff[4] = {0, 1, 8, 9};
+        __half dv[4];
+        unsigned w[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            dv[e] = __ushort_as_half(*reinterpret_cast<const unsigned short *>(
+                scale0 + (ks * 16 + kOff[e]) * kQ4RowBytes));
+            w[e] = (v_word<kOdd>(code0 + (ks * 16 + kOff[e]) * kRowWords, 0) >> shift) & 0x0f0f0f0fu;
+        }
+        const __half2 d01 = __halves2half2(dv[0], dv[1]), d23 = __halves2half2(dv[2], dv[3]);
+        const __half2 ph01 = *reinterpret_cast<const __half2 *>(ph0 + ks * 16);
+        const __half2 ph23 = *reinterpret_cast<const __half2 *>(ph0 + ks * 16 + 8);
+        const __half2 pl01 = *reinterpret_cast<const __half2 *>(pl0 + ks * 16);
+        const __half2 pl23 = *reinterpret_cast<const __half2 *>(pl0 + ks * 16 + 8);
+        const __half2 h01 = __hmul2(ph01, d01), h23 = __hmul2(ph23, d23);
+        const __half2 l01 = __hfma2(pl01, d01, __hfma2(ph01, d01, __hneg2(h01)));
+        const __half2 l23 = __hfma2(pl23, d23, __hfma2(ph23, d23, __hneg2(h23)));
+        unsigned afrag[4];
+        afrag[0] = *reinterpret_cast<const unsigned *>(&h01);
+        afrag[1] = *reinterpret_cast<const unsigned *>(&l01);
+        afrag[2] = *reinterpret_cast<const unsigned *>(&h23);
+        afrag[3] = *reinterpret_cast<const unsigned *>(&l23);
+        const unsigned ab01 = __byte_perm(w[0], w[1], 0x5140);  // [a0 b0 a1 b1]
+        const unsigned ab23 = __byte_perm(w[0], w[1], 0x7362);  // [a2 b2 a3 b3]
+        const unsigned cd01 = __byte_perm(w[2], w[3], 0x5140);
+        const unsigned cd23 = __byte_perm(w[2], w[3], 0x7362);
+        auto conv = [&](unsigned x, unsigned sel) {
+            const unsigned h = __byte_perm(x, 0x64646464u, sel);
+            const __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&h), off);
+            return *reinterpret_cast<const unsigned *>(&r);
+        };
+        mma_16816(acc[0], afrag, conv(ab01, 0x4140), conv(cd01, 0x4140));
+        mma_16816(acc[1], afrag, conv(ab01, 0x4342), conv(cd01, 0x4342));
+        mma_16816(acc[2], afrag, conv(ab23, 0x4140), conv(cd23, 0x4140));
+        mma_16816(acc[3], afrag, conv(ab23, 0x4342), conv(cd23, 0x4342));
+    }
+}
+
+// kQ4: the cache is q4_0; the phases read the 144-byte rows as they were copied.
 template <bool kQ4>
 __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int *status) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -394,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         const int r0 = lo + tile * kTile;
         const unsigned bytes = (unsigned)(min(kTile, hi - r0) * kSrcRow);
         const size_t off = (size_t)r0 * kSrcRow;
-        constexpr int kDst = kQ4 ? kQ4RawOffset : 0;
+        constexpr int kDst = 0;
         // earlier generic-proxy writes to the stage (zero fill, query staging) come first
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * bytes);
@@ -426,7 +539,8 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         __half xh[4], xl[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const float x = qs[g * 256 + k_word_dim(blk, j, i)];
+            const float x = qs[g * 256 + (kQ4 ? k_word_dim_q4(blk, t, i) + 16 * (ks & 1)
+                                              : k_word_dim(blk, j, i))];
             xh[i] = __float2half_rn(x);
             xl[i] = __float2half_rn(x - __half2float(xh[i]));
         }
@@ -445,7 +559,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
             const float xh = __half2float(__float2half_rn(x));
             sum += xh + __half2float(__float2half_rn(x - xh));
         }
-        qsum_s[tid] = -kCodeBias * sum;
+        qsum_s[tid] = -(kQ4 ? kCodeBias / 16.0f : kCodeBias) * sum;   // nibbles carry an offset of 8
     }
     __syncthreads();
     float qbias[4][2];
@@ -483,41 +597,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         }
         const int nvalid = min(kTile, hi - (lo + tile * kTile));
         unsigned char *const ktile_b = ktile_at(buf), *const vtile_b = vtile_at(buf);
-        if constexpr (kQ4) {
-            // expand the raw q4_0 rows into the q8_0 row image: 64 rows x 8 blocks x {K, V} =
-            // 1024 blocks, four per thread; rows past the split's end are left alone
-            unsigned short raw[4][9];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int item = tid + kThreads * i, row = (item & 511) >> 3, blk = item & 7;
-                const unsigned char *src = (item < 512 ? ktile_b : vtile_b) + kQ4RawOffset +
-                                           row * kQ4RowBytes + blk * kQ4BlockBytes;
-#pragma unroll
-                for (int w = 0; w < 9; w++) raw[i][w] = reinterpret_cast<const unsigned short *>(src)[w];
-            }
-            __syncthreads();
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int item = tid + kThreads * i, row = (item & 511) >> 3, blk = item & 7;
-                if (row >= nvalid) continue;
-                unsigned short *dst = reinterpret_cast<unsigned short *>(
-                    (item < 512 ? ktile_b : vtile_b) + row * kRowBytes + blk * kQ8BlockBytes);
-                dst[0] = raw[i][0];
-#pragma unroll
-                for (int w = 0; w < 8; w += 2) {
-                    // bytes 2w..2w+3 of the block: low nibbles are values 2w.., high nibbles 16+2w..
-                    const unsigned pair = raw[i][1 + w] | ((unsigned)raw[i][2 + w] << 16);
-                    const unsigned lo = __vsub4(pair & 0x0f0f0f0fu, 0x08080808u);
-                    const unsigned hi4 = __vsub4((pair >> 4) & 0x0f0f0f0fu, 0x08080808u);
-                    dst[1 + w] = (unsigned short)lo;
-                    dst[2 + w] = (unsigned short)(lo >> 16);
-                    dst[9 + w] = (unsigned short)hi4;
-                    dst[10 + w] = (unsigned short)(hi4 >> 16);
-                }
-            }
-            __syncthreads();
-        }
-        // (no barrier here for q8_0: every thread has seen the copy land for itself)
+        // (no barrier here: every thread has seen the copy land for itself)
         if constexpr (!kQ4) {
             if (p.k_row != nullptr) {
                 // Fused append: the row at the append position was copied as it was before
@@ -541,14 +621,26 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         }
         if (nvalid < kTile) {
             // Rows past the split's end hold stale bytes; their V scales must read as zero.
-            for (int i = tid; i < (kTile - nvalid) * (kRowBytes / 16); i += kThreads)
-                reinterpret_cast<uint4 *>(vtile_b + nvalid * kRowBytes)[i] = make_uint4(0, 0, 0, 0);
+            for (int i = tid; i < (kTile - nvalid) * (kSrcRow / 16); i += kThreads)
+                reinterpret_cast<uint4 *>(vtile_b + nvalid * kSrcRow)[i] = make_uint4(0, 0, 0, 0);
         }
 
         // ---- (1) scores
         {
             float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (dh == 0) {
+            if constexpr (kQ4) {
+                if (dh == 0) {
+                    score_block_q4<0>(ktile_b, kg * 16, g, t, qb[0], qb[1], qbias[0], s);
+                    score_block_q4<1>(ktile_b, kg * 16, g, t, qb[2], qb[3], qbias[1], s);
+                    score_block_q4<2>(ktile_b, kg * 16, g, t, qb[4], qb[5], qbias[2], s);
+                    score_block_q4<3>(ktile_b, kg * 16, g, t, qb[6], qb[7], qbias[3], s);
+                } else {
+                    score_block_q4<4>(ktile_b, kg * 16, g, t, qb[0], qb[1], qbias[0], s);
+                    score_block_q4<5>(ktile_b, kg * 16, g, t, qb[2], qb[3], qbias[1], s);
+                    score_block_q4<6>(ktile_b, kg * 16, g, t, qb[4], qb[5], qbias[2], s);
+                    score_block_q4<7>(ktile_b, kg * 16, g, t, qb[6], qb[7], qbias[3], s);
+                }
+            } else if (dh == 0) {
                 score_block<0>(ktile_b, kg * 16, g, t, qb[0], qb[1], qbias[0], s);
                 score_block<1>(ktile_b, kg * 16, g, t, qb[2], qb[3], qbias[1], s);
                 score_block<2>(ktile_b, kg * 16, g, t, qb[4], qb[5], qbias[2], s);
@@ -591,10 +683,16 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         __syncthreads();
 
         // ---- (3) values: warp = block (32 dims), all 64 keys
-        if (warp & 1)
+        if constexpr (kQ4) {
+            if (warp & 1)
+                values_block_q4<true>(vtile_b, warp, g, t, ph, pl, corr_s[g], acc);
+            else
+                values_block_q4<false>(vtile_b, warp, g, t, ph, pl, corr_s[g], acc);
+        } else if (warp & 1) {
             values_block<true>(vtile_b, warp, g, t, ph, pl, corr_s[g], acc);
-        else
+        } else {
             values_block<false>(vtile_b, warp, g, t, ph, pl, corr_s[g], acc);
+        }
         __syncthreads();  // tile buffers, ss and the weight tile are reused by the next tile
     }
 
