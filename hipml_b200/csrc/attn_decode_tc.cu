@@ -598,25 +598,27 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         const int nvalid = min(kTile, hi - (lo + tile * kTile));
         unsigned char *const ktile_b = ktile_at(buf), *const vtile_b = vtile_at(buf);
         // (no barrier here: every thread has seen the copy land for itself)
-        if constexpr (!kQ4) {
-            if (p.k_row != nullptr) {
-                // Fused append: the row at the append position was copied as it was before
-                // this step. Warp 0 (K) and warp 1 (V) quantise the new row into the tile, with
-                // the encoder's own arithmetic, and store the 272 bytes to the cache.
-                const int prow = append_pos - (lo + tile * kTile);
-                if (prow >= 0 && prow < nvalid) {
-                    if (warp < 2) {
-                        const float *src = (warp == 0 ? p.k_row : p.v_row) + (size_t)slot * p.row_slot +
-                                           (size_t)kvh * 256 + lane * 8;
-                        unsigned char *row = (warp == 0 ? ktile_b : vtile_b) + prow * kRowBytes;
-                        q8_put8(__ldg(reinterpret_cast<const float4 *>(src)),
-                                __ldg(reinterpret_cast<const float4 *>(src) + 1), lane, row);
-                        __syncwarp();
-                        row_store((warp == 0 ? p.kw : p.vw) + head_byte + (size_t)append_pos * kRowBytes, row,
-                                  kRowBytes, lane, 32);
-                    }
-                    __syncthreads();
+        if (p.k_row != nullptr) {
+            // Fused append: the row at the append position was copied as it was before this
+            // step. Warp 0 (K) and warp 1 (V) quantise the new row into the tile, with the
+            // encoder's own arithmetic, and store its bytes to the cache.
+            const int prow = append_pos - (lo + tile * kTile);
+            if (prow >= 0 && prow < nvalid) {
+                if (warp < 2) {
+                    const float *src = (warp == 0 ? p.k_row : p.v_row) + (size_t)slot * p.row_slot +
+                                       (size_t)kvh * 256 + lane * 8;
+                    unsigned char *row = (warp == 0 ? ktile_b : vtile_b) + prow * kSrcRow;
+                    const float4 a = __ldg(reinterpret_cast<const float4 *>(src));
+                    const float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+                    if constexpr (kQ4)
+                        q4_put8(a, b, lane, row);
+                    else
+                        q8_put8(a, b, lane, row);
+                    __syncwarp();
+                    row_store((warp == 0 ? p.kw : p.vw) + head_byte + (size_t)append_pos * kSrcRow, row,
+                              kSrcRow, lane, 32);
                 }
+                __syncthreads();
             }
         }
         if (nvalid < kTile) {

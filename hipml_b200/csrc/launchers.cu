@@ -266,7 +266,7 @@ int hipml_attn_decode_kv_append(hipml_stream_t stream, const int *step, int sele
         return fail(HIPML_ERR_INVALID_ARGUMENT, "k_off/v_off must be multiples of 16 bytes");
     unsigned char *kc = (unsigned char *)k + k_off, *vc = (unsigned char *)v + v_off;
     const bool fused =
-        (selector == 0 || selector == 4) && head_dim == 256 &&
+        (selector == 0 || selector == 1 || selector == 4) && head_dim == 256 &&
         ((reinterpret_cast<size_t>(kc) | reinterpret_cast<size_t>(vc) | reinterpret_cast<size_t>(k_row) |
           reinterpret_cast<size_t>(v_row)) & 15) == 0;
     if (!fused) {
@@ -397,7 +397,7 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
     const bool tensor_core = head_dim == 256 && aligned;
     if (k_rows) {
         // fused append (the caller checked that this combination has it)
-        if (!tensor_core || dtype != 0)
+        if (!tensor_core)
             return fail(HIPML_ERR_INVALID_ARGUMENT, "decode with append: no fused form for this shape");
         p.k_row = k_rows;
         p.v_row = v_rows;
@@ -478,7 +478,7 @@ int hipml_attn_decode_batch_append(hipml_stream_t stream, int dtype, const int *
                                    int ml_slot, int q_slot, int slots) {
     if (!k_f32 || !v_f32) return fail(HIPML_ERR_INVALID_ARGUMENT, "decode with append: no K/V rows");
     const bool fused =
-        dtype == 0 && head_dim == 256 && slots > 0 &&
+        (dtype == 0 || dtype == 1) && head_dim == 256 && slots > 0 &&
         ((reinterpret_cast<size_t>(k_cache) | reinterpret_cast<size_t>(v_cache) | (size_t)kv_slot_bytes |
           reinterpret_cast<size_t>(k_f32) | reinterpret_cast<size_t>(v_f32)) & 15) == 0;
     if (!fused) {

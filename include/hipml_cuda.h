@@ -222,7 +222,7 @@ int hipml_attn_decode_kv_gated(hipml_stream_t stream, const int *step, int selec
 /* One decode step of a layer in one call: append the token's K/V rows (f32 [n_kv][head_dim]) at
  * step[0], then hipml_attn_decode_kv over the step[1] live rows (the reference makes the two
  * launches kv_encode_ptr_on + launch_ptrs, crates/hipml-model/src/gpu/attn_tile.rs:150-224).
- * step[0] must be step[1] - 1 (device status 22 otherwise). With selector 0 / 4, head_dim 256
+ * step[0] must be step[1] - 1 (device status 22 otherwise). With selector 0 / 1 / 4, head_dim 256
  * and 16-byte aligned rows and caches the append happens inside the split pass -- the CTA
  * whose run ends the sequence quantises the row into its tile and stores it to the cache,
  * bit-identical to hipml_kv_encode -- otherwise the two launches are made here. `gate` is
@@ -235,7 +235,7 @@ int hipml_attn_decode_kv_append(hipml_stream_t stream, const int *step, int sele
 
 /* One batched decode step of a layer in one call: hipml_kv_encode_rows (slot s appends row
  * k_f32 + s*n_kv*head_dim at pos[2s], which must be pos[2s+1] - 1) then hipml_attn_decode_rows;
- * with dtype 0, head_dim 256 and 16-byte aligned buffers the append happens inside the split
+ * with dtype 0 / 1, head_dim 256 and 16-byte aligned buffers the append happens inside the split
  * pass, otherwise the two launches are made here. */
 int hipml_attn_decode_batch_append(hipml_stream_t stream, int dtype, const int *pos,
                                    const float *k_f32, const float *v_f32, const float *q,

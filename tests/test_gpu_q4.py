@@ -300,3 +300,43 @@ def test_chunk_2048_rows_at_6144_over_q4_sampled_rows():
     assert not np.isnan(got).any()
     ok, ma, rl = cases.attention_within_bar(want[5::97], got[5::97])
     assert ok, (ma, rl)
+
+
+@pytest.mark.parametrize("seq", [1, 65, 700])
+def test_decode_step_with_fused_append_equals_the_two_launches(seq):
+    """hipml_attn_decode_kv_append over a q4_0 cache: row bytes and output identical to
+    hipml_kv_encode + hipml_attn_decode_kv."""
+    from hipml_b200 import api
+    heads, n_kv, hd, scale, row = 24, 4, 256, 0.0625, 144
+    stride = seq + 9
+    rng = O.Rng(0xA994 + seq)
+    q = rng.normals(heads * hd)
+    k_row, v_row = rng.normals(n_kv * hd), rng.normals(n_kv * hd, 2.0)
+    kc, vc = _poison_cache(n_kv, stride, hd), _poison_cache(n_kv, stride, hd)
+    kc[:, :seq - 1] = O.quantize_q4(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, row)
+    vc[:, :seq - 1] = O.quantize_q4(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, row)
+    splits = api.decode_splits(seq)
+    step = _step(seq - 1, seq)
+    outs, caches = [], []
+    for fused in (False, True):
+        k, v = _dev(kc), _dev(vc)
+        out = torch.full((heads * hd,), float("nan"), device="cuda")
+        acc = torch.empty(heads * splits * hd, device="cuda")
+        ml = torch.empty(heads * splits * 2, device="cuda")
+        if fused:
+            api.attn_decode_kv_append(step, _dev(k_row), _dev(v_row), _dev(q), k, v, acc, ml, out, heads,
+                                      n_kv, hd, stride, scale, splits, selector=Q4)
+        else:
+            api.kv_encode(step, _dev(k_row), _dev(v_row), k, v, n_kv, hd, stride, dtype=Q4)
+            api.attn_decode_kv(step, _dev(q), k, v, acc, ml, out, heads, n_kv, hd, stride, scale,
+                               splits, selector=Q4)
+        torch.cuda.synchronize()
+        assert api.check_device_status() == 0
+        outs.append(out)
+        caches.append((k, v))
+    assert torch.equal(caches[0][0], caches[1][0]) and torch.equal(caches[0][1], caches[1][1])
+    assert torch.equal(outs[0], outs[1])
+    kb = caches[1][0].cpu().numpy().reshape(n_kv, stride, row)
+    vb = caches[1][1].cpu().numpy().reshape(n_kv, stride, row)
+    _assert_close(O.attn_decode_kv(q, kb, vb, Q4, heads, n_kv, hd, seq, scale, stride=stride),
+                  outs[1].cpu().numpy())
