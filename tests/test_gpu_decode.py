@@ -459,3 +459,29 @@ def test_batched_step_with_fused_append_equals_the_two_launches(slots):
     for s, d in enumerate(depths):
         want = O.attn_decode_kv_q8(q[s], kb[s], vb[s], heads, n_kv, hd, d + 2, 0.0625, stride=stride)
         _assert_close(want, out2.cpu().numpy()[s])
+
+
+def test_many_slots_take_the_fixed_position_runs():
+    """More than 64 slots: the shared plan is off and every slot's cache is cut into the
+    reference's fixed runs of ceil(stride / splits) rows."""
+    from hipml_b200 import api
+    slots, stride = 70, 256
+    heads, n_kv, hd, depths, q, kc, vc = _batch_setup(slots, stride, 0x70, 0, 250)
+    splits = api.batch_splits(stride, slots)
+    slot_bytes = n_kv * stride * 272
+    acc_slot, ml_slot, q_slot = heads * splits * hd, heads * splits * 2, heads * hd
+    pos = torch.tensor([[d, d + 1] for d in depths], dtype=torch.int32, device="cuda")
+    out = torch.full((slots, q_slot), float("nan"), device="cuda")
+    acc = torch.full((slots * acc_slot,), float("nan"), device="cuda")
+    ml = torch.full((slots * ml_slot,), float("nan"), device="cuda")
+    api.attn_decode_batch(pos, _dev(q), _dev(kc), _dev(vc), acc, ml, out, heads, n_kv, hd, stride,
+                          0.0625, splits, slot_bytes, acc_slot, ml_slot, q_slot, slots, 0)
+    torch.cuda.synchronize()
+    assert api.check_device_status() == 0
+    # in this form every run of every slot writes its partial, dead runs an empty one
+    assert not np.isnan(acc.cpu().numpy()).any() and not np.isnan(ml.cpu().numpy()).any()
+    got = out.cpu().numpy()
+    for s in range(0, slots, 7):
+        expected = O.attn_decode_kv_q8(q[s], kc[s], vc[s], heads, n_kv, hd, depths[s] + 1, 0.0625,
+                                       stride=stride)
+        _assert_close(expected, got[s])
