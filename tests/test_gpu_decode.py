@@ -485,3 +485,47 @@ def test_many_slots_take_the_fixed_position_runs():
         expected = O.attn_decode_kv_q8(q[s], kc[s], vc[s], heads, n_kv, hd, depths[s] + 1, 0.0625,
                                        stride=stride)
         _assert_close(expected, got[s])
+
+
+def test_batched_plan_follows_the_lengths_across_graph_replays():
+    """The batched split pass derives its runs from the live lengths on the device: one captured
+    launch, replayed after the positions changed, must serve the new lengths."""
+    from hipml_b200 import api
+    slots, stride = 5, 2048
+    heads, n_kv, hd, depths, q, kc, vc = _batch_setup(slots, stride, 0x6A, 1500, 1900)
+    splits = api.batch_splits(stride, slots)
+    slot_bytes = n_kv * stride * 272
+    acc_slot, ml_slot, q_slot = heads * splits * hd, heads * splits * 2, heads * hd
+    dq, dk, dv = _dev(q), _dev(kc), _dev(vc)
+    pos = torch.zeros(slots, 2, dtype=torch.int32, device="cuda")
+    out = torch.full((slots, q_slot), float("nan"), device="cuda")
+    acc = torch.empty(slots * acc_slot, device="cuda")
+    ml = torch.empty(slots * ml_slot, device="cuda")
+
+    def launch():
+        api.attn_decode_batch(pos, dq, dk, dv, acc, ml, out, heads, n_kv, hd, stride, 0.0625, splits,
+                              slot_bytes, acc_slot, ml_slot, q_slot, slots, 0)
+
+    lengths = [[d + 1 for d in depths], [37, 1, 700, 64, 1203]]
+    pos.copy_(torch.tensor([[n - 1, n] for n in lengths[0]], dtype=torch.int32))
+    launch()                                   # first call outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            launch()
+    torch.cuda.current_stream().wait_stream(side)
+    for lens in lengths + lengths[:1]:
+        pos.copy_(torch.tensor([[n - 1, n] for n in lens], dtype=torch.int32))
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert api.check_device_status() == 0
+        got = out.cpu().numpy()
+        for s, n in enumerate(lens):
+            # rows past a slot's original depth carry NaN scales: shorter lengths only
+            assert n <= depths[s] + 1
+            want = O.attn_decode_kv_q8(q[s], kc[s], vc[s], heads, n_kv, hd, n, 0.0625, stride=stride)
+            _assert_close(want, got[s])
