@@ -159,13 +159,12 @@ __device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
     return *reinterpret_cast<const unsigned *>(&r);
 }
 
-// Rows [lo, hi) of split `split`: the reference's runs of ceil(span / splits) rows (span =
-// the live length, or the cache capacity for the multi-slot form), rounded up to whole
-// 64-key tiles so that no run ends in a mostly empty tile. The partials are scratch (only
-// their fold is defined), so splits past the last run simply get no rows and write neutral
-// partials. Coarser runs were measured too (fewer, longer CTAs chosen from the device's CTA
-// slots): no gain for one stream at 100,000 rows and 20 % slower for 8 - 16 slots of mixed
-// depth, where the longest CTAs form the tail.
+// Rows [lo, hi) of run `split` of a slot. The partials are scratch (only their fold is
+// defined), so the rows are dealt out for this device (plan_runs): one round of long runs,
+// balanced to within one 64-key tile, for a single stream; runs in proportion to the live
+// lengths for several slots. Without a plan (more than 64 slots) the reference's runs of
+// ceil(capacity / splits) rows apply, rounded up to whole tiles so that no run ends in a
+// mostly empty one; runs past the live length get no rows and write neutral partials.
 __device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int quota,
                                             int &lo, int &hi) {
     const int len = p.len[slot * p.len_stride + p.len_offset];
