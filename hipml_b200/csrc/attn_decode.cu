@@ -165,18 +165,47 @@ __global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
                                        p.share_slots, p.share_slots > 0 ? s_quota : 0);
         if (plan.runs >= 0) nsplit = plan.runs;
     }
-    float big = -INFINITY;
-    for (int s = sg; s < nsplit; s += 8) big = fmaxf(big, ml[(size_t)s * p.ml_split_stride]);
-    if (dl == 0) s_max[sg] = big;
-    __syncthreads();
+    float big = -INFINITY, num = 0.0f, den = 0.0f;
+    if (nsplit <= 256) {
+        // One (max, sum) pair per thread: the maximum and every run's weight are found with one
+        // round of loads, the weights go to shared memory, and the walk over the partial rows
+        // below has no exponentials and four loads in flight.
+        __shared__ float s_w[256];
+        const int s1 = threadIdx.x;
+        const float m = s1 < nsplit ? ml[(size_t)s1 * p.ml_split_stride] : -INFINITY;
+        const float l = s1 < nsplit ? ml[(size_t)s1 * p.ml_split_stride + 1] : 0.0f;
+        big = warp_max(m);
+        if (dl == 0) s_max[sg] = big;
+        __syncthreads();
 #pragma unroll
-    for (int i = 0; i < 8; i++) big = fmaxf(big, s_max[i]);
-    float num = 0.0f, den = 0.0f;
-    for (int s = sg; s < nsplit; s += 8) {
-        const float m = ml[(size_t)s * p.ml_split_stride];
+        for (int i = 0; i < 8; i++) big = fmaxf(big, s_max[i]);
         const float w = (m == -INFINITY) ? 0.0f : exp2f(m - big);
-        num += pa[(size_t)s * p.acc_split_stride] * w;
-        den += ml[(size_t)s * p.ml_split_stride + 1] * w;
+        s_w[s1] = w;
+        den = l * w;   // summed over the CTA with the per-warp sums below
+        __syncthreads();
+        float n0 = 0.0f, n1 = 0.0f, n2 = 0.0f, n3 = 0.0f;
+        int s = sg;
+        for (; s + 24 < nsplit; s += 32) {
+            n0 += pa[(size_t)s * p.acc_split_stride] * s_w[s];
+            n1 += pa[(size_t)(s + 8) * p.acc_split_stride] * s_w[s + 8];
+            n2 += pa[(size_t)(s + 16) * p.acc_split_stride] * s_w[s + 16];
+            n3 += pa[(size_t)(s + 24) * p.acc_split_stride] * s_w[s + 24];
+        }
+        for (; s < nsplit; s += 8) n0 += pa[(size_t)s * p.acc_split_stride] * s_w[s];
+        num = (n0 + n1) + (n2 + n3);
+        den = warp_sum(den);
+    } else {
+        for (int s = sg; s < nsplit; s += 8) big = fmaxf(big, ml[(size_t)s * p.ml_split_stride]);
+        if (dl == 0) s_max[sg] = big;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; i++) big = fmaxf(big, s_max[i]);
+        for (int s = sg; s < nsplit; s += 8) {
+            const float m = ml[(size_t)s * p.ml_split_stride];
+            const float w = (m == -INFINITY) ? 0.0f : exp2f(m - big);
+            num += pa[(size_t)s * p.acc_split_stride] * w;
+            den += ml[(size_t)s * p.ml_split_stride + 1] * w;
+        }
     }
     s_num[sg][dl] = num;
     if (dl == 0) s_den[sg] = den;
