@@ -895,7 +895,8 @@ def profile_case(args):
               headline workload): kv_encode_bulk, stage, attn_chunk_tc, `--reps` times;
     decode -- one layer's decode at depth 100000 (217.6 MB of q8 K/V, larger than L2):
               kv_encode_q8, attn_decode_kv_tc, attn_decode_kv_reduce, `--reps` times
-              (`--selector 1`: the same over a q4_0 cache, 115.2 MB).
+              (`--selector 1`: the same over a q4_0 cache, 115.2 MB);
+    batched -- one layer of the 16-slot batched decode step (mixed depths 615..7824).
     Prints the CUDA-event time per repetition so the capture has an un-profiled number."""
     import torch
 
@@ -909,6 +910,43 @@ def profile_case(args):
     if args.case == "front":
         r = front_end_bench(torch, api, peaks()["hbm_gbs"], reps=args.reps)
         print(json.dumps({"case": "front end of a 2048-token chunk", **r}))
+        return
+    if args.case == "batched":
+        # one layer of the 16-slot batched decode (depths as in the benchmark, seed 3): the
+        # step of hipml_attn_decode_batch_append, `--reps` times; 157 MB of live K/V rows
+        import oracle as O
+        slots, stride = 16, 8448
+        rng = O.Rng(3)
+        depths = [512 + int(rng.uniform() * 7681) for _ in range(slots)]
+        slot_bytes = KV * stride * ROW
+        kc = torch.zeros(slots * slot_bytes, dtype=torch.uint8, device=dev)
+        vc = torch.zeros_like(kc)
+        for s_, d_ in enumerate(depths):
+            api.kv_encode_bulk(torch.randn(d_, W, device=dev, generator=g),
+                               torch.randn(d_, W, device=dev, generator=g), kc[s_ * slot_bytes:],
+                               vc[s_ * slot_bytes:], KV, D, stride, 0, 0, d_)
+        splits = api.batch_splits(stride, slots)
+        acc_slot, ml_slot = H * splits * D, H * splits * 2
+        q = torch.randn(args.reps, slots, QW, device=dev, generator=g)
+        kn = torch.randn(args.reps, slots, W, device=dev, generator=g)
+        vn = torch.randn(args.reps, slots, W, device=dev, generator=g)
+        out = torch.empty(args.reps, slots, QW, device=dev)
+        acc = torch.empty(slots * acc_slot, device=dev)
+        ml = torch.empty(slots * ml_slot, device=dev)
+        pos = torch.tensor([[[d_ + r, d_ + r + 1] for d_ in depths] for r in range(args.reps)],
+                           dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        for r in range(args.reps):
+            ev[2 * r].record()
+            api.attn_decode_batch_append(pos[r], kn[r], vn[r], q[r], kc, vc, acc, ml, out[r], H, KV, D,
+                                         stride, SCALE, splits, slot_bytes, acc_slot, ml_slot, QW, slots)
+            ev[2 * r + 1].record()
+        torch.cuda.synchronize()
+        for r in range(args.reps):
+            ms = ev[2 * r].elapsed_time(ev[2 * r + 1])
+            nbytes = sum(2 * KV * (d_ + r + 1) * ROW for d_ in depths)
+            print(json.dumps({"case": "batched decode, 16 slots, one layer", "ms": ms,
+                              "kv_gbs": nbytes / ms / 1e6}))
         return
     if args.case == "chunk":
         # --kv-heads < 4 stands for one rank's share of a KV-head-sharded job
@@ -981,7 +1019,7 @@ def profile_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["chunk", "decode", "front"], default=None,
+    ap.add_argument("--case", choices=["chunk", "decode", "front", "batched"], default=None,
                     help="run one small profiling case instead of the benchmark")
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--mode", type=int, default=0)
