@@ -91,6 +91,12 @@ SIGNATURES = {
     "hipml_attn_decode_kv_shard_exchange": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                                                  _i, _i, _f, _i, _sz, _sz, C.POINTER(_vp), _i, _i,
                                                  _i, _u]),
+    "hipml_attn_decode_kv_shard_exchange_append": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                        _vp, _i, _i, _i, _i, _f, _i, _sz, _sz,
+                                                        C.POINTER(_vp), _i, _i, _i, _u]),
+    "hipml_set_decode_cta_slots": (_i, [_i]),
+    "hipml_set_decode_fold_mode": (_i, [_i]),
+    "hipml_decode_plan_quota": (_i, [C.POINTER(_i), _i, _i, _i, _i]),
     "hipml_attn_decode_kv_static": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i,
                                          _sz, _sz]),
     "hipml_attn_decode_cols_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i]),

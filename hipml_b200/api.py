@@ -129,6 +129,33 @@ def attn_decode_kv_shard_exchange(step, q, k, v, part_acc, part_ml, out, n_heads
         phases, wait_limit_us))
 
 
+def attn_decode_kv_shard_exchange_append(step, k_row, v_row, q, k, v, part_acc, part_ml, out, n_heads,
+                                         n_kv, head_dim, stride, scale, splits, peer_ws, rank, phases=3,
+                                         wait_limit_us=2_000_000, selector=0, k_off=0, v_off=0):
+    """attn_decode_kv_shard_exchange that also appends the token's K/V rows (None on the ranks
+    that do not own the new position)."""
+    table = (C.c_void_p * len(peer_ws))(*[C.c_void_p(int(a)) for a in peer_ws])
+    _lib.check("attn_decode_kv_shard_exchange", _lib.load().hipml_attn_decode_kv_shard_exchange_append(
+        _stream(), _p(step), selector, _p(k_row), _p(v_row), _p(q), _p(k), _p(v), _p(part_acc),
+        _p(part_ml), _p(out), n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off, table,
+        len(peer_ws), rank, phases, wait_limit_us))
+
+
+def set_decode_cta_slots(slots: int) -> None:
+    _lib.check("set_decode_cta_slots", _lib.load().hipml_set_decode_cta_slots(slots))
+
+
+def set_decode_fold_mode(mode: int) -> None:
+    """0: the split pass folds its own partials (one launch); 1: the fold is a second launch."""
+    _lib.check("set_decode_fold_mode", _lib.load().hipml_set_decode_fold_mode(mode))
+
+
+def decode_plan_quota(lens, splits, n_kv, cta_slots) -> int:
+    """64-row tiles per run of the multi-slot decode plan for these live lengths (host mirror)."""
+    arr = (C.c_int * len(lens))(*[int(v) for v in lens])
+    return int(_lib.load().hipml_decode_plan_quota(arr, len(lens), splits, n_kv, cta_slots))
+
+
 def attn_decode_kv_static(step, q, k, v, out, n_heads, n_kv, head_dim, stride, scale, splits,
                           selector=0, k_off=0, v_off=0):
     """attn_decode_kv without caller scratch: for callers that cannot allocate device memory.

@@ -15,7 +15,6 @@ SOURCES = [
     "kv_encode.cu",
     "attn_decode.cu",
     "attn_decode_tc.cu",
-    "attn_decode_t5.cu",
     "attn_decode_f32.cu",
     "decode_static.cu",
     "decode_exchange.cu",

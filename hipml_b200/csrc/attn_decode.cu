@@ -150,21 +150,7 @@ __global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
     const int dl = threadIdx.x & 31, sg = threadIdx.x >> 5;
     const float *pa = p.acc + (size_t)slot * p.acc_slot + (size_t)h * p.acc_head_stride + chunk * 32 + dl;
     const float *ml = p.ml + (size_t)slot * p.ml_slot + (size_t)h * p.ml_head_stride;
-    int nsplit = p.splits;
-    if (p.len) {
-        __shared__ int s_quota;
-        if (p.share_slots > 0) {
-            if (sg == 0) {
-                const int q = shared_quota_warp(p.len, p.len_stride, p.len_offset, gridDim.y, p.splits,
-                                                p.share_slots, p.n_kv);
-                if (dl == 0) s_quota = q;
-            }
-            __syncthreads();
-        }
-        const RunPlan plan = plan_runs(p.len, p.len_stride, p.len_offset, slot, p.splits, p.run_cap,
-                                       p.share_slots, p.share_slots > 0 ? s_quota : 0);
-        if (plan.runs >= 0) nsplit = plan.runs;
-    }
+    const int nsplit = p.splits;
     float big = -INFINITY, num = 0.0f, den = 0.0f;
     if (nsplit <= 256) {
         // One (max, sum) pair per thread: the maximum and every run's weight are found with one
@@ -239,90 +225,6 @@ __global__ void __launch_bounds__(256) attn_decode_fold(FoldParams p) {
 }
 
 
-// The same fold for many slots with few live runs each (the batched plan gives a slot runs in
-// proportion to its length, a handful per head): one CTA per (head, slot) and one thread per
-// output dim, so the batch's plan is worked out 8 times less often than in the form above and
-// no warp idles over a run list shorter than the warp count. grid (n_heads, slots), block
-// head_dim.
-__global__ void __launch_bounds__(256) attn_decode_fold_wide(FoldParams p) {
-    griddep_launch();
-    griddep_wait();
-    __shared__ float s_red[8];
-    __shared__ float s_w[256];
-    __shared__ int s_quota;
-    const int h = blockIdx.x, slot = blockIdx.y, d = threadIdx.x;
-    const int lane = d & 31, warp = d >> 5, nwarps = (blockDim.x + 31) >> 5;
-    const float *pa = p.acc + (size_t)slot * p.acc_slot + (size_t)h * p.acc_head_stride + d;
-    const float *ml = p.ml + (size_t)slot * p.ml_slot + (size_t)h * p.ml_head_stride;
-    int nsplit = p.splits;
-    if (p.len) {
-        if (p.share_slots > 0) {
-            if (warp == 0) {
-                const int q = shared_quota_warp(p.len, p.len_stride, p.len_offset, gridDim.y, p.splits,
-                                                p.share_slots, p.n_kv);
-                if (lane == 0) s_quota = q;
-            }
-            __syncthreads();
-        }
-        const RunPlan plan = plan_runs(p.len, p.len_stride, p.len_offset, slot, p.splits, p.run_cap,
-                                       p.share_slots, p.share_slots > 0 ? s_quota : 0);
-        if (plan.runs >= 0) nsplit = plan.runs;
-    }
-    nsplit = min(nsplit, 256);   // (the launcher takes this form only for splits <= 256)
-    float m = -INFINITY, l = 0.0f;
-    if (d < nsplit) {
-        m = ml[(size_t)d * p.ml_split_stride];
-        l = ml[(size_t)d * p.ml_split_stride + 1];
-    }
-    // with head_dim < 256 a thread may own several runs
-    float big = m;
-    for (int s = d + blockDim.x; s < nsplit; s += blockDim.x) big = fmaxf(big, ml[(size_t)s * p.ml_split_stride]);
-    big = warp_max(big);
-    if (lane == 0) s_red[warp] = big;
-    __syncthreads();
-    big = s_red[0];
-    for (int i = 1; i < nwarps; i++) big = fmaxf(big, s_red[i]);
-    float den = 0.0f;
-    for (int s = d; s < nsplit; s += blockDim.x) {
-        const float ms = s == d ? m : ml[(size_t)s * p.ml_split_stride];
-        const float ls = s == d ? l : ml[(size_t)s * p.ml_split_stride + 1];
-        const float w = (ms == -INFINITY) ? 0.0f : exp2f(ms - big);
-        s_w[s] = w;
-        den += ls * w;
-    }
-    den = warp_sum(den);
-    __syncthreads();   // s_red read by everyone, s_w complete
-    if (lane == 0) s_red[warp] = den;
-    __syncthreads();
-    den = 0.0f;
-    for (int i = 0; i < nwarps; i++) den += s_red[i];
-    float n0 = 0.0f, n1 = 0.0f, n2 = 0.0f, n3 = 0.0f;
-    int s = 0;
-    for (; s + 3 < nsplit; s += 4) {
-        n0 += pa[(size_t)s * p.acc_split_stride] * s_w[s];
-        n1 += pa[(size_t)(s + 1) * p.acc_split_stride] * s_w[s + 1];
-        n2 += pa[(size_t)(s + 2) * p.acc_split_stride] * s_w[s + 2];
-        n3 += pa[(size_t)(s + 3) * p.acc_split_stride] * s_w[s + 3];
-    }
-    for (; s < nsplit; s++) n0 += pa[(size_t)s * p.acc_split_stride] * s_w[s];
-    const float n = (n0 + n1) + (n2 + n3);
-    float *o = p.out + (size_t)slot * p.out_slot + (size_t)h * p.out_head_stride;
-    if (p.normalize) {
-        float r = den > 0.0f ? n / den : 0.0f;
-        if (p.gate) {
-            const float g = p.gate[(size_t)slot * p.out_slot + (size_t)h * p.out_head_stride + d];
-            r *= 1.0f / (1.0f + expf(-g));
-        }
-        o[d] = r;
-    } else {
-        o[d] = n;
-        if (d == 0) {
-            o[p.head_dim] = big;
-            o[p.head_dim + 1] = den;
-        }
-    }
-}
-
 }  // namespace
 
 // Entry names and parameter lists of the reduce kernels are the reference's
@@ -382,8 +284,6 @@ int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, b
 
 // Host-side launch of the fold.
 int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots) {
-    if (p.share_slots > 0 && p.splits <= 256)
-        return launch_pdl(attn_decode_fold_wide, dim3(n_heads, slots), dim3(p.head_dim), 0, stream, 1, p);
     dim3 grid(n_heads * (p.head_dim >> 5), slots);
     return launch_pdl(attn_decode_fold, grid, dim3(256), 0, stream, 1, p);
 }
@@ -392,16 +292,8 @@ int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, in
 int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int splits, int slots,
                          long long acc_slot, long long ml_slot, long long out_slot,
-                         const float *gate, const DecodeParams *live_runs) {
+                         const float *gate) {
     FoldParams p;
-    if (live_runs && (live_runs->share_slots > 0 || (live_runs->run_cap > 0 && !live_runs->by_stride))) {
-        p.len = live_runs->len;
-        p.len_stride = live_runs->len_stride;
-        p.len_offset = live_runs->len_offset;
-        p.run_cap = live_runs->by_stride ? 0 : live_runs->run_cap;
-        p.share_slots = live_runs->share_slots;
-        p.n_kv = live_runs->n_kv;
-    }
     p.acc = part_acc;
     p.ml = part_ml;
     p.out = out;
@@ -418,6 +310,21 @@ int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float
     p.normalize = 1;
     p.gate = gate;
     return launch_decode_fold(stream, p, n_heads, slots);
+}
+
+int decode_plan_quota_host(const int *lens, int slots, int splits, int share_slots, int n_kv) {
+    int total = 0, longest = 0;
+    for (int s = 0; s < slots; s++) {
+        const int t = (lens[s] + 63) >> 6;
+        total += t;
+        longest = t > longest ? t : longest;
+    }
+    auto runs_at = [&](int q) {
+        int runs = 0;
+        for (int s = 0; s < slots; s++) runs += shared_runs_of((lens[s] + 63) >> 6, q);
+        return runs;
+    };
+    return solve_quota(total, longest, slots, splits, share_slots, n_kv, runs_at);
 }
 
 const void *lookup_decode_kernel(const char *name) {

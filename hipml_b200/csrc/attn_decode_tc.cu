@@ -30,8 +30,15 @@
 // owns block w (32 dims) for all 64 keys. CPU definition: crates/hipml-core/src/ops.rs:
 // 449-518; kernel replaced: crates/hipml-kernels/kernels/attn_decode_kv_w.hip:92-285 and
 // attn_decode_kv.hip:251-374,427-484.
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "params.cuh"
 #include "q8_pack.cuh"
+#include "sm100_ptx.cuh"
+#include "decode_fold.cuh"
 
 namespace hipml {
 
@@ -59,35 +66,7 @@ constexpr int kOffBar = kOffCorr + 8 * 4;
 constexpr int kSmemBytes = kOffBar + kStages * 8;
 static_assert(2 * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs per SM");
 
-__device__ __forceinline__ unsigned smem_u32(const void *p) {
-    return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Linear global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned);
-// the bytes are counted on `bar` as they land.
-__device__ __forceinline__ void bulk_load(unsigned dst, const void *src, unsigned bytes, unsigned bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
-}
+using namespace ptx;
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0,
                                           unsigned b1) {
@@ -165,6 +144,13 @@ __device__ __forceinline__ unsigned pack_half2(__half lo, __half hi) {
 // lengths for several slots. Without a plan (more than 64 slots) the reference's runs of
 // ceil(capacity / splits) rows apply, rounded up to whole tiles so that no run ends in a
 // mostly empty one; runs past the live length get no rows and write neutral partials.
+// `runs`: the partial slots of a head that the fold reads (never less than one: a slot without
+// rows keeps run 0, which writes a neutral partial, so that its output rows are written).
+__device__ __forceinline__ int live_runs(const DecodeParams &p, int slot, int quota) {
+    const RunPlan plan = plan_runs(p.len, p.len_stride, p.len_offset, slot, p.splits,
+                                   p.by_stride ? 0 : p.run_cap, p.share_slots, quota);
+    return plan.runs < 0 ? p.splits : max(plan.runs, 1);
+}
 __device__ __forceinline__ void split_range(const DecodeParams &p, int slot, int split, int quota,
                                             int &lo, int &hi) {
     const int len = p.len[slot * p.len_stride + p.len_offset];
@@ -395,6 +381,98 @@ __device__ __forceinline__ void values_block_q4(const unsigned char *vtile, int 
     }
 }
 
+// Arrival counters of the fold inside the split pass: kArriveRegions regions of
+// kArriveRegionInts counters, zero at load and zero again after every launch that used them.
+constexpr int kArriveRegions = 128;
+__device__ int g_arrive[kArriveRegions * kArriveRegionInts];
+
+// What the CTA that holds the final fold of a (slot, KV head) does with it: write the output
+// rows, or (sequence-split decode across GPUs) publish the triples to every rank's table
+// and / or collect all ranks' triples and fold those. All threads of the CTA call it; warp w
+// holds head w of the group in f.
+__device__ __forceinline__ void fold_finish(const DecodeParams &p, int *status, int slot, int kvh,
+                                            int group, FoldAcc &f) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = kvh * group + warp;
+    if (p.xch.phases == 0) {
+        if (warp < group) fold_emit(p, slot, h, f, lane, p.normalize != 0);
+        return;
+    }
+    __shared__ int s_epoch;
+    int *hdr = reinterpret_cast<int *>(p.xch.ws[p.xch.rank]);
+    // Every folding CTA of the call reads the epoch before it adds itself to the counter, and
+    // the epoch advances only after the last of them has: all of them see the same value.
+    if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile int *>(hdr) + ((p.xch.phases & 1) ? 1 : 0);
+    __syncthreads();
+    const int e = s_epoch;
+    if (p.xch.phases & 1) {
+        if (warp < group) exchange_publish_warp(p.xch, p.n_heads, h, e, f, lane);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            if (atomicAdd(hdr + 1, 1) == p.n_kv - 1) {
+                hdr[1] = 0;
+                *reinterpret_cast<volatile int *>(hdr) = e;
+            }
+        }
+    }
+    if (p.xch.phases & 2) {
+        if (warp < group) {
+            const unsigned long long deadline = global_timer_ns() + 1000ull * p.xch.wait_us;
+            if (exchange_collect_warp(p.xch, p.n_heads, h, e, deadline, lane, f))
+                fold_emit(p, slot, h, f, lane, true);
+            else if (lane == 0 && status)
+                atomicCAS(status, 0, 31);
+        }
+    }
+}
+
+// The end of a split-pass CTA whose partial is live: arrive at the group's counter; the last
+// of a group folds it into the group's first slot and arrives at the head group's counter;
+// the last of those folds the groups and finishes. Nobody waits: whoever is not last is done.
+__device__ __forceinline__ void fold_tail(const DecodeParams &p, int *status, int slot, int kvh,
+                                          int split, int runs, int group, int tid) {
+    __shared__ int s_role;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int ngroups = (runs + kFoldGroup - 1) / kFoldGroup;
+    const int grp = split / kFoldGroup;
+    const int expect = min(kFoldGroup, runs - grp * kFoldGroup);
+    int *ctr = g_arrive + (size_t)p.arrive_region * kArriveRegionInts +
+               (size_t)(slot * p.n_kv + kvh) * p.arrive_stride;
+    __threadfence();   // this CTA's partial, before its arrival
+    __syncthreads();
+    if (tid == 0) {
+        int role = 1;
+        if (expect > 1) {
+            role = atomicAdd(ctr + 1 + grp, 1) == expect - 1;
+            if (role) ctr[1 + grp] = 0;
+        }
+        s_role = role;
+    }
+    __syncthreads();
+    if (!s_role) return;
+    __threadfence();   // the others' partials, after their arrivals
+    const int h = kvh * group + warp;
+    float *pa = p.part_acc + (size_t)slot * p.acc_slot + (size_t)h * p.splits * 256;
+    float *ml = p.part_ml + (size_t)slot * p.ml_slot + (size_t)h * p.splits * 2;
+    FoldAcc f;
+    if (warp < group) f = fold_warp(pa, ml, grp * kFoldGroup, 1, expect, lane);
+    if (ngroups > 1) {
+        if (warp < group) fold_store_partial(pa, ml, grp * kFoldGroup, f, lane);
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int role = atomicAdd(ctr, 1) == ngroups - 1;
+            if (role) ctr[0] = 0;
+            s_role = role;
+        }
+        __syncthreads();
+        if (!s_role) return;
+        __threadfence();
+        if (warp < group) f = fold_warp(pa, ml, 0, kFoldGroup, ngroups, lane);
+    }
+    fold_finish(p, status, slot, kvh, group, f);
+}
+
 // kQ4: the cache is q4_0; the phases read the 144-byte rows as they were copied.
 template <bool kQ4>
 __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p, int *status) {
@@ -442,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
             for (int s0 = 0; s0 < p.n_slots; s0 += 32) {
                 const int s = s0 + lane;
                 const int per = s < p.n_slots
-                    ? ((p.len[s * p.len_stride + p.len_offset] + 63) / 64 + quota - 1) / quota : 0;
+                    ? shared_runs_of((p.len[s * p.len_stride + p.len_offset] + 63) >> 6, quota) : 0;
                 const int runs = per * p.n_kv;
                 int incl = runs;
 #pragma unroll
@@ -481,9 +559,9 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
             pm[0] = -INFINITY;
             pm[1] = 0.0f;
         }
-        return;
     }
 
+    if (ntiles > 0) {
     constexpr int kSrcRow = kQ4 ? kQ4RowBytes : kRowBytes;   // bytes of a cache row
     const size_t head_byte = (size_t)slot * p.kv_slot_bytes + (size_t)kvh * p.stride * kSrcRow;
     const unsigned char *kbase = p.k + head_byte;
@@ -720,25 +798,132 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         pm[0] = m_run;
         pm[1] = l_run;
     }
+    }   // ntiles > 0
+
+    // ---- fold inside the split pass
+    if (p.out == nullptr) return;
+    const int runs = live_runs(p, slot, p.share_slots > 0 ? s_plan[3] : 0);
+    if (split >= runs) return;   // a launched run past the live ones: its neutral partial is not read
+    fold_tail(p, status, slot, kvh, split, runs, group, tid);
+}
+
+// Stand-alone launch of the same fold: grid (n_kv, slots), 8 warps = the heads of the group.
+__global__ void __launch_bounds__(kThreads) attn_decode_fold_tree(DecodeParams p, int *status) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ int s_quota;
+    const int kvh = blockIdx.x, slot = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = p.n_heads / p.n_kv;
+    if (p.share_slots > 0) {
+        if (warp == 0) {
+            const int q = shared_quota_warp(p.len, p.len_stride, p.len_offset, p.n_slots, p.splits,
+                                            p.share_slots, p.n_kv);
+            if (lane == 0) s_quota = q;
+        }
+        __syncthreads();
+    }
+    const int runs = live_runs(p, slot, p.share_slots > 0 ? s_quota : 0);
+    const int ngroups = (runs + kFoldGroup - 1) / kFoldGroup;
+    FoldAcc f;
+    if (warp < group) {
+        const int h = kvh * group + warp;
+        float *pa = p.part_acc + (size_t)slot * p.acc_slot + (size_t)h * p.splits * 256;
+        float *ml = p.part_ml + (size_t)slot * p.ml_slot + (size_t)h * p.splits * 2;
+        for (int g = 0; g < ngroups; g++) {
+            f = fold_warp(pa, ml, g * kFoldGroup, 1, min(kFoldGroup, runs - g * kFoldGroup), lane);
+            if (ngroups > 1) fold_store_partial(pa, ml, g * kFoldGroup, f, lane);
+        }
+        if (ngroups > 1) {
+            __threadfence();
+            __syncwarp();
+            f = fold_warp(pa, ml, 0, kFoldGroup, ngroups, lane);
+        }
+    }
+    fold_finish(p, status, slot, kvh, group, f);
 }
 
 }  // namespace
 
-int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
+namespace {
+
+// Per-device set-up of the two kernels (dynamic shared memory limit, status word), done once.
+int *decode_tc_setup(int *rc) {
+    static std::mutex mu;
     static int *status_word[64] = {};   // nullptr = device not set up yet
+    *rc = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lock(mu);
     if (status_word[dev] == nullptr) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kv_tc<false>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(attn_decode_kv_tc<true>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
+        if (e != cudaSuccess) {
+            *rc = (int)e;
+            return nullptr;
+        }
         status_word[dev] = device_status_word();
-        if (status_word[dev] == nullptr) return launch_status();
+        if (status_word[dev] == nullptr) *rc = launch_status();
     }
+    return status_word[dev];
+}
+
+std::atomic<int> g_two_launch_fold{0};
+
+}  // namespace
+
+void decode_set_two_launch_fold(int on) { g_two_launch_fold.store(on ? 1 : 0); }
+
+// Which arrival-counter region a launch on `stream` uses. Two launches may share a region
+// only if they cannot overlap on the device, so the key is what serialises launches: the
+// stream (by its process-unique id), and under stream capture also the capture sequence (two
+// graphs captured from one stream may later run side by side). A key keeps its region for
+// the life of the process; when the regions run out the caller takes the two-launch form.
+int decode_arrive_region(cudaStream_t stream, long long counters) {
+    if (counters > kArriveRegionInts || g_two_launch_fold.load()) return -1;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    unsigned long long sid = 0, cap = 0;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamGetId(stream, &sid) != cudaSuccess ||
+        cudaStreamGetCaptureInfo(stream, &st, &cap) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    if (st != cudaStreamCaptureStatusActive) cap = 0;
+    static std::mutex mu;
+    static std::map<std::tuple<int, unsigned long long, unsigned long long>, int> table;
+    static int next_free[64] = {};
+    if (dev < 0 || dev >= 64) return -1;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_tuple(dev, cap, sid);
+    auto it = table.find(key);
+    if (it != table.end()) return it->second;
+    if (next_free[dev] >= kArriveRegions) return -1;
+    const int region = next_free[dev]++;
+    table.emplace(key, region);
+    return region;
+}
+
+int launch_decode_fold_tree(cudaStream_t stream, const DecodeParams &p, int slots) {
+    int rc = 0;
+    int *status = decode_tc_setup(&rc);
+    if (!status) return rc;
+    DecodeParams q = p;
+    q.n_slots = slots;
+    return launch_pdl(attn_decode_fold_tree, dim3(q.n_kv, slots), dim3(kThreads), 0, stream, 1, q, status);
+}
+
+// Split pass; with p.out set also the fold: inside the same launch when an arrival-counter
+// region is to be had, as a second launch otherwise.
+int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
+    int rc = 0;
+    int *status = decode_tc_setup(&rc);
+    if (!status) return rc;
     dim3 grid(p.n_kv * p.splits, slots);
     DecodeParams q = p;
     q.n_slots = slots;
@@ -746,11 +931,26 @@ int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
         grid = dim3(q.share_slots, 1);
     else if (!q.by_stride && q.run_cap > 0 && q.run_cap < q.splits)
         grid = dim3(q.n_kv * q.run_cap, slots);
-    if (q.q4)
-        return launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
-                          status_word[dev]);
-    return launch_pdl(attn_decode_kv_tc<false>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
-                      status_word[dev]);
+    bool second_launch = false;
+    if (q.out != nullptr) {
+        // most runs a (slot, KV head) can have under the plan in force
+        int bound = q.splits;
+        if (q.share_slots > 0) bound = min(bound, max(q.share_slots / q.n_kv, 1));
+        else if (!q.by_stride && q.run_cap > 0) bound = min(bound, q.run_cap);
+        q.arrive_stride = 1 + (bound + kFoldGroup - 1) / kFoldGroup;
+        q.arrive_region = decode_arrive_region(stream, (long long)slots * q.n_kv * q.arrive_stride);
+        if (q.arrive_region < 0) {
+            second_launch = true;
+            q.out = nullptr;
+        }
+    }
+    rc = q.q4 ? launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
+                           status)
+              : launch_pdl(attn_decode_kv_tc<false>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
+                           status);
+    if (rc != 0 || !second_launch) return rc;
+    q.out = p.out;
+    return launch_pdl(attn_decode_fold_tree, dim3(q.n_kv, slots), dim3(kThreads), 0, stream, 1, q, status);
 }
 
 }  // namespace hipml

@@ -4,6 +4,8 @@
 // crates/hipml-kernels/src/launch/device/graph_launch.rs:878-1028,
 // crates/hipml-kernels/src/launch/device/batch_launch.rs:22-316,
 // crates/hipml-kernels/src/attn_gpu/imp/attn_chunk_kv.rs:129-305.
+#include <atomic>
+
 #include "params.cuh"
 
 using namespace hipml;
@@ -25,14 +27,22 @@ int check_encode(int dtype, int n_kv, int head_dim, int stride) {
 
 // Live runs per KV head of the single-stream split pass: one round of the device's CTA slots
 // (two CTAs per SM), so that every CTA streams one long run instead of several short ones.
+// Cached per device; hipml_set_decode_cta_slots overrides it for every device.
+std::atomic<int> g_cta_slots_override{0};
 int decode_cta_slots() {
-    static int slots = 0;
+    const int forced = g_cta_slots_override.load();
+    if (forced > 0) return forced;
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    int slots = cached[dev].load();
     if (slots == 0) {
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
+        int sms = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             sms = 148;
         slots = 2 * sms;
+        cached[dev].store(slots);
     }
     return slots;
 }
@@ -140,24 +150,15 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
     // experimental variants have no counterpart here.
     bool tensor_core;
-    bool tcgen05_body = false;
     if (selector == 0 || selector == 4) {
         tensor_core = head_dim == 256;
         if (selector == 4 && head_dim != 256)
             return fail(HIPML_ERR_INVALID_ARGUMENT,
                         "head_dim %d: the warp kernel is head_dim 256 only", head_dim);
-    } else if (selector == 5) {
-        // the tcgen05 body: head_dim 256 and a GQA group of at most 6
-        if (head_dim != 256 || n_heads / n_kv > 6)
-            return fail(HIPML_ERR_INVALID_ARGUMENT,
-                        "head_dim %d / group %d: the tcgen05 decode kernel needs head_dim 256 and a "
-                        "group <= 6", head_dim, n_heads / n_kv);
-        tensor_core = true;
-        tcgen05_body = true;
     } else if (selector == 6) {
         tensor_core = false;
     } else if (selector == 1) {
-        // q4_0: the same tile kernel, expanding the raw rows in shared memory, at head_dim 256
+        // q4_0: the same tile kernel reading the 144-byte rows in place, at head_dim 256
         tensor_core = head_dim == 256;
     } else {
         return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", selector);
@@ -197,25 +198,36 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
         p.vw = const_cast<unsigned char *>(p.v);
         p.row_slot = 0;
     }
-    if (tcgen05_body) {
-        int *status = device_status_word();
-        if (!status) return launch_status();
-        if (int e = launch_decode_t5(as_stream(stream), p, 1, status)) return e;
-    } else if (int e = launch_decode_split(as_stream(stream), p, 1, tensor_core)) {
-        return e;
+    if (tensor_core) {
+        // one launch: the split pass folds its own partials (and runs the exchange)
+        const size_t align = reinterpret_cast<size_t>(out) | reinterpret_cast<size_t>(gate) |
+                             reinterpret_cast<size_t>(part_acc);
+        if (align & (shard && !xch ? 7 : 15))
+            return fail(HIPML_ERR_INVALID_ARGUMENT, "out, gate and part_acc must be 16-byte aligned");
+        if ((reinterpret_cast<size_t>(part_ml) & 7) != 0)
+            return fail(HIPML_ERR_INVALID_ARGUMENT, "part_ml must be 8-byte aligned");
+        p.out = out;
+        p.out_slot = 0;
+        p.out_head_stride = (shard && !xch) ? head_dim + 2 : head_dim;
+        p.normalize = (shard && !xch) ? 0 : 1;
+        p.gate = gate;
+        if (xch) {
+            for (int w = 0; w < 16; w++)
+                p.xch.ws[w] = w < xch->shards ? reinterpret_cast<unsigned char *>(xch->peer_ws[w]) : nullptr;
+            p.xch.shards = xch->shards;
+            p.xch.rank = xch->rank;
+            p.xch.phases = xch->phases;
+            p.xch.wait_us = xch->wait_limit_us;
+        }
+        return launch_decode_tc(as_stream(stream), p, 1);
     }
-    if (xch) {
-        int *status = device_status_word();
-        if (!status) return launch_status();
-        return launch_decode_fold_exchange(as_stream(stream), part_acc, part_ml, out, n_heads,
-                                           head_dim, splits, xch->peer_ws, xch->shards, xch->rank,
-                                           xch->phases, xch->wait_limit_us, status,
-                                           tensor_core && !tcgen05_body ? &p : nullptr);
-    }
+    if (xch)
+        return fail(HIPML_ERR_INVALID_ARGUMENT,
+                    "exchange: only the head_dim 256 kernel (selectors 0, 1, 4) publishes to peers");
+    if (int e = launch_decode_split(as_stream(stream), p, 1, false)) return e;
     if (!shard)
         return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim,
-                                    splits, 1, 0, 0, 0, gate,
-                                    tensor_core && !tcgen05_body ? &p : nullptr);
+                                    splits, 1, 0, 0, 0, gate);
     FoldParams f;
     f.acc = part_acc;
     f.ml = part_ml;
@@ -230,12 +242,6 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     f.out_head_stride = head_dim + 2;
     f.normalize = 0;
     f.gate = nullptr;
-    if (tensor_core && !tcgen05_body && p.run_cap > 0) {
-        f.len = p.len;
-        f.len_stride = p.len_stride;
-        f.len_offset = p.len_offset;
-        f.run_cap = p.run_cap;
-    }
     return launch_decode_fold(as_stream(stream), f, n_heads, 1);
 }
 
@@ -272,7 +278,7 @@ int hipml_attn_decode_kv_append(hipml_stream_t stream, const int *step, int sele
     if (!fused) {
         // any other selector, head size or alignment: the two launches the reference makes
         const int dtype = selector == 1 ? 1 : 0;
-        if (selector != 0 && selector != 1 && selector != 4 && selector != 5 && selector != 6)
+        if (selector != 0 && selector != 1 && selector != 4 && selector != 6)
             return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", selector);
         if (int e = hipml_kv_encode(stream, step, dtype, k_row, v_row, kc, vc, n_kv, head_dim, stride))
             return e;
@@ -297,13 +303,12 @@ size_t hipml_decode_exchange_bytes(int n_heads, int head_dim, int shards) {
     return decode_exchange_bytes(n_heads, head_dim, shards);
 }
 
-int hipml_attn_decode_kv_shard_exchange(hipml_stream_t stream, const int *step, int selector,
-                                        const float *q, const void *k, const void *v,
-                                        float *part_acc, float *part_ml, float *out, int n_heads,
-                                        int n_kv, int head_dim, int stride, float scale, int splits,
-                                        size_t k_off, size_t v_off, void *const *peer_ws,
-                                        int shards, int rank, int phases,
-                                        unsigned wait_limit_us) {
+static int shard_exchange(hipml_stream_t stream, const int *step, int selector, const float *k_row,
+                          const float *v_row, const float *q, const void *k, const void *v,
+                          float *part_acc, float *part_ml, float *out, int n_heads, int n_kv,
+                          int head_dim, int stride, float scale, int splits, size_t k_off,
+                          size_t v_off, void *const *peer_ws, int shards, int rank, int phases,
+                          unsigned wait_limit_us) {
     if (shards < 1 || shards > 16 || rank < 0 || rank >= shards)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: rank %d of %d shards (1..16)", rank,
                     shards);
@@ -314,20 +319,65 @@ int hipml_attn_decode_kv_shard_exchange(hipml_stream_t stream, const int *step, 
     for (int w = 0; w < shards; w++)
         if (!peer_ws[w] || (reinterpret_cast<size_t>(peer_ws[w]) & 255) != 0)
             return fail(HIPML_ERR_WORKSPACE, "exchange: workspace %d missing or not 256-byte aligned", w);
+    if (head_dim != 256)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: head_dim %d, only 256", head_dim);
     if (wait_limit_us > 10000000u) wait_limit_us = 10000000u;
     ExchangeArgs x = {peer_ws, shards, rank, phases, wait_limit_us};
     if (phases == 2) {
         // collect only: no split pass, the partials are not read
         if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
-        if (head_dim % 32 != 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "head_dim %d", head_dim);
+        if ((reinterpret_cast<size_t>(out) & 15) != 0)
+            return fail(HIPML_ERR_INVALID_ARGUMENT, "out, gate and part_acc must be 16-byte aligned");
         int *status = device_status_word();
         if (!status) return launch_status();
-        return launch_decode_fold_exchange(as_stream(stream), part_acc, part_ml, out, n_heads,
-                                           head_dim, splits < 1 ? 1 : splits, peer_ws, shards, rank,
-                                           2, wait_limit_us, status);
+        DecodeParams p = {};
+        p.n_heads = n_heads;
+        p.n_kv = n_kv;
+        p.head_dim = head_dim;
+        p.out = out;
+        p.out_slot = 0;
+        p.out_head_stride = head_dim;
+        p.normalize = 1;
+        for (int w = 0; w < 16; w++)
+            p.xch.ws[w] = w < shards ? reinterpret_cast<unsigned char *>(peer_ws[w]) : nullptr;
+        p.xch.shards = shards;
+        p.xch.rank = rank;
+        p.xch.phases = 2;
+        p.xch.wait_us = wait_limit_us;
+        return launch_decode_collect(as_stream(stream), p, status);
     }
+    if (k_row &&
+        ((reinterpret_cast<size_t>(k_row) | reinterpret_cast<size_t>(v_row)) & 15) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "decode with append: K/V rows must be 16-byte aligned");
     return decode_kv(stream, step, selector, q, k, v, part_acc, part_ml, out, n_heads, n_kv,
-                     head_dim, stride, scale, splits, k_off, v_off, true, &x);
+                     head_dim, stride, scale, splits, k_off, v_off, true, &x, nullptr, k_row, v_row);
+}
+
+int hipml_attn_decode_kv_shard_exchange(hipml_stream_t stream, const int *step, int selector,
+                                        const float *q, const void *k, const void *v,
+                                        float *part_acc, float *part_ml, float *out, int n_heads,
+                                        int n_kv, int head_dim, int stride, float scale, int splits,
+                                        size_t k_off, size_t v_off, void *const *peer_ws,
+                                        int shards, int rank, int phases,
+                                        unsigned wait_limit_us) {
+    return shard_exchange(stream, step, selector, nullptr, nullptr, q, k, v, part_acc, part_ml, out,
+                          n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off, peer_ws, shards,
+                          rank, phases, wait_limit_us);
+}
+
+int hipml_attn_decode_kv_shard_exchange_append(hipml_stream_t stream, const int *step, int selector,
+                                               const float *k_row, const float *v_row,
+                                               const float *q, void *k, void *v, float *part_acc,
+                                               float *part_ml, float *out, int n_heads, int n_kv,
+                                               int head_dim, int stride, float scale, int splits,
+                                               size_t k_off, size_t v_off, void *const *peer_ws,
+                                               int shards, int rank, int phases,
+                                               unsigned wait_limit_us) {
+    if ((k_row == nullptr) != (v_row == nullptr))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "decode with append: give both rows or neither");
+    return shard_exchange(stream, step, selector, k_row, v_row, q, k, v, part_acc, part_ml, out,
+                          n_heads, n_kv, head_dim, stride, scale, splits, k_off, v_off, peer_ws, shards,
+                          rank, phases, wait_limit_us);
 }
 
 int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, float *out,
@@ -405,9 +455,29 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
         p.vw = const_cast<unsigned char *>(p.v);
         p.row_slot = (long long)n_kv * head_dim;
     }
+    // The tensor-core body folds its own partials (groups of eight runs, then the groups: at
+    // most 32 groups), unless the fixed runs of a very fine caller plan are too many for that.
+    const bool fixed_runs = p.share_slots == 0 && (by_stride || p.run_cap <= 0);
+    const bool tree = tensor_core && !(fixed_runs && splits > 256) &&
+                      ((reinterpret_cast<size_t>(out) | reinterpret_cast<size_t>(part_acc)) & 15) == 0 &&
+                      (reinterpret_cast<size_t>(part_ml) & 7) == 0 && ((acc_slot | q_slot) & 3) == 0 &&
+                      (ml_slot & 1) == 0;
+    if (tree) {
+        p.out = out;
+        p.out_slot = q_slot;
+        p.out_head_stride = head_dim;
+        p.normalize = 1;
+        return launch_decode_tc(as_stream(stream), p, slots);
+    }
+    if (tensor_core && !fixed_runs) {
+        // only the live runs of the device's plan are written; the flat fold reads all `splits`
+        p.run_cap = 0;
+        p.share_slots = 0;
+        p.by_stride = by_stride;
+    }
     if (int e = launch_decode_split(as_stream(stream), p, slots, tensor_core)) return e;
     return launch_decode_reduce(as_stream(stream), part_acc, part_ml, out, n_heads, head_dim, splits,
-                                slots, acc_slot, ml_slot, q_slot, nullptr, tensor_core ? &p : nullptr);
+                                slots, acc_slot, ml_slot, q_slot, nullptr);
 }
 
 int hipml_attn_decode_rows(hipml_stream_t stream, int dtype, const int *pos, const float *q,
@@ -758,6 +828,24 @@ int hipml_attn_decode_cols_f32(hipml_stream_t stream, const float *q, const floa
     splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
     return launch_decode_cols_f32(as_stream(stream), q, k_cache, v_cache, part_acc, part_ml, out,
                                   n_heads, n_kv, head_dim, n_ctx, pos0, rows, splits);
+}
+
+int hipml_set_decode_cta_slots(int slots) {
+    if (slots < 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "decode CTA slots %d", slots);
+    g_cta_slots_override.store(slots);
+    return 0;
+}
+
+int hipml_set_decode_fold_mode(int mode) {
+    if (mode != 0 && mode != 1)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "decode fold mode %d (0 inside the split pass, 1 own launch)", mode);
+    decode_set_two_launch_fold(mode);
+    return 0;
+}
+
+int hipml_decode_plan_quota(const int *lens, int slots, int splits, int n_kv, int cta_slots) {
+    if (!lens || slots <= 0 || splits < 1 || n_kv <= 0 || cta_slots < 2 * slots * n_kv) return -1;
+    return decode_plan_quota_host(lens, slots, splits, cta_slots, n_kv);
 }
 
 }  // extern "C"

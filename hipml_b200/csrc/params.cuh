@@ -34,18 +34,70 @@ struct DecodeParams {
     unsigned char *kw = nullptr, *vw = nullptr;
     long long row_slot = 0;
     long long kv_slot_bytes, acc_slot, ml_slot, q_slot;
+    // Fold inside the split pass (tensor-core body). The CTA that completes a group of eight
+    // runs of a (slot, KV head) folds them into the group's first slot, and the CTA that
+    // completes the last group folds the groups and writes the output rows of the head group,
+    // so a decode step of a layer is one launch. The arrival counters live in library-owned
+    // device memory (region `arrive_region`, `arrive_stride` counters per (slot, KV head):
+    // one for the groups, then one per group) and return to zero by themselves.
+    float *out = nullptr;            // nullptr: partials only, the caller launches the fold
+    long long out_slot = 0, out_head_stride = 0;
+    int normalize = 1;               // 0: out row = [acc (unnormalised) | max | sum]
+    const float *gate = nullptr;     // optional, normalize only: out *= sigmoid(gate)
+    int arrive_region = -1, arrive_stride = 0;
+    // Sequence-split decode across GPUs: instead of writing `out` directly the folding CTA
+    // stores the head group's (acc, max, sum) triples into every rank's table (phase bit 0),
+    // and/or waits for all ranks' triples and folds them into `out` (phase bit 1).
+    struct Exchange {
+        unsigned char *ws[16];
+        int shards = 0, rank = 0, phases = 0;
+        unsigned wait_us = 0;
+    } xch;
 };
 // Live runs of one slot in the tensor-core split pass, in 64-key tiles: `runs` runs deal the
 // slot's `tiles` tiles out to within one tile (run i covers tiles [i*tiles/runs,
 // (i+1)*tiles/runs)). Single stream: min(splits, tiles, run_cap). Several slots sharing the
 // device (share_slots > 0): every run gets `quota` tiles, about total_tiles * n_kv /
 // share_slots, so a slot's runs are proportional to its live length and the whole batch is
-// one round of CTAs. runs == -1: the reference's fixed runs apply instead.
+// one round of CTAs; every slot has at least one run (a slot without rows gets one CTA per KV
+// head, which writes the zero rows of its output). runs == -1: the reference's fixed runs
+// apply instead.
 struct RunPlan {
     int tiles, runs;
 };
-// Tiles per run of the shared plan. Called by all 32 lanes of one warp (lane-strided over
-// the slots); every lane returns the same value.
+__host__ __device__ __forceinline__ int shared_runs_of(int tiles, int quota) {
+    const int r = (tiles + quota - 1) / quota;
+    return r < 1 ? 1 : r;
+}
+// Tiles per run of the shared plan: the smallest quota, not below ceil(longest / splits) (a
+// head has `splits` partial slots), whose runs fit the share_slots CTAs that are launched.
+// runs_at(q) returns the batch's run count per KV head at quota q (non-increasing in q);
+// total / longest are the batch's tile sum and longest slot. The answer always fits:
+// sum(max(1, ceil(t / q))) <= total / q + slots, so q = ceil(total / (fit - slots)) does, and
+// the launchers take this plan only when 2 * slots * n_kv <= share_slots.
+// (runs_at is a host lambda on the host and a device lambda on the device)
+#pragma nv_exec_check_disable
+template <class RunsAt>
+__host__ __device__ __forceinline__ int solve_quota(int total, int longest, int slots, int splits,
+                                                    int share_slots, int n_kv, RunsAt runs_at) {
+    const int fit = share_slots / n_kv;   // runs per KV head that one round of CTAs holds
+    int lo = (total + fit - 1) / fit;
+    const int floor_q = (longest + splits - 1) / splits;
+    if (lo < floor_q) lo = floor_q;
+    if (lo < 1) lo = 1;
+    if (runs_at(lo) <= fit) return lo;
+    int hi = fit > slots ? (total + (fit - slots) - 1) / (fit - slots) : longest;
+    if (hi < lo + 1) hi = lo + 1;
+    // invariant: lo does not fit, hi does
+    while (hi - lo > 1) {
+        const int mid = lo + (hi - lo) / 2;
+        if (runs_at(mid) <= fit) hi = mid; else lo = mid;
+    }
+    return hi;
+}
+#ifdef __CUDACC__
+// Called by all 32 lanes of one warp (lane-strided over the slots); every lane returns the
+// same value.
 __device__ __forceinline__ int shared_quota_warp(const int *len, int len_stride, int len_offset,
                                                  int slots, int splits, int share_slots, int n_kv) {
     const int lane = threadIdx.x & 31;
@@ -57,19 +109,13 @@ __device__ __forceinline__ int shared_quota_warp(const int *len, int len_stride,
     }
     total = __reduce_add_sync(0xffffffffu, total);
     longest = __reduce_max_sync(0xffffffffu, longest);
-    int quota = (total * n_kv + share_slots - 1) / share_slots;
-    quota = max(max(quota, (longest + splits - 1) / splits), 1);
-    // rounding every slot up can push the batch past one round of CTAs: grow the quota until
-    // the live runs fit (a few steps; past `longest` every slot is one run)
-    for (int step = 0; step < 64 && quota < longest; step++) {
+    auto runs_at = [&](int q) {
         int runs = 0;
         for (int s = lane; s < slots; s += 32)
-            runs += ((len[s * len_stride + len_offset] + 63) / 64 + quota - 1) / quota;
-        runs = __reduce_add_sync(0xffffffffu, runs);
-        if (runs * n_kv <= share_slots) break;
-        quota++;
-    }
-    return quota;
+            runs += shared_runs_of((len[s * len_stride + len_offset] + 63) >> 6, q);
+        return (int)__reduce_add_sync(0xffffffffu, runs);
+    };
+    return solve_quota(total, longest, slots, splits, share_slots, n_kv, runs_at);
 }
 // `quota`: shared_quota_warp's value when share_slots > 0 (unused otherwise).
 __device__ __forceinline__ RunPlan plan_runs(const int *len, int len_stride, int len_offset, int slot,
@@ -77,18 +123,28 @@ __device__ __forceinline__ RunPlan plan_runs(const int *len, int len_stride, int
     RunPlan r;
     r.tiles = (len[slot * len_stride + len_offset] + 63) >> 6;
     if (share_slots > 0)
-        r.runs = (r.tiles + quota - 1) / quota;
+        r.runs = shared_runs_of(r.tiles, quota);
     else if (run_cap > 0)
         r.runs = min(min(splits, r.tiles), run_cap);
     else
         r.runs = -1;
     return r;
 }
+#endif
+// The same quota from host-side lengths (the C ABI's hipml_decode_plan_quota).
+int decode_plan_quota_host(const int *lens, int slots, int splits, int share_slots, int n_kv);
 
 // Launches the split pass (the caller launches the reduce).
 int launch_decode_split(cudaStream_t stream, const DecodeParams &p, int slots, bool tensor_core);
 int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots);
-int launch_decode_t5(cudaStream_t stream, const DecodeParams &p, int slots, int *status);
+// The fold of the tensor-core split pass as a launch of its own (the same arithmetic, bit for
+// bit, as the fold inside the split pass): p.out and the fields after it say where it goes.
+int launch_decode_fold_tree(cudaStream_t stream, const DecodeParams &p, int slots);
+// Arrival-counter region for a launch on `stream` (-1: none free, use the two-launch form);
+// `counters` = slots * n_kv * arrive_stride must fit a region.
+int decode_arrive_region(cudaStream_t stream, long long counters);
+constexpr int kFoldGroup = 8;          // runs per first-level group of the fold
+constexpr int kArriveRegionInts = 4096;
 // Fold of (acc, max, sum) triples over the split axis; all strides in floats.
 struct FoldParams {
     const float *acc;
@@ -99,18 +155,13 @@ struct FoldParams {
     long long acc_slot, ml_slot, out_slot, out_head_stride;
     int normalize;     // 1: out = acc/sum; 0: out row = [acc (unnormalised) | max | sum]
     const float *gate; // optional, normalize only: out *= sigmoid(gate), laid out as out
-    // Optional: the partials come from the tensor-core split pass with balanced runs, which
-    // leaves only min(splits, 64-key tiles of the live length, run_cap) live runs per head;
-    // the rest are neutral and need not be read. len == nullptr: fold all `splits`.
-    const int *len = nullptr;
-    int len_stride = 0, len_offset = 0, run_cap = 0, share_slots = 0, n_kv = 1;
 };
 int launch_decode_fold(cudaStream_t stream, const FoldParams &p, int n_heads, int slots);
 // Folds the partials into out[slot][h][d] (slot strides in floats).
 int launch_decode_reduce(cudaStream_t stream, const float *part_acc, const float *part_ml,
                          float *out, int n_heads, int head_dim, int splits, int slots,
                          long long acc_slot, long long ml_slot, long long out_slot,
-                         const float *gate = nullptr, const DecodeParams *live_runs = nullptr);
+                         const float *gate = nullptr);
 
 // Scalar chunk attention (attn_chunk_scalar.cu).
 struct ChunkScalarParams {
@@ -151,13 +202,11 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part
                     int splits, int variant, void *workspace, int *status,
                     const float *gate = nullptr);
 
-// Fold + peer-memory exchange + final fold of a sequence-split decode (decode_exchange.cu).
+// Sequence-split decode across GPUs (decode_exchange.cu): workspace size, and the collect
+// half as a launch of its own (p.xch, p.out, p.n_heads are read).
 size_t decode_exchange_bytes(int n_heads, int head_dim, int shards);
-int launch_decode_fold_exchange(cudaStream_t stream, const float *part_acc, const float *part_ml,
-                                float *out, int n_heads, int head_dim, int splits,
-                                void *const *peer_ws, int shards, int rank, int phases,
-                                unsigned wait_limit_us, int *status,
-                                const DecodeParams *live_runs = nullptr);
+int launch_decode_collect(cudaStream_t stream, const DecodeParams &p, int *status);
+void decode_set_two_launch_fold(int on);
 
 // Attention front end and tail (attn_front.cu).
 int launch_q_gate(cudaStream_t stream, const float *q, const float *gate, float *y, long long n);

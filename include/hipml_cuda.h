@@ -162,13 +162,26 @@ int hipml_kv_append_chunk_f32(hipml_stream_t stream, float *k_cache, float *v_ca
                               const float *k, const float *v, int pos0, int width, int tokens);
 
 /* launch_kv::launch_ptrs (crates/hipml-kernels/src/launch_kv.rs:110-280): split-K decode over
- * the q8_0 cache, then the split reduce. `selector` is the reference's kernel id: 0 and 4
- * select the tensor-core kernel (head_dim 256 only), 6 the scalar kernel (any head_dim in
- * 32..256 step 32); other ids are rejected. `stride` is the cache's rows per KV head; the
- * live length is step[1]. Split s covers positions [s*per, min((s+1)*per, seq)),
- * per = ceil(seq/splits). part_acc is f32 [n_heads][splits][head_dim], part_ml f32
- * [n_heads][splits][2] = (max in log2 units, sum). k_off/v_off are byte offsets (multiples
- * of 16) added to k/v. out is f32 [n_heads][head_dim]. */
+ * the q8_0 cache and the fold of the split partials into out f32 [n_heads][head_dim].
+ * `selector` is the reference's kernel id: 0 and 4 select the tensor-core kernel (head_dim 256
+ * only), 1 the same kernel over a q4_0 cache, 6 the scalar kernel (any head_dim in 32..256
+ * step 32); other ids are rejected. `stride` is the cache's rows per KV head; the live length
+ * is step[1]. k_off/v_off are byte offsets (multiples of 16) added to k/v.
+ * part_acc f32 [n_heads][splits][head_dim] and part_ml f32 [n_heads][splits][2] = (max in log2
+ * units, sum) are SCRATCH: only `out` is defined. The reference makes two launches (split pass,
+ * attn_decode_kv_reduce, launch_kv.rs:232-279) with split s over positions [s*per, (s+1)*per),
+ * per = ceil(seq/splits). The scalar kernel (selector 6, or any head_dim other than 256) keeps
+ * exactly that and fills every slot. The tensor-core kernel is ONE launch and deals the rows
+ * out for this device instead: R = max(1, min(splits, ceil(seq/64), CTA slots / n_kv)) runs
+ * per KV head, balanced to within one 64-row tile, partial of run r in slot r; slots from R up
+ * to min(splits, CTA slots / n_kv) receive neutral partials (max -inf, sum 0), slots past that
+ * are not written at all; the CTA that completes a group of eight runs folds it into the
+ * group's first slot, and the last CTA of a KV head folds the groups and writes `out`. A
+ * caller must therefore not point the by-name attn_decode_kv_reduce kernel at these partials.
+ * The tensor-core kernel needs out, part_acc (16 bytes) and part_ml (8 bytes) aligned. Two
+ * calls that may overlap on the device must not share scratch (as in the reference); the
+ * arrival counters of the in-kernel fold are library memory, keyed by stream (and capture),
+ * and need no care from the caller. */
 int hipml_attn_decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
                          const void *k, const void *v, float *part_acc, float *part_ml,
                          float *out, int n_heads, int n_kv, int head_dim, int stride, float scale,
@@ -301,21 +314,26 @@ int hipml_attn_decode_kv_shard(hipml_stream_t stream, const int *step, int selec
 int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, float *out,
                               int n_heads, int head_dim, int shards);
 
-/* The same sequence-split decode with the exchange done by the kernel itself over peer memory
- * instead of a collective call (no counterpart in the reference). Every rank owns a workspace
- * of hipml_decode_exchange_bytes(...) bytes, 256-byte aligned, zero-filled once before the
- * first call, that every other rank has mapped (peer access, IPC handle or symmetric memory);
- * peer_ws is a HOST array of `shards` device pointers, peer_ws[w] = rank w's workspace as
- * mapped in this process, peer_ws[rank] = the local one. One call = split pass over the local
- * rows, then one kernel that folds the local partials, stores the folded triple into every
- * rank's workspace (each value tagged with the call's number in the same 8-byte store), waits
- * until every rank's values of the same call have arrived and folds the shards into out f32
- * [n_heads][head_dim]. All ranks must make
- * the same sequence of calls. phases: 3 = all of it; 1 = split pass + publish only and 2 =
- * wait + final fold only (the two halves, for hosts that drive several ranks from one stream).
- * The wait is bounded by wait_limit_us (capped at 10 s): when it runs out the kernel leaves
- * `out` untouched and hipml_check_device_status reports 31. Safe to capture in a graph and
- * replay (the call counters live in the workspace and only grow). */
+/* The same sequence-split decode with the exchange done by the decode kernel itself over peer
+ * memory instead of a collective call (no counterpart in the reference). Every rank owns a
+ * workspace of hipml_decode_exchange_bytes(...) bytes, 256-byte aligned, zero-filled once
+ * before the first call, that every other rank has mapped (peer access, IPC handle or
+ * symmetric memory); peer_ws is a HOST array of `shards` device pointers, peer_ws[w] = rank w's
+ * workspace as mapped in this process, peer_ws[rank] = the local one. One call = ONE launch:
+ * the split pass over the local rows, whose last CTA per KV head folds the local partials,
+ * stores the folded triples into every rank's workspace (each value tagged with the call's
+ * number in the same 64-bit store), waits until every rank's values of the same call have
+ * arrived and folds the shards into out f32 [n_heads][head_dim]. head_dim 256, selectors 0, 1,
+ * 4. All ranks must make the same sequence of calls. phases: 3 = all of it; 1 = split pass +
+ * publish only and 2 = wait + final fold only, a small launch of its own (the two halves, for
+ * hosts that drive several ranks from one stream). The wait is bounded in time by
+ * wait_limit_us (capped at 10 s): when it runs out the kernel leaves `out` untouched and
+ * hipml_check_device_status reports 31. If a rank misses a call the ranks' call numbers
+ * differ for good: zero every rank's workspace (between steps, with a host barrier) to
+ * resynchronise. Safe to capture in a graph and replay (the call counters live in the
+ * workspace and only grow). The _append form also appends the token's K/V rows (as
+ * hipml_attn_decode_kv_append) on the rank that owns the new position; pass NULL rows on the
+ * others. */
 size_t hipml_decode_exchange_bytes(int n_heads, int head_dim, int shards);
 int hipml_attn_decode_kv_shard_exchange(hipml_stream_t stream, const int *step, int selector,
                                         const float *q, const void *k, const void *v,
@@ -324,6 +342,14 @@ int hipml_attn_decode_kv_shard_exchange(hipml_stream_t stream, const int *step, 
                                         size_t k_off, size_t v_off, void *const *peer_ws,
                                         int shards, int rank, int phases,
                                         unsigned wait_limit_us);
+int hipml_attn_decode_kv_shard_exchange_append(hipml_stream_t stream, const int *step, int selector,
+                                               const float *k_row, const float *v_row,
+                                               const float *q, void *k, void *v, float *part_acc,
+                                               float *part_ml, float *out, int n_heads, int n_kv,
+                                               int head_dim, int stride, float scale, int splits,
+                                               size_t k_off, size_t v_off, void *const *peer_ws,
+                                               int shards, int rank, int phases,
+                                               unsigned wait_limit_us);
 
 /* The same decode for callers that cannot allocate device memory (this entry has no
  * counterpart in the reference): a host that serves from a fixed arena and may not call
@@ -416,6 +442,20 @@ int hipml_attn_chunk_staged_gated(hipml_stream_t stream, const float *q, float *
                                   const float *gate, int n_heads, int n_kv, int head_dim, int pos0,
                                   int tokens, float *part_acc, float *part_ml, int splits, int mode,
                                   int key_capacity, void *workspace, size_t workspace_bytes);
+
+/* Tuning and test knobs of the decode path (no counterpart in the reference).
+ * hipml_set_decode_cta_slots: how many CTAs of the tensor-core decode kernel one round of the
+ * device holds (default 0 = 2 per SM of the current device); a process that shares the GPU
+ * (MPS, a partitioned context) can lower it, and tests use it to reach the plan's limits with
+ * small caches. hipml_set_decode_fold_mode: 0 (default) folds inside the split pass, 1 makes
+ * the fold a second launch with the same arithmetic (bit-identical output).
+ * hipml_decode_plan_quota: host restatement of the multi-slot plan, for tests -- the 64-row
+ * tiles per run that the kernel derives from the live lengths `lens[slots]`; the plan's runs,
+ * sum over slots of max(1, ceil(ceil(len/64) / quota)) * n_kv, never exceed cta_slots.
+ * Returns -1 for arguments outside the plan's domain (cta_slots < 2 * slots * n_kv). */
+int hipml_set_decode_cta_slots(int slots);
+int hipml_set_decode_fold_mode(int mode);
+int hipml_decode_plan_quota(const int *lens, int slots, int splits, int n_kv, int cta_slots);
 
 /* Reads and clears the device status word that kernels with bounded waits set when a wait
  * ran out (0 = none). Synchronises `stream`. Returns HIPML_ERR_DEVICE_STATUS if it was set. */

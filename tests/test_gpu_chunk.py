@@ -101,7 +101,8 @@ def test_other_gqa_groups_and_head_dims():
 
 
 def test_config1_prefill_672_tokens_f32_cache():
-    """BASELINE config 1: T=672, 24/4/256, seed 0, draw order Q, K, V; whole output checked."""
+    """Prefill of T=672 tokens over the f32 cache, 24/4/256, seed 0, draw order Q, K, V; the whole
+    output is checked."""
     heads, n_kv, hd, tok = 24, 4, 256, 672
     rng = O.Rng(0)
     q = rng.normals(tok * heads * hd).reshape(tok, heads * hd)
@@ -114,8 +115,8 @@ def test_config1_prefill_672_tokens_f32_cache():
 
 
 def test_chunk_2048_at_6144_q8_sampled_rows_and_cross_kernel():
-    """The last chunk of BASELINE config 2 (T=8192 in 2048-token chunks): oracle on every
-    64th row, and the full output of the tensor-core kernel against the scalar kernel."""
+    """The last chunk of a T=8192 prefill in 2048-token chunks: oracle on every 64th row, and the
+    full output of the tensor-core kernel against the scalar kernel."""
     from hipml_b200 import api
     heads, n_kv, hd, tok, pos0 = 24, 4, 256, 2048, 6144
     stride = 8200
@@ -148,6 +149,84 @@ def test_chunk_2048_at_6144_q8_sampled_rows_and_cross_kernel():
     rows = np.arange(5, tok, 64)
     _assert_bar(expected[rows], outs[0][rows], 0, "2048@6144 sampled")
     _assert_bar(expected[rows], outs[2][rows], 2, "2048@6144 sampled")
+
+
+_DEEP = {}
+
+
+def _deep_cache(n_keys, stride):
+    """A q8_0 cache of n_keys live rows per KV head (N(0,1) data quantised on the device, seed
+    4) with NaN-scale canary rows from n_keys to `stride`, its bytes and its dequantised
+    position-major values for the oracle. Built once per (n_keys, stride)."""
+    from hipml_b200 import api
+    key = (n_keys, stride)
+    if key not in _DEEP:
+        _DEEP.clear()   # one deep cache at a time: the dequantised copy is 0.8 GB at 100,000 rows
+        n_kv, hd = 4, 256
+        g = torch.Generator(device="cuda").manual_seed(4)
+        canary = np.zeros((n_kv, stride, 8, 34), dtype=np.uint8)
+        canary[..., 0], canary[..., 1], canary[..., 2:] = 0x00, 0x7E, 0x55   # f16 NaN scales
+        kc = _dev(canary.reshape(-1))
+        vc = kc.clone()
+        for p0 in range(0, n_keys, 8192):
+            n = min(8192, n_keys - p0)
+            api.kv_encode_bulk(torch.randn(n, n_kv * hd, device="cuda", generator=g),
+                               torch.randn(n, n_kv * hd, device="cuda", generator=g), kc, vc, n_kv, hd,
+                               stride, p0, 0, n)
+        torch.cuda.synchronize()
+        kb = kc.cpu().numpy().reshape(n_kv, stride, 272)[:, :n_keys]
+        vb = vc.cpu().numpy().reshape(n_kv, stride, 272)[:, :n_keys]
+        kq = cases.unpack_head_major(O.dequantize_q8(kb), n_kv, n_keys, hd)
+        vq = cases.unpack_head_major(O.dequantize_q8(vb), n_kv, n_keys, hd)
+        _DEEP[key] = (kc, vc, kq, vq)
+    return _DEEP[key]
+
+
+@pytest.mark.parametrize("pos0,tok,n_keys,stride", [
+    (8192, 2048, 10240, 10248),       # the first chunk past the split gate
+    (30720, 2048, 32768, 32776),
+    (98304, 1696, 100000, 100008),    # the last chunk of a 100,000-token prefill
+], ids=["2048@8192", "2048@30720", "1696@98304"])
+def test_chunk_past_the_split_gate_sampled_rows(pos0, tok, n_keys, stride):
+    """The reference switches to key-split prefill for chunks at pos0 >= 8192
+    (crates/hipml-model/src/gpu/attn_tile.rs:122-151) and checks its chunk kernel at a non-zero
+    position on purpose (crates/hipml-cli/src/attn_chunk_parity.rs:4-8,124-207). Here: chunks at
+    8,192, 30,720 and 98,304 over a q8_0 cache with stride beyond the live length, the CTA-pair
+    and the single-CTA form, one pass and the reference's 8 key slices, every result held to
+    max-abs 2e-3 AND rel-L2 1e-4 against the oracle over the dequantised cache on 8 sampled
+    rows x 24 heads (the last row included: it sees every key tile), plus all rows of each
+    variant against the first (a dropped or double-counted key tile would show there too)."""
+    from hipml_b200 import api
+    heads, n_kv, hd = 24, 4, 256
+    kc, vc, kq, vq = _deep_cache(n_keys, stride)
+    g = torch.Generator(device="cuda").manual_seed(40 + pos0)
+    q = torch.randn(tok, heads * hd, device="cuda", generator=g)
+    step = tok // 8
+    row0 = (tok - 1) % step
+    rows = np.arange(row0, tok, step)
+    c = cases.ChunkCase(q.cpu().numpy(), kq, vq, None, None, heads, n_kv, hd, pos0, tok, stride)
+    expected = cases.chunk_expected(c, rows=(row0, step), threads=16)[rows]
+    ws = torch.full((api.attn_chunk_workspace_bytes(n_kv, hd, pos0, tok),), 0xFF, dtype=torch.uint8,
+                    device="cuda")
+    qslots = (tok + 31) // 32 * 32
+    first = None
+    for mode, splits in ((0, 1), (0, 8), (3, 1), (3, 8)):
+        assert api.prefill_splits(pos0) == 8
+        pa = pm = None
+        if splits >= 2:
+            pa = torch.full((splits * qslots * heads * hd,), float("nan"), device="cuda")
+            pm = torch.full((splits * qslots * heads * 2,), float("nan"), device="cuda")
+        out = torch.full((tok, heads * hd), float("nan"), device="cuda")
+        api.attn_chunk(q, kc, vc, out, heads, n_kv, hd, pos0, tok, 1, stride, pa, pm, splits, mode, ws)
+        assert api.check_device_status() == 0
+        got = out.cpu().numpy()
+        _assert_bar(expected, got[rows], mode, f"{tok}@{pos0} x{splits}")
+        if first is None:
+            first = got
+        else:
+            _assert_bar(first, got, mode, f"{tok}@{pos0} x{splits} vs the pair form, all rows")
+        del out, pa, pm
+    del ws
 
 
 def test_split_partials_layout_and_combine():

@@ -55,11 +55,9 @@ def _assert_close(expected, got, tight=2e-5):
     assert ma <= tight and rl <= tight, (ma, rl)
 
 
-@pytest.mark.parametrize("selector", [0, 5, 6], ids=["tensor_core", "tcgen05", "scalar"])
+@pytest.mark.parametrize("selector", [0, 6], ids=["tensor_core", "scalar"])
 @pytest.mark.parametrize("case", cases.KV_CASES, ids=lambda c: c.name)
 def test_reference_kv_cases(case, selector):
-    if selector == 5 and case.dim != 256:
-        pytest.skip("the tcgen05 body is head_dim 256 only")
     q, kb, vb = cases.kv_case_inputs(case)
     expected = cases.kv_case_expected(case, q, kb, vb)
     got, acc, ml = _run_decode(q, kb, vb, case.heads, case.n_kv, case.dim, case.seq, case.seq,
@@ -69,7 +67,7 @@ def test_reference_kv_cases(case, selector):
     assert not np.isnan(acc).any() and not np.isnan(ml).any()
 
 
-@pytest.mark.parametrize("selector", [0, 5, 6], ids=["tensor_core", "tcgen05", "scalar"])
+@pytest.mark.parametrize("selector", [0, 6], ids=["tensor_core", "scalar"])
 def test_reference_deep_case_100000_tokens(selector):
     c = cases.DEEP_CASE
     q, kb, vb = cases.kv_case_inputs(c)
@@ -79,7 +77,7 @@ def test_reference_deep_case_100000_tokens(selector):
     _assert_close(expected, got)
 
 
-@pytest.mark.parametrize("selector", [0, 5, 6], ids=["tensor_core", "tcgen05", "scalar"])
+@pytest.mark.parametrize("selector", [0, 6], ids=["tensor_core", "scalar"])
 @pytest.mark.parametrize("seq,pad", [(1, 7), (63, 1), (64, 0), (65, 200), (127, 3), (129, 0), (672, 136),
                                      (2500, 600)])
 def test_shipped_shape_with_stride_beyond_live_length(seq, pad, selector):
@@ -97,9 +95,7 @@ def test_shipped_shape_with_stride_beyond_live_length(seq, pad, selector):
     splits = api.decode_splits(seq)
     got, _, _ = _run_decode(q, kc, vc, heads, n_kv, hd, seq, stride, scale, splits, selector)
     _assert_close(expected, got)
-    if selector == 5:
-        from hipml_b200 import api as _api
-        assert _api.check_device_status() == 0
+    assert api.check_device_status() == 0
 
 
 def test_more_splits_than_positions_leaves_empty_partials_neutral():
@@ -108,7 +104,7 @@ def test_more_splits_than_positions_leaves_empty_partials_neutral():
     q = rng.normals(heads * hd)
     kb, vb = O.quantize_q8(rng.normals(seq * hd)), O.quantize_q8(rng.normals(seq * hd))
     expected = O.attn_decode_kv_q8(q, kb, vb, heads, n_kv, hd, seq, 0.0625)
-    for selector in (0, 5, 6):
+    for selector in (0, 6):
         got, acc, ml = _run_decode(q, kb, vb, heads, n_kv, hd, seq, seq, 0.0625, splits, selector)
         _assert_close(expected, got)
         ml = ml.reshape(heads, splits, 2)
@@ -529,3 +525,210 @@ def test_batched_plan_follows_the_lengths_across_graph_replays():
             assert n <= depths[s] + 1
             want = O.attn_decode_kv_q8(q[s], kc[s], vc[s], heads, n_kv, hd, n, 0.0625, stride=stride)
             _assert_close(want, got[s])
+
+
+# ---- the fold inside the split pass ------------------------------------------------------------
+
+@pytest.mark.parametrize("seq", [1, 64, 513, 700, 4097, 30000])
+@pytest.mark.parametrize("gated", [False, True], ids=["plain", "gated"])
+def test_fold_inside_the_split_pass_equals_the_second_launch_bit_for_bit(seq, gated):
+    """One launch per decode step: the last CTA of every group of eight runs folds the group,
+    the last CTA of a KV head folds the groups and writes the output. The same arithmetic as a
+    launch of its own (the reference's two-launch shape, launch_kv.rs:232-279) must give the
+    same bits, whichever CTA happens to arrive last; three repetitions reuse the counters."""
+    from hipml_b200 import api
+    heads, n_kv, hd, scale = 24, 4, 256, 0.0625
+    stride = seq + 5
+    rng = O.Rng(0xF01D + seq)
+    kc, vc = _canary_cache(n_kv, stride, 272), _canary_cache(n_kv, stride, 272)
+    kc[:, :seq] = O.quantize_q8(rng.normals(n_kv * seq * hd)).reshape(n_kv, seq, 272)
+    vc[:, :seq] = O.quantize_q8(rng.normals(n_kv * seq * hd)).reshape(n_kv, seq, 272)
+    dk, dv = _dev(kc), _dev(vc)
+    splits = api.decode_splits(seq)
+    step = _step(seq - 1, seq)
+    gate = _dev(rng.normals(heads * hd)) if gated else None
+    outs = {}
+    try:
+        for mode in (1, 0):
+            api.set_decode_fold_mode(mode)
+            for rep in range(3):
+                q = O.Rng(0xF01E + rep).normals(heads * hd)
+                acc = torch.full((heads * splits * hd,), float("nan"), device="cuda")
+                ml = torch.full((heads * splits * 2,), float("nan"), device="cuda")
+                out = torch.full((heads * hd,), float("nan"), device="cuda")
+                if gated:
+                    api.attn_decode_kv_gated(step, _dev(q), dk, dv, acc, ml, out, gate, heads, n_kv, hd,
+                                             stride, scale, splits)
+                else:
+                    api.attn_decode_kv(step, _dev(q), dk, dv, acc, ml, out, heads, n_kv, hd, stride,
+                                       scale, splits)
+                torch.cuda.synchronize()
+                outs[(mode, rep)] = out.cpu().numpy()
+                if not gated:
+                    want = O.attn_decode_kv_q8(q, kc, vc, heads, n_kv, hd, seq, scale, stride=stride)
+                    _assert_close(want, outs[(mode, rep)])
+    finally:
+        api.set_decode_fold_mode(0)
+    assert api.check_device_status() == 0
+    for rep in range(3):
+        assert np.array_equal(outs[(0, rep)], outs[(1, rep)])
+
+
+def test_single_stream_step_replays_from_a_graph_with_growing_length():
+    """The arrival counters of the in-kernel fold return to zero by themselves: one captured
+    launch serves every replay while the live length (read on the device) grows past a group
+    and a tile boundary."""
+    from hipml_b200 import api
+    heads, n_kv, hd, scale, cap = 24, 4, 256, 0.0625, 1200
+    rng = O.Rng(0x6EA9)
+    q = rng.normals(heads * hd)
+    kc = O.quantize_q8(rng.normals(n_kv * cap * hd)).reshape(n_kv, cap, 272)
+    vc = O.quantize_q8(rng.normals(n_kv * cap * hd)).reshape(n_kv, cap, 272)
+    dq, dk, dv = _dev(q), _dev(kc), _dev(vc)
+    splits = api.decode_splits(cap)
+    step = _step(0, 1)
+    acc = torch.empty(heads * splits * hd, device="cuda")
+    ml = torch.empty(heads * splits * 2, device="cuda")
+    out = torch.full((heads * hd,), float("nan"), device="cuda")
+
+    def launch():
+        api.attn_decode_kv(step, dq, dk, dv, acc, ml, out, heads, n_kv, hd, cap, scale, splits)
+
+    launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            launch()
+    torch.cuda.current_stream().wait_stream(side)
+    for seq in (1, 511, 512, 513, 577, 1200, 64):
+        step.copy_(torch.tensor([seq - 1, seq, 0, 0, 0, 0, 0, 0], dtype=torch.int32))
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        want = O.attn_decode_kv_q8(q, kc, vc, heads, n_kv, hd, seq, scale, stride=cap)
+        _assert_close(want, out.cpu().numpy())
+    assert api.check_device_status() == 0
+
+
+def test_two_streams_decode_side_by_side_with_their_own_counters():
+    """Launches that may overlap on the device get different arrival-counter regions (keyed by
+    stream): two streams, each with its own scratch, interleaved many times."""
+    from hipml_b200 import api
+    heads, n_kv, hd, scale, seq = 24, 4, 256, 0.0625, 9000
+    rng = O.Rng(0x2575)
+    kc = O.quantize_q8(rng.normals(n_kv * seq * hd)).reshape(n_kv, seq, 272)
+    vc = O.quantize_q8(rng.normals(n_kv * seq * hd)).reshape(n_kv, seq, 272)
+    dk, dv = _dev(kc), _dev(vc)
+    splits = api.decode_splits(seq)
+    step = _step(seq - 1, seq)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    qs = [rng.normals(heads * hd) for _ in streams]
+    dq = [_dev(x) for x in qs]
+    bufs = [(torch.empty(heads * splits * hd, device="cuda"), torch.empty(heads * splits * 2, device="cuda"),
+             torch.full((20, heads * hd), float("nan"), device="cuda")) for _ in streams]
+    torch.cuda.synchronize()
+    for rep in range(20):
+        for i, s in enumerate(streams):
+            with torch.cuda.stream(s):
+                acc, ml, out = bufs[i]
+                api.attn_decode_kv(step, dq[i], dk, dv, acc, ml, out[rep], heads, n_kv, hd, seq, scale,
+                                   splits)
+    torch.cuda.synchronize()
+    assert api.check_device_status() == 0
+    for i in range(2):
+        want = O.attn_decode_kv_q8(qs[i], kc, vc, heads, n_kv, hd, seq, scale)
+        got = bufs[i][2].cpu().numpy()
+        _assert_close(want, got[0])
+        for rep in range(1, 20):
+            assert np.array_equal(got[rep], got[0])
+
+
+@pytest.mark.parametrize("slots,cta_slots", [(2, 16), (3, 24), (5, 64)])
+def test_batched_plan_with_few_cta_slots_still_covers_every_row(slots, cta_slots):
+    """The multi-slot plan must fit the CTAs that are launched whatever the lengths are: with
+    the device's CTA slots forced small, long slots need a quota far above the first guess
+    (runs the grid does not hold would never be computed)."""
+    from hipml_b200 import api
+    stride = 4200
+    heads, n_kv, hd, depths, q, kc, vc = _batch_setup(slots, stride, 0x51 + slots, 3000, 4100)
+    splits = api.batch_splits(stride, slots)
+    slot_bytes = n_kv * stride * 272
+    acc_slot, ml_slot, q_slot = heads * splits * hd, heads * splits * 2, heads * hd
+    pos = torch.tensor([[d, d + 1] for d in depths], dtype=torch.int32, device="cuda")
+    out = torch.full((slots, q_slot), float("nan"), device="cuda")
+    acc = torch.full((slots * acc_slot,), float("nan"), device="cuda")
+    ml = torch.full((slots * ml_slot,), float("nan"), device="cuda")
+    quota = api.decode_plan_quota([d + 1 for d in depths], splits, n_kv, cta_slots)
+    runs = sum(max(1, -(-(-(-(d + 1) // 64)) // quota)) for d in depths) * n_kv
+    assert 0 < runs <= cta_slots
+    try:
+        api.set_decode_cta_slots(cta_slots)
+        api.attn_decode_batch(pos, _dev(q), _dev(kc), _dev(vc), acc, ml, out, heads, n_kv, hd, stride,
+                              0.0625, splits, slot_bytes, acc_slot, ml_slot, q_slot, slots, 0)
+        torch.cuda.synchronize()
+    finally:
+        api.set_decode_cta_slots(0)
+    assert api.check_device_status() == 0
+    got = out.cpu().numpy()
+    for s, d in enumerate(depths):
+        expected = O.attn_decode_kv_q8(q[s], kc[s], vc[s], heads, n_kv, hd, d + 1, 0.0625,
+                                       stride=stride)
+        _assert_close(expected, got[s])
+
+
+def test_slot_without_rows_gets_a_zero_output_row():
+    from hipml_b200 import api
+    slots, stride = 3, 512
+    heads, n_kv, hd, depths, q, kc, vc = _batch_setup(slots, stride, 0x0E, 100, 400)
+    splits = api.batch_splits(stride, slots)
+    slot_bytes = n_kv * stride * 272
+    acc_slot, ml_slot, q_slot = heads * splits * hd, heads * splits * 2, heads * hd
+    lens = [depths[0] + 1, 0, depths[2] + 1]
+    pos = torch.tensor([[max(n - 1, 0), n] for n in lens], dtype=torch.int32, device="cuda")
+    out = torch.full((slots, q_slot), float("nan"), device="cuda")
+    acc = torch.empty(slots * acc_slot, device="cuda")
+    ml = torch.empty(slots * ml_slot, device="cuda")
+    api.attn_decode_batch(pos, _dev(q), _dev(kc), _dev(vc), acc, ml, out, heads, n_kv, hd, stride,
+                          0.0625, splits, slot_bytes, acc_slot, ml_slot, q_slot, slots, 0)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert np.all(got[1] == 0.0)
+    for s in (0, 2):
+        want = O.attn_decode_kv_q8(q[s], kc[s], vc[s], heads, n_kv, hd, lens[s], 0.0625, stride=stride)
+        _assert_close(want, got[s])
+
+
+def test_exchange_in_one_launch_with_a_single_rank():
+    """phases = 3 on one rank: the folding CTA publishes to its own table and collects from it
+    inside the split pass (nothing to wait for), with the append fused in."""
+    from hipml_b200 import api
+    heads, n_kv, hd, scale, seq = 24, 4, 256, 0.0625, 1500
+    stride = seq + 8
+    rng = O.Rng(0x0E1C)
+    kc, vc = _canary_cache(n_kv, stride, 272), _canary_cache(n_kv, stride, 272)
+    kc[:, :seq - 1] = O.quantize_q8(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, 272)
+    vc[:, :seq - 1] = O.quantize_q8(rng.normals(n_kv * (seq - 1) * hd)).reshape(n_kv, seq - 1, 272)
+    k_row, v_row = rng.normals(n_kv * hd), rng.normals(n_kv * hd)
+    dk, dv = _dev(kc), _dev(vc)
+    ws = torch.zeros(api.decode_exchange_bytes(heads, hd, 1), dtype=torch.uint8, device="cuda")
+    splits = api.decode_splits(seq)
+    acc = torch.empty(heads * splits * hd, device="cuda")
+    ml = torch.empty(heads * splits * 2, device="cuda")
+    for tok in range(2):
+        q = rng.normals(heads * hd)
+        out = torch.full((heads * hd,), float("nan"), device="cuda")
+        rows = (_dev(k_row), _dev(v_row)) if tok == 0 else (None, None)
+        api.attn_decode_kv_shard_exchange_append(_step(seq - 1, seq), rows[0], rows[1], _dev(q), dk, dv,
+                                                 acc, ml, out, heads, n_kv, hd, stride, scale, splits,
+                                                 [ws.data_ptr()], 0, phases=3, wait_limit_us=1000)
+        assert api.check_device_status() == 0
+        kb = dk.cpu().numpy().reshape(n_kv, stride, 272)
+        vb = dv.cpu().numpy().reshape(n_kv, stride, 272)
+        assert np.array_equal(kb[:, seq - 1], O.quantize_q8(k_row).reshape(n_kv, 272))
+        want = O.attn_decode_kv_q8(q, kb, vb, heads, n_kv, hd, seq, scale, stride=stride)
+        _assert_close(want, out.cpu().numpy())
+    hdr = ws[:256].view(torch.int32).cpu().numpy()
+    assert hdr[0] == 2 and hdr[1] == 0
