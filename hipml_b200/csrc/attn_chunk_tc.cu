@@ -89,6 +89,13 @@ constexpr int kSmemNeed = kQBytes + kStages * kStageBytes + 256 /*barriers*/ + k
 constexpr int kSmemBytes = 232448;        // everything an SM offers: kSmemNeed + 768 B of alignment slack
 constexpr unsigned kSpinLimit = 1u << 22;        // polls per wait before giving up
 constexpr float kRescaleThreshold = 8.0f;        // log2 units: P stays <= 256
+// The tensor cores add into the f32 accumulators with less than f32 rounding: measured against
+// the f32 definition, the relative-L2 error of O grows by ~3.5e-9 per key of an unbroken
+// accumulation chain (3.4e-5 at 10,000 keys, 3.5e-4 at 100,000). Every kFlushTiles key tiles
+// the softmax warps therefore move O out of TMEM into the output rows in memory (added there
+// in f32 by the CUDA cores) and the next PV product starts a fresh accumulator, which bounds
+// the chain at 8,192 keys whatever the depth. Rows that see at most 8,192 keys never flush.
+constexpr int kFlushTiles = 64;
 
 // ------------------------------------------------------------------ PTX helpers
 
@@ -486,7 +493,9 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             };
             auto pv = [&](int i) {
                 const unsigned a_base = tmem_s[i & 1];
-                const unsigned later = i != 0;   // only the first tile's first MMA overwrites O
+                // the first MMA of the first tile, and of every tile that follows a flush of O to
+                // memory, overwrites the accumulator
+                const unsigned later = (i % kFlushTiles) != 0;
 #pragma unroll
                 for (int kc = 0; kc < 2; kc++)
 #pragma unroll
@@ -535,8 +544,17 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
         const int qi = min(r / p.group, nq - 1);            // dead rows shadow a live query
         const int kmax = p.pos0 + t0 + qi;                  // last visible cache row
         float m_used = -INFINITY, l = 0.0f;
+        float m_glob = -INFINITY;   // reference maximum of the part of O already moved to memory
         bool ok = true;
         unsigned v[32];
+        // where this thread's half row of the output (or of the slice's partial) lives
+        const bool live = r < rows_live;
+        const int rq = r / p.group, rh = r - rq * p.group;
+        const int h = kvh * p.group + rh;
+        const bool norm = p.splits < 2;
+        const size_t slot = ((size_t)sp * p.qslots + (t0 + rq)) * p.n_heads + h;
+        float *const dst = (norm ? p.out + ((size_t)(t0 + rq) * p.n_heads + h) * kD : p.part_acc + slot * kD) +
+                           128 * half;
         // x-th meeting of the two halves: returns the other half's value
         auto meet = [&](int x, float mine, float &other) -> bool {
             float *buf = xch + (x & 1) * 256;
@@ -570,9 +588,42 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
             // Rescale O only when the maximum moved by more than the threshold (P <= 2^8
             // otherwise); the decision is per warp because the TMEM accesses are collective
             // (both halves of a row see the same maxima, so they decide alike).
-            const bool want = (i > 0) && (m_new > m_used + kRescaleThreshold ||
-                                          (m_used == -INFINITY && m_new > -INFINITY));
+            const bool flush = i > 0 && (i % kFlushTiles) == 0;   // the same in every thread of the pair
+            const bool want = !flush && (i > 0) && (m_new > m_used + kRescaleThreshold ||
+                                                    (m_used == -INFINITY && m_new > -INFINITY));
             if (i == 0) m_used = m_new;
+            if (flush) {
+                // O (relative to m_used) leaves TMEM: memory += O, in f32, and PV(i) starts afresh
+                ok = mbar_wait(bar_o + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, peer_abort, p.status, 6);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                tc_fence_after();
+                const bool first = m_glob == -INFINITY;
+                const float cg = first ? 0.0f : exp2f(m_glob - m_used);
+#pragma unroll 1
+                for (int j = 0; j < 4; j++) {
+                    tmem_ld32(tmem_o + lane_addr + 128 * half + 32 * j, v);
+                    if (live) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4) {
+                            float4 *at = reinterpret_cast<float4 *>(dst + 32 * j + e);
+                            float4 w = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                                   __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                            if (!first) {
+                                const float4 g = *at;
+                                w.x = fmaf(g.x, cg, w.x);
+                                w.y = fmaf(g.y, cg, w.y);
+                                w.z = fmaf(g.z, cg, w.z);
+                                w.w = fmaf(g.w, cg, w.w);
+                            }
+                            *at = w;
+                        }
+                    }
+                }
+                tc_fence_before();
+                m_glob = m_used;
+                l *= (m_used == -INFINITY) ? 0.0f : exp2f(m_used - m_new);
+                m_used = m_new;
+            }
             if (__any_sync(0xffffffffu, want)) {
                 ok = mbar_wait(bar_o + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, peer_abort, p.status, 6);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
@@ -630,17 +681,12 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                            peer_abort, p.status, 7);
         }
         ok = __all_sync(0xffffffffu, ok);
-        const bool live = r < rows_live;
-        const int rq = r / p.group, rh = r - rq * p.group;
-        const int h = kvh * p.group + rh;
         if (ok) {
             griddep_wait();   // (already satisfied unless the CTA had no key tiles to wait for)
             tc_fence_after();
-            const bool norm = p.splits < 2;
             const float inv = norm ? (l > 0.0f ? 1.0f / l : 0.0f) : 1.0f;
-            const size_t slot = ((size_t)sp * p.qslots + (t0 + rq)) * p.n_heads + h;
-            float *dst = (norm ? p.out + ((size_t)(t0 + rq) * p.n_heads + h) * kD : p.part_acc + slot * kD) +
-                         128 * half;
+            const bool flushed = m_glob != -INFINITY;   // part of O is in memory already
+            const float cg = flushed ? exp2f(m_glob - m_used) : 0.0f;
             const float *gsrc =
                 (norm && p.gate) ? p.gate + ((size_t)(t0 + rq) * p.n_heads + h) * kD + 128 * half : nullptr;
 #pragma unroll 1
@@ -649,11 +695,21 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                 if (live) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 4) {
-                        float4 w;
-                        w.x = n_tiles > 0 ? __uint_as_float(v[e]) * inv : 0.0f;
-                        w.y = n_tiles > 0 ? __uint_as_float(v[e + 1]) * inv : 0.0f;
-                        w.z = n_tiles > 0 ? __uint_as_float(v[e + 2]) * inv : 0.0f;
-                        w.w = n_tiles > 0 ? __uint_as_float(v[e + 3]) * inv : 0.0f;
+                        float4 w = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        if (n_tiles > 0)
+                            w = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                            __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+                        if (flushed) {
+                            const float4 g = *reinterpret_cast<const float4 *>(dst + 32 * j + e);
+                            w.x = fmaf(g.x, cg, w.x);
+                            w.y = fmaf(g.y, cg, w.y);
+                            w.z = fmaf(g.z, cg, w.z);
+                            w.w = fmaf(g.w, cg, w.w);
+                        }
+                        w.x *= inv;
+                        w.y *= inv;
+                        w.z *= inv;
+                        w.w *= inv;
                         if (gsrc) {   // the layer's output gate, applied where the row is produced
                             const float4 g = *reinterpret_cast<const float4 *>(gsrc + 32 * j + e);
                             w.x *= 1.0f / (1.0f + expf(-g.x));

@@ -881,7 +881,8 @@ void decode_set_two_launch_fold(int on) { g_two_launch_fold.store(on ? 1 : 0); }
 // Which arrival-counter region a launch on `stream` uses. Two launches may share a region
 // only if they cannot overlap on the device, so the key is what serialises launches: the
 // stream (by its process-unique id), and under stream capture also the capture sequence (two
-// graphs captured from one stream may later run side by side). A key keeps its region for
+// graphs captured from one stream may later run side by side; capture ids start at 1, so a
+// captured launch never shares a key with an eager one). A key keeps its region for
 // the life of the process; when the regions run out the caller takes the two-launch form.
 int decode_arrive_region(cudaStream_t stream, long long counters) {
     if (counters > kArriveRegionInts || g_two_launch_fold.load()) return -1;
@@ -889,12 +890,21 @@ int decode_arrive_region(cudaStream_t stream, long long counters) {
     if (cudaGetDevice(&dev) != cudaSuccess) return -1;
     unsigned long long sid = 0, cap = 0;
     cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-    if (cudaStreamGetId(stream, &sid) != cudaSuccess ||
-        cudaStreamGetCaptureInfo(stream, &st, &cap) != cudaSuccess) {
+    if (cudaStreamGetCaptureInfo(stream, &st, &cap) != cudaSuccess) {
         cudaGetLastError();
         return -1;
     }
-    if (st != cudaStreamCaptureStatusActive) cap = 0;
+    if (st == cudaStreamCaptureStatusActive) {
+        // (only capture-safe calls here) the streams of one capture are all alive, so their
+        // handles tell them apart
+        sid = (unsigned long long)reinterpret_cast<uintptr_t>(stream);
+    } else {
+        cap = 0;
+        if (cudaStreamGetId(stream, &sid) != cudaSuccess) {
+            cudaGetLastError();
+            return -1;
+        }
+    }
     static std::mutex mu;
     static std::map<std::tuple<int, unsigned long long, unsigned long long>, int> table;
     static int next_free[64] = {};
