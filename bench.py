@@ -1088,9 +1088,20 @@ def profile_case(args):
     entry.build()
     from hipml_b200 import api
     torch.cuda.set_device(0)
+    api.set_decode_fold_mode(args.fold_mode)
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(7)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.reps)]
+    if args.case == "decode_steps":
+        # the decode section of the benchmark alone: 128 graph-captured steps x 16 layers per depth
+        pk = peaks()
+        depths = DECODE_DEPTHS if args.depth == 100000 and args.all_depths else (args.depth,)
+        for r in decode_bench(torch, api, depths, DECODE_STEPS, LAYERS, pk["hbm_gbs"]):
+            print(json.dumps(r))
+        if args.all_depths:
+            for r in decode_batched(torch, api, (8, 16), LAYERS, pk["hbm_gbs"]):
+                print(json.dumps({k: v for k, v in r.items() if k != "depths"}))
+        return
     if args.case == "front":
         r = front_end_bench(torch, api, peaks()["hbm_gbs"], reps=args.reps)
         print(json.dumps({"case": "front end of a 2048-token chunk", **r}))
@@ -1203,7 +1214,7 @@ def profile_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", choices=["chunk", "decode", "front", "batched"], default=None,
+    ap.add_argument("--case", choices=["chunk", "decode", "front", "batched", "decode_steps"], default=None,
                     help="run one small profiling case instead of the benchmark")
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--mode", type=int, default=0)
@@ -1216,6 +1227,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="hipml_b200")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--all-depths", action="store_true", help="decode_steps: every depth and the batched cases")
+    ap.add_argument("--fold-mode", type=int, default=0, help="decode cases: 1 = the fold as its own launch")
     args = ap.parse_args()
     if args.case:
         profile_case(args)

@@ -56,8 +56,7 @@ constexpr int kStages = 3;                       // ring depth (tiles of K and V
 constexpr unsigned kSpinLimit = 1u << 24;        // polls of a full barrier before giving up
 
 // Dynamic shared memory: stage[3] = (K tile | V tile) | scores [2][8][72] f32 | weights hi,
-// lo [8][72] f16 | corr[8] f32 | full barriers [3]. The query staging area [8][256] f32
-// aliases stage 2 during set-up (stage 2 is first filled after the set-up).
+// lo [8][72] f16 | corr[8] f32 | full barriers [3].
 constexpr int kOffSs = 2 * kStages * kTileBytes;
 constexpr int kOffPh = kOffSs + 2 * 8 * kSsStride * 4;
 constexpr int kOffPl = kOffPh + 8 * kPStride * 2;
@@ -438,19 +437,18 @@ __device__ __forceinline__ void fold_tail(const DecodeParams &p, int *status, in
     const int expect = min(kFoldGroup, runs - grp * kFoldGroup);
     int *ctr = g_arrive + (size_t)p.arrive_region * kArriveRegionInts +
                (size_t)(slot * p.n_kv + kvh) * p.arrive_stride;
-    __threadfence();   // this CTA's partial, before its arrival
+    // (every thread's partial stores precede the barrier; the arrival releases them)
     __syncthreads();
     if (tid == 0) {
         int role = 1;
         if (expect > 1) {
-            role = atomicAdd(ctr + 1 + grp, 1) == expect - 1;
+            role = arrive_acq_rel(ctr + 1 + grp) == expect - 1;
             if (role) ctr[1 + grp] = 0;
         }
         s_role = role;
     }
     __syncthreads();
     if (!s_role) return;
-    __threadfence();   // the others' partials, after their arrivals
     const int h = kvh * group + warp;
     float *pa = p.part_acc + (size_t)slot * p.acc_slot + (size_t)h * p.splits * 256;
     float *ml = p.part_ml + (size_t)slot * p.ml_slot + (size_t)h * p.splits * 2;
@@ -458,16 +456,14 @@ __device__ __forceinline__ void fold_tail(const DecodeParams &p, int *status, in
     if (warp < group) f = fold_warp(pa, ml, grp * kFoldGroup, 1, expect, lane);
     if (ngroups > 1) {
         if (warp < group) fold_store_partial(pa, ml, grp * kFoldGroup, f, lane);
-        __threadfence();
         __syncthreads();
         if (tid == 0) {
-            const int role = atomicAdd(ctr, 1) == ngroups - 1;
+            const int role = arrive_acq_rel(ctr) == ngroups - 1;
             if (role) ctr[0] = 0;
             s_role = role;
         }
         __syncthreads();
         if (!s_role) return;
-        __threadfence();
         if (warp < group) f = fold_warp(pa, ml, 0, kFoldGroup, ngroups, lane);
     }
     fold_finish(p, status, slot, kvh, group, f);
@@ -484,12 +480,10 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     griddep_wait();
     auto ktile_at = [&](int stage) { return smem + 2 * stage * kTileBytes; };
     auto vtile_at = [&](int stage) { return smem + (2 * stage + 1) * kTileBytes; };
-    float *qs = reinterpret_cast<float *>(ktile_at(2));              // set-up only
     float *ss = reinterpret_cast<float *>(smem + kOffSs);            // [2][8][kSsStride]
     __half *ph = reinterpret_cast<__half *>(smem + kOffPh);          // [8][kPStride]
     __half *pl = reinterpret_cast<__half *>(smem + kOffPl);
     float *corr_s = reinterpret_cast<float *>(smem + kOffCorr);      // [8]
-    float *qsum_s = ss;                                              // [8][8], set-up only
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -544,6 +538,24 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         split = s_plan[2];
         if (slot < 0) return;
     }
+    // The query values this lane feeds to the tensor cores, loaded straight into registers
+    // before anything that depends on the live length, so that the two round trips overlap.
+    float qv[8][4];
+    {
+        const float *qh = p.q + (size_t)slot * p.q_slot + (size_t)(kvh * group + g) * 256;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+            const int blk = dh * 4 + (ks >> 1), j = (ks & 1) * 4 + t;
+#pragma unroll
+            for (int i = 0; i < 4; i += 2) {
+                const int d = kQ4 ? k_word_dim_q4(blk, t, i) + 16 * (ks & 1) : k_word_dim(blk, j, i);
+                float2 x = make_float2(0.0f, 0.0f);
+                if (g < group) x = *reinterpret_cast<const float2 *>(qh + d);
+                qv[ks][i] = x.x;
+                qv[ks][i + 1] = x.y;
+            }
+        }
+    }
     int lo, hi;
     split_range(p, slot, split, p.share_slots > 0 ? s_plan[3] : 0, lo, hi);
     const int ntiles = (hi - lo + kTile - 1) / kTile;
@@ -585,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         const unsigned bytes = (unsigned)(min(kTile, hi - r0) * kSrcRow);
         const size_t off = (size_t)r0 * kSrcRow;
         constexpr int kDst = 0;
-        // earlier generic-proxy writes to the stage (zero fill, query staging) come first
+        // earlier generic-proxy writes to the stage (the zero fill of a short tile) come first
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * bytes);
         bulk_load(smem_u32(ktile_at(stage)) + kDst, kbase + off, bytes, bar_full + 8 * stage);
@@ -599,55 +611,43 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
         if (ntiles > 1) fetch(1);
     }
 
-    // Query rows of this KV head's group in log2 units; rows past the group are zero.
-    const float *q = p.q + (size_t)slot * p.q_slot + (size_t)kvh * group * 256;
-    for (int i = tid; i < 8 * 256; i += kThreads)
-        qs[i] = (i >> 8) < group ? q[i] * p.scale_log2 : 0.0f;
-    __syncthreads();
-
     // B fragments of the query for this warp's four blocks and both 16-slot steps of each:
     // column g = head g, as an f16 high and low part ({hi b0, hi b1, lo b0, lo b1}); the
     // contraction slots follow k_word's order (slots 2t, 2t+1 = bytes 0, 1 of word t, slots
-    // 2t+8, 2t+9 = bytes 2, 3).
+    // 2t+8, 2t+9 = bytes 2, 3). The 32 values a lane needs arrived in registers (qv, loaded
+    // straight from memory in that order while the first tiles were being fetched); rows past
+    // the group are zero. Scores are kept in log2 units.
     unsigned qb[8][4];
-#pragma unroll
-    for (int ks = 0; ks < 8; ks++) {
-        const int blk = dh * 4 + (ks >> 1), j = (ks & 1) * 4 + t;
-        __half xh[4], xl[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float x = qs[g * 256 + (kQ4 ? k_word_dim_q4(blk, t, i) + 16 * (ks & 1)
-                                              : k_word_dim(blk, j, i))];
-            xh[i] = __float2half_rn(x);
-            xl[i] = __float2half_rn(x - __half2float(xh[i]));
-        }
-        qb[ks][0] = pack_half2(xh[0], xh[1]);
-        qb[ks][1] = pack_half2(xh[2], xh[3]);
-        qb[ks][2] = pack_half2(xl[0], xl[1]);
-        qb[ks][3] = pack_half2(xl[2], xl[3]);
-    }
-    // Per (head, block) sums of the query as the tensor cores see it (high + low part), times
-    // -2^-17: the starting value of the score accumulators. 64 threads sum one pair each.
-    if (tid < 64) {
-        const int h = tid >> 3, blk = tid & 7;
-        float sum = 0.0f;
-        for (int d = 0; d < 32; d++) {
-            const float x = qs[h * 256 + blk * 32 + d];
-            const float xh = __half2float(__float2half_rn(x));
-            sum += xh + __half2float(__float2half_rn(x - xh));
-        }
-        qsum_s[tid] = -(kQ4 ? kCodeBias / 16.0f : kCodeBias) * sum;   // nibbles carry an offset of 8
-    }
-    __syncthreads();
     float qbias[4][2];
 #pragma unroll
     for (int b = 0; b < 4; b++) {
-        qbias[b][0] = qsum_s[(2 * t) * 8 + dh * 4 + b];
-        qbias[b][1] = qsum_s[(2 * t + 1) * 8 + dh * 4 + b];
+        float sum = 0.0f;   // of the block's query values as the tensor cores see them
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int ks = 2 * b + half;
+            __half xh[4], xl[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float x = qv[ks][i] * p.scale_log2;
+                xh[i] = __float2half_rn(x);
+                xl[i] = __float2half_rn(x - __half2float(xh[i]));
+                sum += __half2float(xh[i]) + __half2float(xl[i]);
+            }
+            qb[ks][0] = pack_half2(xh[0], xh[1]);
+            qb[ks][1] = pack_half2(xh[2], xh[3]);
+            qb[ks][2] = pack_half2(xl[0], xl[1]);
+            qb[ks][3] = pack_half2(xl[2], xl[3]);
+        }
+        // the four lanes of a head hold a quarter of the block each; the score accumulators of
+        // lane (g, t) are heads 2t and 2t + 1 and start at -2^-17 * (sum over the block), which
+        // takes the codes' offset of 128 out again (nibbles carry an offset of 8)
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const float bias = -(kQ4 ? kCodeBias / 16.0f : kCodeBias) * sum;
+        qbias[b][0] = __shfl_sync(0xffffffffu, bias, (2 * t) * 4);
+        qbias[b][1] = __shfl_sync(0xffffffffu, bias, (2 * t + 1) * 4);
     }
-    // qs aliases stage 2: every warp is done with it (and its generic-proxy writes are ordered
-    // before the bulk copy's) before tile 2 is fetched
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // (set-up wrote the barriers; the first tiles are on their way)
     __syncthreads();
 
     float acc[4][4];  // block `warp`: [byte i of the code word][c0..c3]

@@ -21,14 +21,29 @@ struct FoldAcc {
 };
 
 // Partials of one head at slots first, first + step, ..., `count` of them (<= 32). pa / ml
-// point at the head's slot 0. Reads go to L2 (the partials were written by other SMs).
+// point at the head's slot 0. Reads go to L2 (the partials were written by other SMs). The
+// loads of a batch of eight partial rows are issued together with the (max, sum) pairs, so a
+// group of eight costs one round trip to L2.
 __device__ __forceinline__ FoldAcc fold_warp(const float *pa, const float *ml, int first, int step,
                                              int count, int lane) {
+    constexpr int kBatch = 8;
+    float4 x[kBatch][2];
+#pragma unroll
+    for (int j = 0; j < kBatch; j++) {
+        if (j < count) {
+            const float4 *src =
+                reinterpret_cast<const float4 *>(pa + (size_t)(first + j * step) * 256 + lane * 8);
+            x[j][0] = __ldcg(src);
+            x[j][1] = __ldcg(src + 1);
+        } else {
+            x[j][0] = x[j][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    }
     float m = -INFINITY, l = 0.0f;
     if (lane < count) {
-        const float *src = ml + 2 * (size_t)(first + lane * step);
-        m = __ldcg(src);
-        l = __ldcg(src + 1);
+        const float2 v = __ldcg(reinterpret_cast<const float2 *>(ml + 2 * (size_t)(first + lane * step)));
+        m = v.x;
+        l = v.y;
     }
     FoldAcc r;
     r.big = warp_max(m);
@@ -37,21 +52,22 @@ __device__ __forceinline__ FoldAcc fold_warp(const float *pa, const float *ml, i
     r.den = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) r.a[i] = 0.0f;
-    for (int s0 = 0; s0 < count; s0 += 4) {
-        float4 x[4][2];
+    for (int s0 = 0; s0 < count; s0 += kBatch) {
+        if (s0 > 0) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            if (s0 + j < count) {
-                const float4 *src = reinterpret_cast<const float4 *>(
-                    pa + (size_t)(first + (s0 + j) * step) * 256 + lane * 8);
-                x[j][0] = __ldcg(src);
-                x[j][1] = __ldcg(src + 1);
-            } else {
-                x[j][0] = x[j][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int j = 0; j < kBatch; j++) {
+                if (s0 + j < count) {
+                    const float4 *src = reinterpret_cast<const float4 *>(
+                        pa + (size_t)(first + (s0 + j) * step) * 256 + lane * 8);
+                    x[j][0] = __ldcg(src);
+                    x[j][1] = __ldcg(src + 1);
+                } else {
+                    x[j][0] = x[j][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
             }
         }
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < kBatch; j++) {
             // (lanes past `count` hold weight 0)
             const float ws = __shfl_sync(0xffffffffu, w, (s0 + j) & 31);
             r.den = __fadd_rn(r.den, __shfl_sync(0xffffffffu, lw, (s0 + j) & 31));
@@ -66,6 +82,15 @@ __device__ __forceinline__ FoldAcc fold_warp(const float *pa, const float *ml, i
         }
     }
     return r;
+}
+
+// Arrival at a counter with release (this CTA's writes, made visible to the arriving thread by
+// the preceding CTA barrier, come first) and acquire (the other arrivals' writes are visible
+// afterwards) in one round trip. Returns the count before the arrival.
+__device__ __forceinline__ int arrive_acq_rel(int *counter) {
+    int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
+    return prev;
 }
 
 // Writes a folded group back as a partial (slot `at` of the head).

@@ -190,6 +190,8 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     p.kv_slot_bytes = p.acc_slot = p.ml_slot = p.q_slot = 0;
     if (tensor_core && ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v)) & 15) != 0)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "the KV cache must be 16-byte aligned");
+    if (tensor_core && (reinterpret_cast<size_t>(q) & 7) != 0)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "the query row must be 8-byte aligned");
     if (k_row) {
         // the caller checked that this combination has the fused form
         p.k_row = k_row;
@@ -444,7 +446,8 @@ static int decode_rows(hipml_stream_t stream, int dtype, const int *pos, const f
     const bool aligned =
         ((reinterpret_cast<size_t>(p.k) | reinterpret_cast<size_t>(p.v) | (size_t)kv_slot_bytes) &
          15) == 0;
-    const bool tensor_core = head_dim == 256 && aligned;
+    const bool tensor_core = head_dim == 256 && aligned && (reinterpret_cast<size_t>(q) & 7) == 0 &&
+                             (q_slot & 1) == 0;
     if (k_rows) {
         // fused append (the caller checked that this combination has it)
         if (!tensor_core)
