@@ -738,24 +738,6 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
-                cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
 // 2D f16 tensor [rows][cols] (cols contiguous), box `box_rows` rows x 64 cols, 128-byte swizzle.
 int make_map(CUtensorMap *map, void *base, uint64_t cols, uint64_t rows, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();

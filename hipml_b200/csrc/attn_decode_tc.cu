@@ -807,6 +807,566 @@ __global__ void __launch_bounds__(kThreads, 2) attn_decode_kv_tc(DecodeParams p,
     fold_tail(p, status, slot, kvh, split, runs, group, tid);
 }
 
+// ------------------------------------------------------------------------------------------
+// The q8_0 body with the value side on the 5th-generation tensor cores (tcgen05.mma kind::i8,
+// accumulators in TMEM). Scores, tiles, run plan, fused append and fold are those of
+// attn_decode_kv_tc; what changes is phase (3):
+//   * the V tile is brought in by 17 tensor (TMA) copies of {16 bytes, 64 rows}, one per
+//     16-byte column chunk of the 272-byte rows, so it lands as [chunk][key][16 B]: exactly the
+//     canonical MN-major operand of the MMA (8 keys x 16 bytes contiguous per core matrix).
+//     The int8 codes are the A operand as they are: M = byte of the row (three M tiles of 128
+//     cover the 272 bytes; the two scale bytes of each block are rows whose results are never
+//     read), K = key. No conversion of a single code on the CUDA cores;
+//   * the B operand is built per tile: column (block b, head h, digit) holds the weight
+//     exp2(score - ref_h) * scale(key, b) as a 23-bit fixed-point number in three unsigned
+//     bytes, taken straight out of the mantissa of weight * F + 2^23. A block's results only
+//     need that block's columns, so an M tile multiplies a window of 32 .. 96 columns;
+//   * products accumulate as int32 in TMEM (exact); per head the reference `ref_h` of the
+//     exponentials and the unit of the value scales stay fixed while the running maximum stays
+//     within 2^5.5 of it, so the accumulators are read out only when a reference moves (a few
+//     times per run) and at the end: digits are combined and scaled in f32 there.
+// Weights carry 17 bits below the reference (error 2^-18 of the largest weight), the int32
+// sums are exact, scores are as before: results agree with the f32 definition to ~1e-6.
+namespace i8 {
+
+constexpr float kMagicLimit = 8388608.0f;
+constexpr int kKStages = 2;                    // the K tile is free once its scores are out
+constexpr int kVStages = 3;                    // the V tile until its MMAs have run
+constexpr int kDigits = 3;
+constexpr int kCols = 6 * kDigits;               // columns per block: 6 heads x 3 digits
+constexpr int kBRows = 162;                      // 8 * 18 weight rows + what the last windows read past them;
+                                                 // 162 * 16 B keeps the four key chunks on different banks
+constexpr int kBChunk = kBRows * 16;             // bytes between 16-key chunks of the B operand
+constexpr int kOffV = kKStages * kTileBytes;                // K ring first
+constexpr int kOffB = kOffV + kVStages * kTileBytes;
+constexpr int kOffSs = kOffB + 4 * kBChunk;                 // scores [2][8][kSsStride] f32
+constexpr int kOffPw = kOffSs + 2 * 8 * kSsStride * 4;      // weights' exponentials [6][64] f32
+constexpr int kOffDv = kOffPw + 6 * 64 * 4;                 // value scales [8][64] f32
+constexpr int kOffMisc = kOffDv + 8 * 64 * 4;               // fscale[8] f32, dvmax bits, flush flag
+constexpr int kOffRow = kOffMisc + 64;                      // one row image (fused append)
+constexpr int kOffBar = kOffRow + 288;                      // K full [2], V full [3], MMA done
+constexpr int kSmem = kOffBar + 64;
+static_assert(2 * (kSmem + 1024) <= 227 * 1024, "two CTAs per SM");
+// the M tile that starts at chunk 16 reads 8 chunks: 7 KB past the V stage, still inside the window
+static_assert(kOffV + kVStages * kTileBytes + 7 * 1024 <= kSmem, "M tile 2 reads past the stage");
+constexpr unsigned kTmemCols = 256;
+// M tile mt covers row bytes [128 mt, 128 mt + 128) = blocks {0..3}, {3..7}, {7}: window of B rows
+// [n0, n0 + N) and TMEM columns [tcol, tcol + N)
+__device__ __forceinline__ int win_n0(int mt) { return mt == 0 ? 0 : (mt == 1 ? 48 : 120); }
+__device__ __forceinline__ int win_n(int mt) { return mt == 0 ? 80 : (mt == 1 ? 96 : 32); }
+__device__ __forceinline__ int win_tcol(int mt) { return mt == 0 ? 0 : (mt == 1 ? 80 : 176); }
+constexpr float kHeadroom = 3.0f;                // log2 units: exponentials stay below 2^3 of the reference
+constexpr float kDvSlack = 1.25f;                // the unit of the value scales: this much above the largest seen
+constexpr float kFixedOne = 524288.0f;           // 2^19: fixed-point value of weight 1 at the unit scale
+static_assert(8.0f * kFixedOne < kMagicLimit, "the largest weight (2^3 at the unit scale) must stay below 2^23");
+constexpr float kMagic = 8388608.0f;             // 2^23: weight * F + 2^23 has the integer in its mantissa
+
+__device__ __forceinline__ uint64_t desc_nosw(unsigned addr, unsigned lbo, unsigned sbo) {
+    return (uint64_t)((addr & 0x3ffff) >> 4) | ((uint64_t)((lbo >> 4) & 0x3fff) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3fff) << 32) | ((uint64_t)1 << 46);
+}
+// s32 accumulate, A = s8 MN-major, B = u8 K-major, M = 128
+__device__ __forceinline__ unsigned idesc_i8(unsigned n) {
+    return (2u << 4) | (1u << 7) | (0u << 10) | (1u << 15) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void mma_i8(unsigned d, uint64_t a, uint64_t b, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(unsigned taddr, unsigned (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Adds what the accumulators of this thread's row byte hold to acc (f32), in `unit`s. The warp's
+// 32 row bytes lie in at most two blocks, whose 36 columns are read with one address.
+__device__ __forceinline__ void readout(unsigned tmem, int mt, int lane_base, int lane, float unit,
+                                        float (&acc)[6]) {
+    const int byte0 = 128 * mt + lane_base;
+    const int blk_lo = byte0 / 34;
+    const bool second = (byte0 + lane) / 34 != blk_lo;
+    const unsigned taddr = tmem + ((unsigned)lane_base << 16) + win_tcol(mt) + kCols * blk_lo - win_n0(mt);
+    unsigned r[32], r2[4];
+    tmem_ld32(taddr, r);
+    tmem_ld4(taddr + 32, r2);
+#pragma unroll
+    for (int h = 0; h < 6; h++) {
+        int d[3];
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+            const int lo = (int)r[3 * h + j];
+            const int idx = kCols + 3 * h + j;   // the same column of the warp's second block
+            const int hi = idx < 32 ? (int)r[idx] : (int)r2[idx - 32];
+            d[j] = second ? hi : lo;
+        }
+        const float v = fmaf((float)d[2], 65536.0f, fmaf((float)d[1], 256.0f, (float)d[0]));
+        acc[h] = fmaf(v, unit, acc[h]);
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap *map, int x, int y, int z,
+                                            unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+// vmap: the V cache as rows of 272 bytes. v3d != 0: a 3-D view {16 bytes, rows, 17 chunks} whose
+// box {16, 64, 17} lands a whole tile in chunk order with one copy; else a 2-D view {272, rows}
+// with box {16, 64}, one copy per chunk.
+__global__ void __launch_bounds__(kThreads, 2)
+attn_decode_kv_i8(const __grid_constant__ CUtensorMap vmap, int v3d, DecodeParams p, int *status) {
+    extern __shared__ __align__(128) unsigned char smem_i8[];
+    unsigned char *const smem = smem_i8;
+    griddep_launch();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = p.n_heads / p.n_kv;
+    const int kg = warp & 3, dh = warp >> 2;
+    unsigned *tmem_slot = reinterpret_cast<unsigned *>(smem + kOffBar + 56);
+    if (warp == 0) {
+        // (nothing of memory is touched; a CTA of the grid before may still hold its columns)
+        tmem_alloc<1>(smem_u32(tmem_slot), kTmemCols);
+    }
+    // Everything this kernel reads may come from the grids before it: nothing is read before this.
+    griddep_wait();
+    auto ktile_at = [&](int stage) { return smem + stage * kTileBytes; };   // kKStages of them
+    auto vtile_at = [&](int stage) { return smem + kOffV + stage * kTileBytes; };
+    unsigned char *bop = smem + kOffB;
+    float *ss = reinterpret_cast<float *>(smem + kOffSs);
+    float *pw = reinterpret_cast<float *>(smem + kOffPw);            // [6][64]
+    float *sdv = reinterpret_cast<float *>(smem + kOffDv);           // [8][64]
+    float *s_fscale = reinterpret_cast<float *>(smem + kOffMisc);    // [8]
+    // per tile parity: the tile's largest value scale (f32 bits) and "a reference moved"
+    unsigned *s_dvmax = reinterpret_cast<unsigned *>(smem + kOffMisc + 32);   // [2]
+    int *s_flush = reinterpret_cast<int *>(smem + kOffMisc + 40);             // [2]
+    unsigned char *rowbuf = smem + kOffRow;
+
+    __shared__ int s_plan[4];   // slot (-1: none), kvh, split, quota
+    const int grid_splits = (p.by_stride || p.run_cap <= 0) ? p.splits : min(p.splits, p.run_cap);
+    int slot = blockIdx.y, kvh = blockIdx.x / grid_splits, split = blockIdx.x - kvh * grid_splits;
+    if (p.share_slots > 0) {
+        if (warp == 1) {
+            const int quota = shared_quota_warp(p.len, p.len_stride, p.len_offset, p.n_slots, p.splits,
+                                                p.share_slots, p.n_kv);
+            const int b = blockIdx.x;
+            int base = 0;
+            if (lane == 0) {
+                s_plan[0] = -1;
+                s_plan[3] = quota;
+            }
+            __syncwarp();
+            for (int s0 = 0; s0 < p.n_slots; s0 += 32) {
+                const int s = s0 + lane;
+                const int per = s < p.n_slots
+                    ? shared_runs_of((p.len[s * p.len_stride + p.len_offset] + 63) >> 6, quota) : 0;
+                const int runs = per * p.n_kv;
+                int incl = runs;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                const int first = base + incl - runs;
+                if (runs > 0 && b >= first && b < first + runs) {
+                    const int r = b - first;
+                    s_plan[0] = s;
+                    s_plan[1] = r / per;
+                    s_plan[2] = r - (r / per) * per;
+                }
+                base += __shfl_sync(0xffffffffu, incl, 31);
+            }
+        }
+        __syncthreads();
+        slot = s_plan[0];
+        kvh = s_plan[1];
+        split = s_plan[2];
+    }
+    const bool idle = slot < 0;   // (the shared grid is one round of CTAs; the tail of it may be spare)
+
+    // query values of this lane (see attn_decode_kv_tc), before anything that depends on the length
+    float qv[8][4];
+    if (!idle) {
+        const float *qh = p.q + (size_t)slot * p.q_slot + (size_t)(kvh * group + g) * 256;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+            const int blk = dh * 4 + (ks >> 1), j = (ks & 1) * 4 + t;
+#pragma unroll
+            for (int i = 0; i < 4; i += 2) {
+                float2 x = make_float2(0.0f, 0.0f);
+                if (g < group) x = *reinterpret_cast<const float2 *>(qh + k_word_dim(blk, j, i));
+                qv[ks][i] = x.x;
+                qv[ks][i + 1] = x.y;
+            }
+        }
+    }
+    int lo = 0, hi = 0;
+    if (!idle) split_range(p, slot, split, p.share_slots > 0 ? s_plan[3] : 0, lo, hi);
+    const int ntiles = (hi - lo + kTile - 1) / kTile;
+    if (!idle && ntiles == 0) {
+        // A split without rows: neutral partials (zero sum, -inf maximum), nothing else.
+        for (int i = tid; i < group * 256; i += kThreads) {
+            const int h = kvh * group + (i >> 8);
+            p.part_acc[(size_t)slot * p.acc_slot + ((size_t)h * p.splits + split) * 256 + (i & 255)] = 0.0f;
+        }
+        if (tid < group) {
+            float *pm = p.part_ml + (size_t)slot * p.ml_slot +
+                        ((size_t)(kvh * group + tid) * p.splits + split) * 2;
+            pm[0] = -INFINITY;
+            pm[1] = 0.0f;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = *tmem_slot;
+
+    if (ntiles > 0) {
+    const size_t head_byte = (size_t)slot * p.kv_slot_bytes + (size_t)kvh * p.stride * kRowBytes;
+    const unsigned char *kbase = p.k + head_byte;
+    // first row of this KV head in the V tensor of 272-byte rows
+    const int vrow0 = (int)(((size_t)slot * p.kv_slot_bytes) / kRowBytes) + kvh * p.stride;
+    int append_pos = -1;
+    if (p.k_row != nullptr) {
+        append_pos = p.len[slot * p.len_stride + p.len_offset - 1];
+        if (split == 0 && kvh == 0 && tid == 0 &&
+            append_pos != p.len[slot * p.len_stride + p.len_offset] - 1 && status)
+            atomicCAS(status, 0, 22);
+    }
+    const unsigned bar_k = smem_u32(smem + kOffBar), bar_v = bar_k + 16, bar_mma = bar_k + 40;
+    auto fetch_k = [&](int tile) {
+        const int stage = tile % kKStages;
+        const int r0 = lo + tile * kTile;
+        const unsigned bytes = (unsigned)(min(kTile, hi - r0) * kRowBytes);
+        fence_async_shared();
+        mbar_arrive_expect_tx(bar_k + 8 * stage, bytes);
+        bulk_load(smem_u32(ktile_at(stage)), kbase + (size_t)r0 * kRowBytes, bytes, bar_k + 8 * stage);
+    };
+    // 17 copies of {16 bytes, 64 rows}; rows past the run are other rows of the cache (or zeros
+    // past its end): their weights are zero
+    // (called by all lanes of one warp)
+    auto fetch_v = [&](int tile) {
+        const int stage = tile % kVStages;
+        const unsigned dst = smem_u32(vtile_at(stage));
+        fence_async_shared();
+        if (lane == 0) mbar_arrive_expect_tx(bar_v + 8 * stage, (unsigned)kTileBytes);
+        __syncwarp();
+        if (v3d) {
+            if (lane == 0) tma_load_3d(dst, &vmap, 0, vrow0 + lo + tile * kTile, 0, bar_v + 8 * stage);
+        } else if (lane < 17) {
+            tma_load_2d<1>(dst + lane * 1024, &vmap, 16 * lane, vrow0 + lo + tile * kTile, bar_v + 8 * stage);
+        }
+    };
+    // warp 7 is the producer of both rings: two tiles are always on their way
+    if (warp == 7) {
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < 6; s++) mbar_init(bar_k + 8 * s, 1);
+            mbar_init_fence();
+            s_dvmax[0] = s_dvmax[1] = 0u;
+            s_flush[0] = s_flush[1] = 0;
+            fetch_k(0);
+            if (ntiles > 1) fetch_k(1);
+        }
+        __syncwarp();
+        fetch_v(0);
+        if (ntiles > 1) fetch_v(1);
+    }
+
+    unsigned qb[8][4];
+    float qbias[4][2];
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int ks = 2 * b + half;
+            __half xh[4], xl[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float x = qv[ks][i] * p.scale_log2;
+                xh[i] = __float2half_rn(x);
+                xl[i] = __float2half_rn(x - __half2float(xh[i]));
+                sum += __half2float(xh[i]) + __half2float(xl[i]);
+            }
+            qb[ks][0] = pack_half2(xh[0], xh[1]);
+            qb[ks][1] = pack_half2(xh[2], xh[3]);
+            qb[ks][2] = pack_half2(xl[0], xl[1]);
+            qb[ks][3] = pack_half2(xl[2], xl[3]);
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const float bias = -kCodeBias * sum;
+        qbias[b][0] = __shfl_sync(0xffffffffu, bias, (2 * t) * 4);
+        qbias[b][1] = __shfl_sync(0xffffffffu, bias, (2 * t + 1) * 4);
+    }
+    __syncthreads();
+
+    // f32 accumulators of this thread's row byte, in units of 2^ref_h: warps 0..3 own bytes
+    // 0..127 (M tile 0), warps 4..7 bytes 128..255 (M tile 1); warp 0 also bytes 256..271
+    float acc[6] = {0, 0, 0, 0, 0, 0}, acc2[6] = {0, 0, 0, 0, 0, 0};
+    const int mt = warp >> 2, lane_base = (warp & 3) * 32;
+    float m_ref = -INFINITY, l_ref = 0.0f;   // meaningful in warp h = head of the group
+    float dvref = 0.0f;                      // unit of the value scales (the same in every thread)
+    bool fresh = true;                       // the accumulators in TMEM hold nothing yet
+    bool mma_fresh = true;                   // ... as the MMAs of the tile before will find them
+    // O += codes^T x weights of `tile`: three M tiles, two steps of 32 keys each (one thread)
+    auto issue_mma = [&](int tile, bool overwrite) {
+        tc_fence_after();
+        const unsigned va = smem_u32(vtile_at(tile % kVStages)), ba = smem_u32(bop);
+#pragma unroll
+        for (int m = 0; m < 3; m++) {
+            const unsigned idesc = idesc_i8((unsigned)win_n(m));
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++)
+                mma_i8(tmem + win_tcol(m), desc_nosw(va + m * 8 * 1024 + ks * 512, 128, 1024),
+                       desc_nosw(ba + win_n0(m) * 16 + ks * 2 * kBChunk, kBChunk, 128), idesc,
+                       (ks != 0 || !overwrite) ? 1u : 0u);
+        }
+        tc_commit<1>(bar_mma);
+    };
+    bool landed = true;
+    auto wait_bar = [&](unsigned bar, unsigned parity) {
+        unsigned spin = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if (++spin > kSpinLimit) {
+                landed = false;
+                break;
+            }
+        }
+    };
+
+    for (int tile = 0; tile < ntiles; tile++) {
+        const int kbuf = tile % kKStages, vbuf = tile % kVStages;
+        wait_bar(bar_k + 8 * kbuf, (unsigned)(tile / kKStages) & 1u);
+        const int nvalid = min(kTile, hi - (lo + tile * kTile));
+        unsigned char *const ktile_b = ktile_at(kbuf), *const vtile_b = vtile_at(vbuf);
+        if (p.k_row != nullptr) {
+            const int prow = append_pos - (lo + tile * kTile);
+            if (prow >= 0 && prow < nvalid) {
+                if (warp == 0) {
+                    const float *src = p.k_row + (size_t)slot * p.row_slot + (size_t)kvh * 256 + lane * 8;
+                    unsigned char *row = ktile_b + prow * kRowBytes;
+                    q8_put8(__ldg(reinterpret_cast<const float4 *>(src)),
+                            __ldg(reinterpret_cast<const float4 *>(src) + 1), lane, row);
+                    __syncwarp();
+                    row_store(p.kw + head_byte + (size_t)append_pos * kRowBytes, row, kRowBytes, lane, 32);
+                } else if (warp == 1) {
+                    // the V row: built as a row image, copied into the tile's chunk order and stored
+                    wait_bar(bar_v + 8 * vbuf, (unsigned)(tile / kVStages) & 1u);
+                    const float *src = p.v_row + (size_t)slot * p.row_slot + (size_t)kvh * 256 + lane * 8;
+                    q8_put8(__ldg(reinterpret_cast<const float4 *>(src)),
+                            __ldg(reinterpret_cast<const float4 *>(src) + 1), lane, rowbuf);
+                    __syncwarp();
+                    if (lane < 17)
+                        *reinterpret_cast<uint4 *>(vtile_b + lane * 1024 + prow * 16) =
+                            *reinterpret_cast<const uint4 *>(rowbuf + lane * 16);
+                    row_store(p.vw + head_byte + (size_t)append_pos * kRowBytes, rowbuf, kRowBytes, lane, 32);
+                }
+                __syncthreads();
+            }
+        }
+
+        // ---- (1) scores
+        {
+            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (dh == 0) {
+                score_block<0>(ktile_b, kg * 16, g, t, qb[0], qb[1], qbias[0], s);
+                score_block<1>(ktile_b, kg * 16, g, t, qb[2], qb[3], qbias[1], s);
+                score_block<2>(ktile_b, kg * 16, g, t, qb[4], qb[5], qbias[2], s);
+                score_block<3>(ktile_b, kg * 16, g, t, qb[6], qb[7], qbias[3], s);
+            } else {
+                score_block<4>(ktile_b, kg * 16, g, t, qb[0], qb[1], qbias[0], s);
+                score_block<5>(ktile_b, kg * 16, g, t, qb[2], qb[3], qbias[1], s);
+                score_block<6>(ktile_b, kg * 16, g, t, qb[4], qb[5], qbias[2], s);
+                score_block<7>(ktile_b, kg * 16, g, t, qb[6], qb[7], qbias[3], s);
+            }
+            float *dst = ss + (dh * 8 + 2 * t) * kSsStride + kg * 16 + g;
+            dst[0] = s[0];
+            dst[kSsStride] = s[1];
+            dst[8] = s[2];
+            dst[kSsStride + 8] = s[3];
+        }
+        __syncthreads();
+        // the K stage is free again: tile + 2 goes there
+        if (tid == 6 * 32 && tile + 2 < ntiles) fetch_k(tile + 2);
+        // The weights of the tile before are complete in every warp (and their V tile landed: this
+        // thread waited for it then): their MMAs run beside this tile's exponentials.
+        if (tid == 7 * 32 && tile >= 1) issue_mma(tile - 1, mma_fresh);
+
+        // ---- (2) exponentials (warp = head, lane = keys 2*lane, 2*lane + 1), and beside them the
+        // value scales of the tile as f32 with their maximum (warps 6, 7: one key per lane)
+        if (warp < group) {
+            const float2 a = *reinterpret_cast<const float2 *>(ss + warp * kSsStride + 2 * lane);
+            const float2 b = *reinterpret_cast<const float2 *>(ss + (8 + warp) * kSsStride + 2 * lane);
+            const float s0 = 2 * lane < nvalid ? (a.x + b.x) * kCodeUnit : -INFINITY;
+            const float s1 = 2 * lane + 1 < nvalid ? (a.y + b.y) * kCodeUnit : -INFINITY;
+            const float tmax = warp_max(fmaxf(s0, s1));
+            // the reference of this head's exponentials moves only when the tile's maximum leaves
+            // the headroom above it (or at the first tile): the accumulators then restart
+            const bool move = m_ref == -INFINITY || tmax > m_ref + kHeadroom;
+            const float ref = move ? tmax : m_ref;
+            const float fs = (m_ref == -INFINITY || !move) ? 1.0f : exp2f(m_ref - ref);
+            l_ref *= fs;
+            m_ref = ref;
+            const float p0 = (s0 == -INFINITY) ? 0.0f : exp2f(s0 - m_ref);
+            const float p1 = (s1 == -INFINITY) ? 0.0f : exp2f(s1 - m_ref);
+            l_ref += warp_sum(p0 + p1);
+            *reinterpret_cast<float2 *>(pw + warp * 64 + 2 * lane) = make_float2(p0, p1);
+            if (lane == 0) {
+                s_fscale[warp] = fs;
+                if (move) s_flush[tile & 1] = 1;
+            }
+        } else if (warp >= 6) {
+            wait_bar(bar_v + 8 * vbuf, (unsigned)(tile / kVStages) & 1u);
+            const int k = (warp - 6) * 32 + lane;
+            float mx = 0.0f;
+#pragma unroll
+            for (int b = 0; b < 8; b++) {
+                const int at = b * kQ8BlockBytes;   // byte of the row where block b's scale sits
+                const unsigned short bits =
+                    *reinterpret_cast<const unsigned short *>(vtile_b + (at >> 4) * 1024 + k * 16 + (at & 15));
+                float d = 0.0f;
+                if (k < nvalid) {
+                    // q8_0 scales are amax / 127 >= 0; anything else (negative, inf, NaN) is not a
+                    // cache this body can weigh: flagged, read as zero
+                    if (bits >= 0x7c00u) {
+                        if (status) atomicCAS(status, 0, 23);
+                    } else {
+                        d = half_bits_to_float(bits);
+                    }
+                }
+                sdv[b * 64 + k] = d;
+                mx = fmaxf(mx, d);
+            }
+            mx = warp_max(mx);
+            if (lane == 0) atomicMax(s_dvmax + (tile & 1), __float_as_uint(mx));
+        }
+        __syncthreads();
+
+        // ---- (3) a reference moved: the accumulators leave TMEM (old units), then restart
+        const float dvmax = __uint_as_float(s_dvmax[tile & 1]);
+        const bool flush = s_flush[tile & 1] != 0 || dvmax > dvref;
+        if (tid == 0) {
+            // (the other parity was read by every thread a tile ago and is written a tile from now)
+            s_dvmax[(tile + 1) & 1] = 0u;
+            s_flush[(tile + 1) & 1] = 0;
+        }
+        // the MMAs of the tile before are done: their B operand may be rewritten, TMEM read
+        if (tile >= 1) wait_bar(bar_mma, (unsigned)(tile - 1) & 1u);
+        tc_fence_after();
+        // ... and the V stage they read takes tile + 2
+        if (warp == 7 && tile + 2 < ntiles) fetch_v(tile + 2);
+        if (flush) {
+            if (!fresh) {
+                const float unit = dvref / kFixedOne;
+                readout(tmem, mt, lane_base, lane, unit, acc);
+                if (warp == 0) readout(tmem, 2, 0, lane, unit, acc2);
+            }
+#pragma unroll
+            for (int h = 0; h < 6; h++) {
+                const float fs = h < group ? s_fscale[h] : 1.0f;
+                acc[h] *= fs;
+                acc2[h] *= fs;
+            }
+            if (dvmax > dvref) dvref = kDvSlack * dvmax;
+            fresh = true;
+            tc_fence_before();
+        }
+
+        // ---- (4) weights: warp = block, lane = (three heads, four keys)
+        {
+            const int kq = lane & 15, hh = lane >> 4;
+            const float f = dvref > 0.0f ? kFixedOne / dvref : 0.0f;
+            const float4 dv = *reinterpret_cast<const float4 *>(sdv + warp * 64 + 4 * kq);
+            const float d0 = dv.x * f, d1 = dv.y * f, d2 = dv.z * f, d3 = dv.w * f;
+            unsigned char *dst = bop + (kq >> 2) * kBChunk + (kq & 3) * 4;
+#pragma unroll
+            for (int j = 0; j < 3; j++) {
+                const int h = 3 * hh + j;
+                const float4 pe = *reinterpret_cast<const float4 *>(pw + h * 64 + 4 * kq);
+                const unsigned w0 = __float_as_uint(fmaf(pe.x, d0, kMagic));
+                const unsigned w1 = __float_as_uint(fmaf(pe.y, d1, kMagic));
+                const unsigned w2 = __float_as_uint(fmaf(pe.z, d2, kMagic));
+                const unsigned w3 = __float_as_uint(fmaf(pe.w, d3, kMagic));
+                // digit j of the four keys = byte j of the four mantissas
+                const unsigned lo01 = __byte_perm(w0, w1, 0x5140);   // [w0.b0 w1.b0 w0.b1 w1.b1]
+                const unsigned lo23 = __byte_perm(w2, w3, 0x5140);
+                const unsigned hi01 = __byte_perm(w0, w1, 0x0062);   // [w0.b2 w1.b2 . .]
+                const unsigned hi23 = __byte_perm(w2, w3, 0x0062);
+                const int n = kCols * warp + kDigits * h;
+                *reinterpret_cast<unsigned *>(dst + (n + 0) * 16) = __byte_perm(lo01, lo23, 0x5410);
+                *reinterpret_cast<unsigned *>(dst + (n + 1) * 16) = __byte_perm(lo01, lo23, 0x7632);
+                *reinterpret_cast<unsigned *>(dst + (n + 2) * 16) = __byte_perm(hi01, hi23, 0x5410);
+            }
+        }
+        // (the MMAs of this tile are issued after the next barrier, beside the next tile's phase 2)
+        fence_async_shared();
+        tc_fence_before();
+        mma_fresh = fresh;
+        fresh = false;
+    }
+
+    // ---- the end of the run: the last tile's MMAs, the last accumulators, then the partials
+    __syncthreads();
+    if (tid == 7 * 32) issue_mma(ntiles - 1, mma_fresh);
+    wait_bar(bar_mma, (unsigned)(ntiles - 1) & 1u);
+    tc_fence_after();
+    {
+        const float unit = dvref / kFixedOne;
+        readout(tmem, mt, lane_base, lane, unit, acc);
+        if (warp == 0) readout(tmem, 2, 0, lane, unit, acc2);
+    }
+    if (!landed && status) atomicCAS(status, 0, 21);
+    {
+        // row byte -> head dim: byte 34 b + 2 + i is dim 32 b + i; the two scale bytes hold nothing
+        const int byte = 128 * mt + lane_base + lane, blk = byte / 34, i = byte - 34 * blk - 2;
+        if (i >= 0) {
+#pragma unroll
+            for (int h = 0; h < 6; h++)
+                if (h < group)
+                    p.part_acc[(size_t)slot * p.acc_slot + ((size_t)(kvh * group + h) * p.splits + split) * 256 +
+                               32 * blk + i] = acc[h];
+        }
+        if (warp == 0 && lane < 16) {
+            // bytes 256..271 are codes 16..31 of block 7
+#pragma unroll
+            for (int h = 0; h < 6; h++)
+                if (h < group)
+                    p.part_acc[(size_t)slot * p.acc_slot + ((size_t)(kvh * group + h) * p.splits + split) * 256 +
+                               240 + lane] = acc2[h];
+        }
+    }
+    if (warp < group && lane == 0) {
+        float *pm = p.part_ml + (size_t)slot * p.ml_slot + ((size_t)(kvh * group + warp) * p.splits + split) * 2;
+        pm[0] = m_ref;
+        pm[1] = l_ref;
+    }
+    }   // ntiles > 0
+
+    // every access to TMEM is over in every warp before its columns go back
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc<1>(tmem, kTmemCols);
+    }
+    if (idle || p.out == nullptr) return;
+    const int runs = live_runs(p, slot, p.share_slots > 0 ? s_plan[3] : 0);
+    if (split >= runs) return;
+    fold_tail(p, status, slot, kvh, split, runs, group, tid);
+}
+
+}  // namespace i8
+
 // Stand-alone launch of the same fold: grid (n_kv, slots), 8 warps = the heads of the group.
 __global__ void __launch_bounds__(kThreads) attn_decode_fold_tree(DecodeParams p, int *status) {
     griddep_launch();
@@ -873,6 +1433,22 @@ int *decode_tc_setup(int *rc) {
 }
 
 std::atomic<int> g_two_launch_fold{0};
+
+int i8_setup() {
+    static std::mutex mu;
+    static bool done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(i8::attn_decode_kv_i8,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, i8::kSmem);
+        if (e != cudaSuccess) return (int)e;
+        done[dev] = true;
+    }
+    return 0;
+}
 
 }  // namespace
 
@@ -941,6 +1517,43 @@ int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
         grid = dim3(q.share_slots, 1);
     else if (!q.by_stride && q.run_cap > 0 && q.run_cap < q.splits)
         grid = dim3(q.n_kv * q.run_cap, slots);
+    // The body with the value side on tcgen05 (int8 operands): q8_0, a GQA group of at most 6,
+    // slots a whole number of 272-byte rows apart.
+    const bool i8_body = !q.q4 && !q.legacy_body && q.n_heads / q.n_kv <= 6 && q.kv_slot_bytes % kRowBytes == 0;
+    CUtensorMap vmap;
+    int v3d = 0;
+    if (i8_body) {
+        if (int e = i8_setup()) return e;
+        EncodeTiledFn fn = encode_tiled_fn();
+        if (!fn) return fail(HIPML_ERR_INVALID_ARGUMENT, "cuTensorMapEncodeTiled is not available");
+        const cuuint64_t rows = (cuuint64_t)(slots > 1 ? (slots - 1) * (q.kv_slot_bytes / kRowBytes) : 0) +
+                                (cuuint64_t)q.n_kv * q.stride;
+        // the tile in chunk order with one copy: {16 bytes, rows (272 apart), 17 chunks (16 apart)}
+        const cuuint64_t dims3[3] = {16, rows, 17};
+        const cuuint64_t strides3[2] = {(cuuint64_t)kRowBytes, 16};
+        const cuuint32_t box3[3] = {16, (cuuint32_t)kTile, 17};
+        const cuuint32_t elem3[3] = {1, 1, 1};
+        CUresult r = fn(&vmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<unsigned char *>(q.v), dims3,
+                        strides3, box3, elem3, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        v3d = r == CUDA_SUCCESS;
+        static const bool verbose = getenv("HIPML_VERBOSE") != nullptr;
+        if (verbose)
+            fprintf(stderr, "hipml: decode V tiles land with %s\n",
+                    v3d ? "one 3-D tensor copy" : "17 2-D tensor copies (3-D view refused)");
+        if (!v3d) {
+            // the driver refuses the overlapping view: one copy per chunk from the plain 2-D view
+            const cuuint64_t dims[2] = {(cuuint64_t)kRowBytes, rows};
+            const cuuint64_t strides[1] = {(cuuint64_t)kRowBytes};
+            const cuuint32_t box[2] = {16, (cuuint32_t)kTile};
+            const cuuint32_t elem[2] = {1, 1};
+            r = fn(&vmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<unsigned char *>(q.v), dims, strides,
+                   box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        }
+        if (r != CUDA_SUCCESS)
+            return fail(HIPML_ERR_INVALID_ARGUMENT, "cuTensorMapEncodeTiled (V cache) failed: %d", (int)r);
+    }
     bool second_launch = false;
     if (q.out != nullptr) {
         // most runs a (slot, KV head) can have under the plan in force
@@ -954,10 +1567,14 @@ int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
             q.out = nullptr;
         }
     }
-    rc = q.q4 ? launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
-                           status)
-              : launch_pdl(attn_decode_kv_tc<false>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1, q,
-                           status);
+    if (i8_body)
+        rc = launch_pdl(i8::attn_decode_kv_i8, grid, dim3(kThreads), (size_t)i8::kSmem, stream, 1, vmap, v3d, q,
+                        status);
+    else
+        rc = q.q4 ? launch_pdl(attn_decode_kv_tc<true>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1,
+                               q, status)
+                  : launch_pdl(attn_decode_kv_tc<false>, grid, dim3(kThreads), (size_t)kSmemBytes, stream, 1,
+                               q, status);
     if (rc != 0 || !second_launch) return rc;
     q.out = p.out;
     return launch_pdl(attn_decode_fold_tree, dim3(q.n_kv, slots), dim3(kThreads), 0, stream, 1, q, status);

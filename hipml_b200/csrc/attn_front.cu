@@ -5,8 +5,8 @@
 // 315-329 (qg_split), 354-360 (q_gate), composed as in attention.rs:117-143. Kernels replaced:
 // crates/hipml-kernels/kernels/attn_front_f32.hip:34-135, attn_chunk_f32.hip:22-98 and
 // q_gate_f32.hip. The four kernels with the reference's names keep its parameter lists and
-// launch shapes (a launch by name with the reference's argument array works unchanged);
-// attn_front_rows_q8 is the form this library's own launchers use.
+// launch shapes (a launch by name with the reference's argument array works unchanged) around
+// bodies of this file's own; attn_front_rows_q8 is the form this library's own launchers use.
 //
 // attn_front_rows_q8: one CTA of 8 warps per token. The rotation angles depend on the
 // position and the channel pair only, so the CTA computes the n_rot/2 (cos, sin) pairs once
@@ -51,7 +51,9 @@ __device__ __forceinline__ void rope_angle(const RopeSpec &r, int c, const int (
     sn = (float)s;
 }
 
-// Block-wide sum (any block size up to 1024 that is a multiple of 32).
+constexpr int kMaxHeadDim = 256;
+
+// Sum over the block (any block size that is a multiple of 32); `red` holds one float per warp.
 __device__ __forceinline__ float block_sum(float v, float *red) {
     v = warp_sum(v);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
@@ -63,36 +65,45 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
     return t;
 }
 
-// One head row by one block: RMS norm with weights w, then M-RoPE; src may equal dst.
-__device__ __forceinline__ void norm_rope_row(const float *src, float *dst, const float *w,
-                                              int head_dim, const RopeSpec &r, const int (&pos)[4],
-                                              float eps, float *buf, float *red) {
-    float acc = 0.0f;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) acc = fmaf(src[d], src[d], acc);
-    const float mean_sq = block_sum(acc, red) / (float)head_dim;
-    const float scale = 1.0f / sqrtf(mean_sq + eps);
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) buf[d] = src[d] * scale * w[d];
-    __syncthreads();
-    const int half = r.n_rot >> 1;
-    for (int c = threadIdx.x; c < half; c += blockDim.x) {
-        float cs, sn;
-        rope_angle(r, c, pos, cs, sn);
-        const float x1 = buf[c], x2 = buf[c + half];
-        dst[c] = x1 * cs - x2 * sn;
-        dst[c + half] = x1 * sn + x2 * cs;
+// One head row by one block, written from the CPU definition: y = x / sqrt(mean(x^2) + eps) * w
+// (ops.rs:181-187), then the first n_rot channels rotated in NeoX pairs (c, c + n_rot / 2) by the
+// angle position * theta^(-2c / n_rot) (ops.rs:260-309). No staging buffer: a thread owns whole
+// pairs, reads both inputs, and writes both outputs, so `in` may be `out` (the K rows are
+// rotated in place); channels past n_rot are only normalised.
+__device__ __forceinline__ void head_row_norm_rope(const float *in, float *out, const float *weight,
+                                                   int head_dim, const RopeSpec &rope,
+                                                   const int (&pos)[4], float eps, float *red) {
+    float sq = 0.0f;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) sq = fmaf(in[d], in[d], sq);
+    const float inv_rms = 1.0f / sqrtf(block_sum(sq, red) / (float)head_dim + eps);
+    const int pairs = rope.n_rot >> 1;
+    // work item i: a rotated pair for i < pairs, one plain channel after them
+    for (int i = threadIdx.x; i < head_dim - pairs; i += blockDim.x) {
+        if (i < pairs) {
+            const float a = in[i] * inv_rms * weight[i];
+            const float b = in[i + pairs] * inv_rms * weight[i + pairs];
+            float cs, sn;
+            rope_angle(rope, i, pos, cs, sn);
+            out[i] = a * cs - b * sn;
+            out[i + pairs] = a * sn + b * cs;
+        } else {
+            const int d = i + pairs;
+            out[d] = in[d] * inv_rms * weight[d];
+        }
     }
-    for (int d = r.n_rot + threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = buf[d];
-    __syncthreads();
 }
-
-constexpr int kMaxHeadDim = 256;
 
 }  // namespace
 
-// ---- the reference's entry points ----------------------------------------------------------
+// ---- entries by the reference's names --------------------------------------------------------
+// Kept so that a launch by name with the reference's argument array and launch shape works
+// unchanged (Kernel::launch, crates/hipml-hip/src/device.rs:543-580): the names, parameter
+// lists and grids are the reference's (attn_front_f32.hip, attn_chunk_f32.hip), the bodies are
+// this file's own (one routine for all three, written from the CPU definition above). The
+// library's own launchers take the one-pass form further down instead.
 
-// grid (n_heads + n_kv), block 256: block h < n_heads owns query head h (joint q|gate row in,
-// q and gate out), the others own key head h - n_heads (in place in k).
+// grid (n_heads + n_kv), block 256: blocks below n_heads take a query head (q half of its
+// q|gate row -> q, gate half -> gate), the rest a key head (in place).
 extern "C" __global__ void attn_front_f32(const float *__restrict__ qg, float *__restrict__ q,
                                           float *__restrict__ gate, float *k,
                                           const float *__restrict__ q_norm,
@@ -101,42 +112,42 @@ extern "C" __global__ void attn_front_f32(const float *__restrict__ qg, float *_
                                           const int *__restrict__ pos, float theta_base, float eps) {
     griddep_launch();
     griddep_wait();
-    __shared__ float buf[kMaxHeadDim];
     __shared__ float red[32];
-    const int h = blockIdx.x;
-    const bool is_q = h < n_heads;
-    const int hr = is_q ? h : h - n_heads;
-    if (hr >= (is_q ? n_heads : n_kv) || head_dim > kMaxHeadDim) return;
-    const float *src = is_q ? qg + (size_t)hr * 2 * head_dim : k + (size_t)hr * head_dim;
-    float *dst = is_q ? q + (size_t)hr * head_dim : k + (size_t)hr * head_dim;
-    if (is_q) {
-        float *gd = gate + (size_t)hr * head_dim;
-        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) gd[d] = src[head_dim + d];
+    const int row = blockIdx.x;
+    if (row >= n_heads + n_kv) return;
+    const RopeSpec rope = {n_rot, s0, s1, s2, s3, theta_base};
+    const int ids[4] = {pos[0], pos[1], pos[2], pos[3]};
+    if (row < n_heads) {
+        const float *pair = qg + (size_t)row * 2 * head_dim;
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x)
+            gate[(size_t)row * head_dim + d] = pair[head_dim + d];
+        head_row_norm_rope(pair, q + (size_t)row * head_dim, q_norm, head_dim, rope, ids, eps, red);
+    } else {
+        float *key = k + (size_t)(row - n_heads) * head_dim;
+        head_row_norm_rope(key, key, k_norm, head_dim, rope, ids, eps, red);
     }
-    const RopeSpec r = {n_rot, s0, s1, s2, s3, theta_base};
-    const int p4[4] = {pos[0], pos[1], pos[2], pos[3]};
-    norm_rope_row(src, dst, is_q ? q_norm : k_norm, head_dim, r, p4, eps, buf, red);
 }
 
-// grid (n_heads, tokens), block head_dim.
+// grid (n_heads, tokens), block head_dim: the q|gate rows of a chunk pulled apart.
 extern "C" __global__ void qg_split_chunk_f32(const float *__restrict__ qg, float *__restrict__ q,
                                               float *__restrict__ gate, int n_heads, int head_dim,
                                               int tokens) {
     griddep_launch();
     griddep_wait();
-    const int t = blockIdx.y, h = blockIdx.x;
-    if (t >= tokens || h >= n_heads) return;
-    const float *src = qg + ((size_t)t * n_heads + h) * 2 * head_dim;
-    float *qd = q + ((size_t)t * n_heads + h) * head_dim;
-    float *gd = gate + ((size_t)t * n_heads + h) * head_dim;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        qd[d] = src[d];
-        gd[d] = src[head_dim + d];
+    if ((int)blockIdx.y >= tokens || (int)blockIdx.x >= n_heads) return;
+    const size_t row = (size_t)blockIdx.y * n_heads + blockIdx.x;
+    // element e of the joint row goes to q (first half) or gate (second half)
+    for (int e = threadIdx.x; e < 2 * head_dim; e += blockDim.x) {
+        const float x = qg[row * 2 * head_dim + e];
+        if (e < head_dim)
+            q[row * head_dim + e] = x;
+        else
+            gate[row * head_dim + e - head_dim] = x;
     }
 }
 
-// grid (n_heads + n_kv, tokens), block head_dim: RMS norm then rope in place, text positions
-// (every section uses pos0 + t).
+// grid (n_heads + n_kv, tokens), block head_dim: norm + rope of a chunk's rows in place; token t
+// sits at text position pos0 + t (all four position ids equal).
 extern "C" __global__ void norm_rope_chunk_f32(float *__restrict__ q, float *__restrict__ k,
                                                const float *__restrict__ qw,
                                                const float *__restrict__ kw, int n_heads, int n_kv,
@@ -144,17 +155,14 @@ extern "C" __global__ void norm_rope_chunk_f32(float *__restrict__ q, float *__r
                                                int pos0, int tokens) {
     griddep_launch();
     griddep_wait();
-    __shared__ float buf[kMaxHeadDim];
     __shared__ float red[32];
-    const int t = blockIdx.y, hb = blockIdx.x;
-    const bool is_q = hb < n_heads;
-    const int h = is_q ? hb : hb - n_heads;
-    const int rows = is_q ? n_heads : n_kv;
-    if (t >= tokens || h >= rows || head_dim > kMaxHeadDim) return;
-    float *x = (is_q ? q : k) + ((size_t)t * rows + h) * head_dim;
-    const RopeSpec r = {n_rot, 0, 0, 0, 0, theta_base};
-    const int p4[4] = {pos0 + t, pos0 + t, pos0 + t, pos0 + t};
-    norm_rope_row(x, x, is_q ? qw : kw, head_dim, r, p4, eps, buf, red);
+    const int t = blockIdx.y, row = blockIdx.x;
+    if (t >= tokens || row >= n_heads + n_kv) return;
+    const RopeSpec rope = {n_rot, 0, 0, 0, 0, theta_base};
+    const int ids[4] = {pos0 + t, pos0 + t, pos0 + t, pos0 + t};
+    float *x = row < n_heads ? q + ((size_t)t * n_heads + row) * head_dim
+                             : k + ((size_t)t * n_kv + (row - n_heads)) * head_dim;
+    head_row_norm_rope(x, x, row < n_heads ? qw : kw, head_dim, rope, ids, eps, red);
 }
 
 // y[i] = q[i] * sigmoid(gate[i]); one thread per element.

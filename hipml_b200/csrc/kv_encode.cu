@@ -247,19 +247,21 @@ int launch_kv_encode_bulk_rows_q4(cudaStream_t stream, const float *k, const flo
                       kc, vc, n_kv, stride, start, rows, src0);
 }
 
-// Threads [0,width) copy K, [width,2*width) copy V, into cache row step[0].
+// One token's K and V rows into row step[0] of the position-major f32 caches. The entry name,
+// parameter list and launch shape (ceil(2 * width / 256) blocks of 256 threads, one element per
+// thread) are what a launch by name passes (AttnLayer::append_at, crates/hipml-kernels/src/
+// attn_gpu.rs:885-912); the body treats the launch as one index space over the pair of rows.
 extern "C" __global__ void kv_append_f32(float *__restrict__ k_cache, float *__restrict__ v_cache,
                                          const float *__restrict__ k, const float *__restrict__ v,
                                          const int *__restrict__ step, int width) {
     griddep_launch();
     griddep_wait();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= 2 * width) return;
-    const size_t base = (size_t)step[0] * (size_t)width;
-    if (i < width)
-        k_cache[base + i] = k[i];
-    else
-        v_cache[base + (i - width)] = v[i - width];
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;   // element of the (K row | V row) pair
+    const int which = e / width, col = e - which * width;
+    if (which > 1) return;
+    float *cache = which ? v_cache : k_cache;
+    const float *row = which ? v : k;
+    cache[(size_t)step[0] * (size_t)width + col] = row[col];
 }
 
 // Rows t < tokens of k/v land at cache row pos0+t. One thread per 4 floats when

@@ -21,6 +21,7 @@ struct DecodeParams {
     int splits;
     int by_stride;        // 1: runs of ceil(stride/splits) cache rows; 0: ceil(len/splits)
     int q4;               // 1: the cache is q4_0 (18-byte blocks), 0: q8_0
+    int legacy_body = 0;  // 1: q8_0 with the value side on mma.sync too (the A/B body, selector 7)
     int run_cap;          // tensor-core body, by_stride == 0: at most this many live runs per
                           // KV head, balanced to within one 64-key tile (0: the reference's runs)
     int share_slots;      // tensor-core body, several slots: the device's CTA slots, shared by
