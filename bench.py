@@ -1089,6 +1089,8 @@ def profile_case(args):
     from hipml_b200 import api
     torch.cuda.set_device(0)
     api.set_decode_fold_mode(args.fold_mode)
+    if args.body:
+        api.set_decode_body(args.body)
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(7)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.reps)]
@@ -1228,6 +1230,7 @@ def main():
     ap.add_argument("--impl", default="hipml_b200")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--all-depths", action="store_true", help="decode_steps: every depth and the batched cases")
+    ap.add_argument("--body", type=int, default=0, help="decode cases: 1 values on mma.sync, 2 on tcgen05")
     ap.add_argument("--fold-mode", type=int, default=0, help="decode cases: 1 = the fold as its own launch")
     args = ap.parse_args()
     if args.case:

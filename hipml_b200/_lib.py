@@ -96,6 +96,7 @@ SIGNATURES = {
                                                         C.POINTER(_vp), _i, _i, _i, _u]),
     "hipml_set_decode_cta_slots": (_i, [_i]),
     "hipml_set_decode_fold_mode": (_i, [_i]),
+    "hipml_set_decode_body": (_i, [_i]),
     "hipml_decode_plan_quota": (_i, [C.POINTER(_i), _i, _i, _i, _i]),
     "hipml_attn_decode_kv_static": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i,
                                          _sz, _sz]),

@@ -150,6 +150,11 @@ def set_decode_fold_mode(mode: int) -> None:
     _lib.check("set_decode_fold_mode", _lib.load().hipml_set_decode_fold_mode(mode))
 
 
+def set_decode_body(body: int) -> None:
+    """1: values on mma.sync (default); 2: values on tcgen05 kind::i8."""
+    _lib.check("set_decode_body", _lib.load().hipml_set_decode_body(body))
+
+
 def decode_plan_quota(lens, splits, n_kv, cta_slots) -> int:
     """64-row tiles per run of the multi-slot decode plan for these live lengths (host mirror)."""
     arr = (C.c_int * len(lens))(*[int(v) for v in lens])

@@ -1433,6 +1433,7 @@ int *decode_tc_setup(int *rc) {
 }
 
 std::atomic<int> g_two_launch_fold{0};
+std::atomic<int> g_decode_body{1};   // 1: values on mma.sync, 2: values on tcgen05 kind::i8
 
 int i8_setup() {
     static std::mutex mu;
@@ -1453,6 +1454,7 @@ int i8_setup() {
 }  // namespace
 
 void decode_set_two_launch_fold(int on) { g_two_launch_fold.store(on ? 1 : 0); }
+void decode_set_body(int body) { g_decode_body.store(body); }
 
 // Which arrival-counter region a launch on `stream` uses. Two launches may share a region
 // only if they cannot overlap on the device, so the key is what serialises launches: the
@@ -1519,7 +1521,10 @@ int launch_decode_tc(cudaStream_t stream, const DecodeParams &p, int slots) {
         grid = dim3(q.n_kv * q.run_cap, slots);
     // The body with the value side on tcgen05 (int8 operands): q8_0, a GQA group of at most 6,
     // slots a whole number of 272-byte rows apart.
-    const bool i8_body = !q.q4 && !q.legacy_body && q.n_heads / q.n_kv <= 6 && q.kv_slot_bytes % kRowBytes == 0;
+    // (selector 7 asks for the mma.sync values, selector 8 for the tcgen05 values; otherwise the
+    // process-wide choice of hipml_set_decode_body, whose default is the faster of the two)
+    const int want = q.legacy_body == 1 ? 1 : (q.legacy_body == 2 ? 2 : g_decode_body.load());
+    const bool i8_body = want == 2 && !q.q4 && q.n_heads / q.n_kv <= 6 && q.kv_slot_bytes % kRowBytes == 0;
     CUtensorMap vmap;
     int v3d = 0;
     if (i8_body) {

@@ -150,8 +150,9 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     // The reference remaps selector 0 to its warp kernel at head_dim 256; ids it keeps for
     // experimental variants have no counterpart here.
     bool tensor_core;
-    if (selector == 0 || selector == 4 || selector == 7) {
-        // (7: this library's A/B body with both contractions on mma.sync, head_dim 256 only)
+    if (selector == 0 || selector == 4 || selector == 7 || selector == 8) {
+        // (7 / 8: this library's two bodies by name -- values on mma.sync / on tcgen05 kind::i8 --
+        // for A/B runs, head_dim 256 only; 0 takes the process-wide default)
         tensor_core = head_dim == 256;
         if (selector != 0 && head_dim != 256)
             return fail(HIPML_ERR_INVALID_ARGUMENT,
@@ -185,7 +186,7 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
     p.splits = splits;
     p.by_stride = 0;
     p.q4 = selector == 1;
-    p.legacy_body = selector == 7;
+    p.legacy_body = selector == 7 ? 1 : (selector == 8 ? 2 : 0);
     p.run_cap = decode_run_cap(n_kv);
     p.share_slots = 0;
     p.n_slots = 1;
@@ -276,13 +277,13 @@ int hipml_attn_decode_kv_append(hipml_stream_t stream, const int *step, int sele
         return fail(HIPML_ERR_INVALID_ARGUMENT, "k_off/v_off must be multiples of 16 bytes");
     unsigned char *kc = (unsigned char *)k + k_off, *vc = (unsigned char *)v + v_off;
     const bool fused =
-        (selector == 0 || selector == 1 || selector == 4 || selector == 7) && head_dim == 256 &&
+        (selector == 0 || selector == 1 || selector == 4 || selector == 7 || selector == 8) && head_dim == 256 &&
         ((reinterpret_cast<size_t>(kc) | reinterpret_cast<size_t>(vc) | reinterpret_cast<size_t>(k_row) |
           reinterpret_cast<size_t>(v_row)) & 15) == 0;
     if (!fused) {
         // any other selector, head size or alignment: the two launches the reference makes
         const int dtype = selector == 1 ? 1 : 0;
-        if (selector != 0 && selector != 1 && selector != 4 && selector != 6 && selector != 7)
+        if (selector != 0 && selector != 1 && selector != 4 && selector != 6 && selector != 7 && selector != 8)
             return fail(HIPML_ERR_INVALID_ARGUMENT, "unknown KV dtype %d", selector);
         if (int e = hipml_kv_encode(stream, step, dtype, k_row, v_row, kc, vc, n_kv, head_dim, stride))
             return e;
@@ -838,6 +839,13 @@ int hipml_attn_decode_cols_f32(hipml_stream_t stream, const float *q, const floa
 int hipml_set_decode_cta_slots(int slots) {
     if (slots < 0) return fail(HIPML_ERR_INVALID_ARGUMENT, "decode CTA slots %d", slots);
     g_cta_slots_override.store(slots);
+    return 0;
+}
+
+int hipml_set_decode_body(int body) {
+    if (body != 1 && body != 2)
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "decode body %d (1 values on mma.sync, 2 values on tcgen05)", body);
+    decode_set_body(body);
     return 0;
 }
 

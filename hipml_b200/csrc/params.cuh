@@ -21,7 +21,8 @@ struct DecodeParams {
     int splits;
     int by_stride;        // 1: runs of ceil(stride/splits) cache rows; 0: ceil(len/splits)
     int q4;               // 1: the cache is q4_0 (18-byte blocks), 0: q8_0
-    int legacy_body = 0;  // 1: q8_0 with the value side on mma.sync too (the A/B body, selector 7)
+    int legacy_body = 0;  // q8_0 value side: 0 the process-wide default, 1 mma.sync (selector 7),
+                          // 2 tcgen05 kind::i8 (selector 8)
     int run_cap;          // tensor-core body, by_stride == 0: at most this many live runs per
                           // KV head, balanced to within one 64-key tile (0: the reference's runs)
     int share_slots;      // tensor-core body, several slots: the device's CTA slots, shared by
@@ -208,6 +209,7 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part
 size_t decode_exchange_bytes(int n_heads, int head_dim, int shards);
 int launch_decode_collect(cudaStream_t stream, const DecodeParams &p, int *status);
 void decode_set_two_launch_fold(int on);
+void decode_set_body(int body);
 
 // Attention front end and tail (attn_front.cu).
 int launch_q_gate(cudaStream_t stream, const float *q, const float *gate, float *y, long long n);

@@ -454,6 +454,11 @@ int hipml_attn_chunk_staged_gated(hipml_stream_t stream, const float *q, float *
  * sum over slots of max(1, ceil(ceil(len/64) / quota)) * n_kv, never exceed cta_slots.
  * Returns -1 for arguments outside the plan's domain (cta_slots < 2 * slots * n_kv). */
 int hipml_set_decode_cta_slots(int slots);
+/* Which body the q8_0 head_dim-256 decode kernel uses where the caller leaves the choice open
+ * (selector 0 / 4, and every multi-slot entry): 1 = both contractions on mma.sync (default),
+ * 2 = the value contraction on tcgen05.mma kind::i8 with int32 accumulators in TMEM (GQA group
+ * <= 6). Selectors 7 and 8 of hipml_attn_decode_kv name the two bodies directly. */
+int hipml_set_decode_body(int body);
 int hipml_set_decode_fold_mode(int mode);
 int hipml_decode_plan_quota(const int *lens, int slots, int splits, int n_kv, int cta_slots);
 

@@ -19,6 +19,16 @@ pytestmark = pytest.mark.gpu
 NAN_SCALE = 0x7E00  # f16 NaN: a canary for rows a kernel must not read
 
 
+@pytest.fixture(params=[1, 2], ids=["values_mma_sync", "values_tcgen05"], autouse=True)
+def decode_body(request):
+    """Every test of this file runs once per body of the head_dim-256 q8_0 kernel (the entries
+    that leave the choice open take the process-wide one)."""
+    from hipml_b200 import api
+    api.set_decode_body(request.param)
+    yield request.param
+    api.set_decode_body(1)
+
+
 def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
@@ -55,11 +65,11 @@ def _assert_close(expected, got, tight=2e-5):
     assert ma <= tight and rl <= tight, (ma, rl)
 
 
-@pytest.mark.parametrize("selector", [0, 7, 6], ids=["tensor_core", "mma_sync_values", "scalar"])
+@pytest.mark.parametrize("selector", [7, 8, 6], ids=["mma_sync_values", "tcgen05_values", "scalar"])
 @pytest.mark.parametrize("case", cases.KV_CASES, ids=lambda c: c.name)
 def test_reference_kv_cases(case, selector):
-    if selector == 7 and case.dim != 256:
-        pytest.skip("the mma.sync A/B body is head_dim 256 only")
+    if selector in (7, 8) and case.dim != 256:
+        pytest.skip("the tensor-core bodies are head_dim 256 only")
     q, kb, vb = cases.kv_case_inputs(case)
     expected = cases.kv_case_expected(case, q, kb, vb)
     got, acc, ml = _run_decode(q, kb, vb, case.heads, case.n_kv, case.dim, case.seq, case.seq,
@@ -69,7 +79,7 @@ def test_reference_kv_cases(case, selector):
     assert not np.isnan(acc).any() and not np.isnan(ml).any()
 
 
-@pytest.mark.parametrize("selector", [0, 7, 6], ids=["tensor_core", "mma_sync_values", "scalar"])
+@pytest.mark.parametrize("selector", [7, 8, 6], ids=["mma_sync_values", "tcgen05_values", "scalar"])
 def test_reference_deep_case_100000_tokens(selector):
     c = cases.DEEP_CASE
     q, kb, vb = cases.kv_case_inputs(c)
@@ -79,7 +89,7 @@ def test_reference_deep_case_100000_tokens(selector):
     _assert_close(expected, got)
 
 
-@pytest.mark.parametrize("selector", [0, 7, 6], ids=["tensor_core", "mma_sync_values", "scalar"])
+@pytest.mark.parametrize("selector", [7, 8, 6], ids=["mma_sync_values", "tcgen05_values", "scalar"])
 @pytest.mark.parametrize("seq,pad", [(1, 7), (63, 1), (64, 0), (65, 200), (127, 3), (129, 0), (672, 136),
                                      (2500, 600)])
 def test_shipped_shape_with_stride_beyond_live_length(seq, pad, selector):
@@ -106,7 +116,7 @@ def test_more_splits_than_positions_leaves_empty_partials_neutral():
     q = rng.normals(heads * hd)
     kb, vb = O.quantize_q8(rng.normals(seq * hd)), O.quantize_q8(rng.normals(seq * hd))
     expected = O.attn_decode_kv_q8(q, kb, vb, heads, n_kv, hd, seq, 0.0625)
-    for selector in (0, 7, 6):
+    for selector in (7, 8, 6):
         got, acc, ml = _run_decode(q, kb, vb, heads, n_kv, hd, seq, seq, 0.0625, splits, selector)
         _assert_close(expected, got)
         ml = ml.reshape(heads, splits, 2)
