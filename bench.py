@@ -768,12 +768,16 @@ def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs)
         st_peer, mode_peer, out_peer = measure(token_peer)
         ok = api.check_device_status() == 0
         same = bool(torch.allclose(out_peer, out_nccl, rtol=0, atol=1e-6))
+        # up to 2 ranks the split pass publishes and collects itself; beyond that the exchange is
+        # a second launch of (head, rank) CTAs (one SM cannot feed NVLink for many peers)
+        one_launch = world <= 2
         peer = {"ms_per_step": st_peer["median"], "ms_per_step_min": st_peer["min"],
                 "ms_per_step_max": st_peer["max"], "launch": mode_peer, "status_ok": ok,
-                "matches_nccl_form": same, "launches_per_step": layers}
+                "matches_nccl_form": same, "launches_per_step": layers * (1 if one_launch else 2)}
         if ok and same and st_peer["median"] < ms_nccl:
             stats, ms_step, mode = st_peer, st_peer["median"], mode_peer
-            exchange = "peer-memory stores inside the split pass"
+            exchange = ("peer-memory stores inside the split pass" if one_launch else
+                        "peer-memory stores by an exchange launch after the split pass")
     # parity: layer 0's cache shards gathered on rank 0, last step against the oracle
     pad = max(sharding.decode_shard_range(capacity, world, r)[1] -
               sharding.decode_shard_range(capacity, world, r)[0] for r in range(world))
@@ -845,6 +849,14 @@ def gpu_main(args):
     import oracle as O
     from hipml_b200 import _lib as L, api
     pk = peaks()
+    if args.decode_only and world > 1:
+        # (development aid: the sequence-split decode leg alone)
+        r = decode_sharded(torch, dist, api, args.depth, DECODE_STEPS, LAYERS, world, rank, pk["hbm_gbs"])
+        if rank == 0:
+            print(json.dumps(r))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
 
     def rank_max(x):
         if dist is None:
@@ -1229,6 +1241,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="hipml_b200")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--decode-only", action="store_true", help="N > 1: only the sequence-split decode leg")
     ap.add_argument("--all-depths", action="store_true", help="decode_steps: every depth and the batched cases")
     ap.add_argument("--body", type=int, default=0, help="decode cases: 1 values on mma.sync, 2 on tcgen05")
     ap.add_argument("--fold-mode", type=int, default=0, help="decode cases: 1 = the fold as its own launch")

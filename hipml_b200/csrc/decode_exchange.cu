@@ -49,10 +49,134 @@ __global__ void __launch_bounds__(256) attn_decode_collect(DecodeParams p, int *
         atomicCAS(status, 0, 31);
 }
 
+// The exchange as a launch of its own, for many ranks: one SM cannot feed NVLink with the
+// triples of six heads for eight peers (100 KB of 16-byte stores took ~10 us from one SM), so
+// with more than kInKernelShards ranks the split pass leaves its folded triples in the local
+// staging area of the workspace and this grid of (n_heads, shards) CTAs moves them: CTA (h, w)
+// stores head h's triple into rank w's table; CTA (h, 0) then collects head h (warp = rank).
+// grid (n_heads, shards), block 256.
+__global__ void __launch_bounds__(256) attn_decode_exchange_wide(DecodeParams p, int *status) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float s_m[16], s_l[16];
+    __shared__ float s_part[8][256];
+    __shared__ int s_bad;
+    const int h = blockIdx.x, w = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int *hdr = reinterpret_cast<int *>(p.xch.ws[p.xch.rank]);
+    // every CTA reads the epoch before it adds itself to the counter; the last one advances it
+    const int e = *reinterpret_cast<volatile int *>(hdr) + 1;
+    const float *stage = reinterpret_cast<const float *>(
+        p.xch.ws[p.xch.rank] + kExchangeHeaderBytes +
+        2 * (size_t)p.xch.shards * p.n_heads * 258 * 8) + (size_t)h * 258;
+    {
+        unsigned long long *row = cell_row(p.xch.ws[w], e & 1, p.xch.shards, p.n_heads, p.xch.rank, h);
+        st_cell(row + tid, stage[tid], e);
+        if (tid < 2) st_cell(row + 256 + tid, stage[256 + tid], e);
+    }
+    if (tid == 0) s_bad = 0;
+    __syncthreads();
+    if (tid == 0) {
+        const int total = (int)(gridDim.x * gridDim.y);
+        if (atomicAdd(hdr + 1, 1) == total - 1) {
+            hdr[1] = 0;
+            *reinterpret_cast<volatile int *>(hdr) = e;
+        }
+    }
+    if (w != 0) return;
+    // ---- collect head h: warp r (and r + 8) polls rank r's cells, eight per lane
+    const unsigned long long deadline = global_timer_ns() + 1000ull * p.xch.wait_us;
+    float part[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) part[i] = 0.0f;
+    bool ok = true;
+    float vals[2][8];
+    for (int k = 0; k < 2; k++) {
+        const int r = warp + 8 * k;
+        if (r >= p.xch.shards) break;
+        const unsigned long long *src = cell_row(p.xch.ws[p.xch.rank], e & 1, p.xch.shards, p.n_heads, r, h);
+        unsigned long long c[8];
+        for (unsigned i = 0;; i++) {
+            ld_cell2(src + lane * 8, c[0], c[1]);
+            ld_cell2(src + lane * 8 + 2, c[2], c[3]);
+            ld_cell2(src + lane * 8 + 4, c[4], c[5]);
+            ld_cell2(src + lane * 8 + 6, c[6], c[7]);
+            bool all = true;
+#pragma unroll
+            for (int j = 0; j < 8; j++) all = all && (int)(c[j] >> 32) == e;
+            if (lane == 0) {
+                unsigned long long a, b;
+                ld_cell2(src + 256, a, b);
+                all = all && (int)(a >> 32) == e && (int)(b >> 32) == e;
+                if (all) {
+                    s_m[r] = __uint_as_float((unsigned)a);
+                    s_l[r] = __uint_as_float((unsigned)b);
+                }
+            }
+            if (__all_sync(0xffffffffu, all)) break;
+            if ((i & 7) == 7) {
+                if (global_timer_ns() > deadline) {
+                    ok = false;
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int j = 0; j < 8; j++) vals[k][j] = __uint_as_float((unsigned)c[j]);
+    }
+    if (!ok) s_bad = 1;
+    __syncthreads();
+    if (s_bad) {
+        if (tid == 0) atomicCAS(status, 0, 31);
+        return;
+    }
+    float big = -INFINITY;
+    for (int r = 0; r < p.xch.shards; r++) big = fmaxf(big, s_m[r]);
+    // weighted rows to shared memory, then the sum in rank order (as the other forms do)
+    for (int k = 0; k < 2; k++) {
+        const int r = warp + 8 * k;
+        if (r >= p.xch.shards) break;
+        const float wt = (s_m[r] == -INFINITY) ? 0.0f : exp2f(s_m[r] - big);
+#pragma unroll
+        for (int j = 0; j < 8; j++) vals[k][j] = __fmul_rn(vals[k][j], wt);
+    }
+    float out = 0.0f;
+    for (int k = 0; k < 2; k++) {
+        if (8 * k >= p.xch.shards) break;
+        __syncthreads();
+        if (warp + 8 * k < p.xch.shards) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) s_part[warp][lane * 8 + j] = vals[k][j];
+        }
+        __syncthreads();
+        for (int r = 0; r < 8 && 8 * k + r < p.xch.shards; r++) out = __fadd_rn(out, s_part[r][tid]);
+    }
+    float den = 0.0f;
+    for (int r = 0; r < p.xch.shards; r++) {
+        const float wt = (s_m[r] == -INFINITY) ? 0.0f : exp2f(s_m[r] - big);
+        den = __fadd_rn(den, __fmul_rn(s_l[r], wt));
+    }
+    p.out[(size_t)h * p.out_head_stride + tid] = den > 0.0f ? __fdiv_rn(out, den) : 0.0f;
+}
+
 }  // namespace
 
 size_t decode_exchange_bytes(int n_heads, int head_dim, int shards) {
-    return (size_t)kExchangeHeaderBytes + 2 * (size_t)shards * n_heads * (head_dim + 2) * 8;
+    // header, the double-buffered table of cells, and the local staging rows of the wide form
+    return (size_t)kExchangeHeaderBytes + 2 * (size_t)shards * n_heads * (head_dim + 2) * 8 +
+           (size_t)n_heads * (head_dim + 2) * 4;
+}
+
+float *decode_exchange_stage(void *ws, int n_heads, int shards) {
+    return reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(ws) + kExchangeHeaderBytes +
+                                     2 * (size_t)shards * n_heads * 258 * 8);
+}
+
+int launch_decode_exchange_wide(cudaStream_t stream, const DecodeParams &p, int *status) {
+    return launch_pdl(attn_decode_exchange_wide, dim3(p.n_heads, p.xch.shards), dim3(256), 0, stream, 1, p,
+                      status);
 }
 
 int launch_decode_collect(cudaStream_t stream, const DecodeParams &p, int *status) {

@@ -193,19 +193,36 @@ __device__ __forceinline__ bool exchange_collect_warp(const DecodeParams::Exchan
     f.den = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) f.a[i] = 0.0f;
-    for (int w = 0; w < x.shards; w++) {
-        const unsigned long long *src = cell_row(x.ws[x.rank], e & 1, x.shards, n_heads, w, h) + lane * 8;
-        unsigned long long c[8];
-        for (unsigned i = 0;; i++) {
-            ld_cell2(src, c[0], c[1]);
-            ld_cell2(src + 2, c[2], c[3]);
-            ld_cell2(src + 4, c[4], c[5]);
-            ld_cell2(src + 6, c[6], c[7]);
-            bool all = true;
+    // four ranks per round: their cells are requested together, so a round costs one trip to
+    // memory once the peers' stores have landed; the sums still run in rank order
+    for (int w0 = 0; w0 < x.shards; w0 += 4) {
+        unsigned long long c[4][8];
+        unsigned pending = 0;
 #pragma unroll
-            for (int j = 0; j < 8; j++) all = all && (int)(c[j] >> 32) == e;
-            if (all) break;
-            if ((i & 7) == 7) {
+        for (int j = 0; j < 4; j++)
+            if (w0 + j < x.shards) pending |= 1u << j;
+        for (unsigned i = 0; pending != 0; i++) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (pending & (1u << j)) {
+                    const unsigned long long *src =
+                        cell_row(x.ws[x.rank], e & 1, x.shards, n_heads, w0 + j, h) + lane * 8;
+                    ld_cell2(src, c[j][0], c[j][1]);
+                    ld_cell2(src + 2, c[j][2], c[j][3]);
+                    ld_cell2(src + 4, c[j][4], c[j][5]);
+                    ld_cell2(src + 6, c[j][6], c[j][7]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (pending & (1u << j)) {
+                    bool all = true;
+#pragma unroll
+                    for (int q = 0; q < 8; q++) all = all && (int)(c[j][q] >> 32) == e;
+                    if (all) pending &= ~(1u << j);
+                }
+            }
+            if (pending != 0 && (i & 7) == 7) {
                 if (global_timer_ns() > deadline) {
                     ok = false;
                     break;
@@ -215,10 +232,15 @@ __device__ __forceinline__ bool exchange_collect_warp(const DecodeParams::Exchan
         }
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return false;
-        const float ws = __shfl_sync(0xffffffffu, wt, w);
-        f.den = __fadd_rn(f.den, __shfl_sync(0xffffffffu, lw, w));
 #pragma unroll
-        for (int j = 0; j < 8; j++) f.a[j] = fmaf(__uint_as_float((unsigned)c[j]), ws, f.a[j]);
+        for (int j = 0; j < 4; j++) {
+            if (w0 + j < x.shards) {
+                const float ws = __shfl_sync(0xffffffffu, wt, w0 + j);
+                f.den = __fadd_rn(f.den, __shfl_sync(0xffffffffu, lw, w0 + j));
+#pragma unroll
+                for (int q = 0; q < 8; q++) f.a[q] = fmaf(__uint_as_float((unsigned)c[j][q]), ws, f.a[q]);
+            }
+        }
     }
     return true;
 }

@@ -223,6 +223,20 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
             p.xch.rank = xch->rank;
             p.xch.phases = xch->phases;
             p.xch.wait_us = xch->wait_limit_us;
+            if (xch->shards > kInKernelShards && xch->phases == 3) {
+                // many ranks: the split pass leaves the folded triples in the workspace's staging
+                // rows and a grid of (head, rank) CTAs does the exchange
+                DecodeParams local = p;
+                local.xch.phases = 0;
+                local.out = decode_exchange_stage(xch->peer_ws[xch->rank], n_heads, xch->shards);
+                local.out_head_stride = head_dim + 2;
+                local.normalize = 0;
+                local.gate = nullptr;
+                if (int e = launch_decode_tc(as_stream(stream), local, 1)) return e;
+                int *status = device_status_word();
+                if (!status) return launch_status();
+                return launch_decode_exchange_wide(as_stream(stream), p, status);
+            }
         }
         return launch_decode_tc(as_stream(stream), p, 1);
     }

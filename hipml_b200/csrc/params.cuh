@@ -208,6 +208,10 @@ int launch_chunk_tc(cudaStream_t stream, const float *q, float *out, float *part
 // half as a launch of its own (p.xch, p.out, p.n_heads are read).
 size_t decode_exchange_bytes(int n_heads, int head_dim, int shards);
 int launch_decode_collect(cudaStream_t stream, const DecodeParams &p, int *status);
+// With more ranks than this the exchange is a launch of its own over (head, rank) CTAs.
+constexpr int kInKernelShards = 2;
+float *decode_exchange_stage(void *ws, int n_heads, int shards);
+int launch_decode_exchange_wide(cudaStream_t stream, const DecodeParams &p, int *status);
 void decode_set_two_launch_fold(int on);
 void decode_set_body(int body);
 
