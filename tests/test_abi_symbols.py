@@ -43,6 +43,20 @@ def test_python_prototypes_cover_the_header():
     assert sorted(L.SIGNATURES) == _declared()
 
 
+def test_rust_binding_is_in_step_with_the_header():
+    """hipml_b200/host/hipml-cuda/src/ffi.rs is generated from the header (no Rust toolchain
+    exists where this library is built): the committed file must be what the generator writes,
+    with one declaration per symbol."""
+    import importlib.util
+    crate = os.path.join(ROOT, "hipml_b200", "host", "hipml-cuda")
+    spec = importlib.util.spec_from_file_location("gen_ffi", os.path.join(crate, "gen_ffi.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    text = open(os.path.join(crate, "src", "ffi.rs")).read()
+    assert text == gen.render()
+    assert sorted(re.findall(r"pub fn (hipml_[a-z0-9_]+)\(", text)) == _declared()
+
+
 def test_calls_that_need_no_gpu():
     L = _lib()
     lib = L.load()
