@@ -1166,7 +1166,9 @@ def profile_case(args):
         return
     if args.case == "chunk":
         # --kv-heads < 4 stands for one rank's share of a KV-head-sharded job
-        pos0, n, stride = 6144, 2048, 8200
+        # --pos0 / --rows move and shorten the chunk (a rank's share of the query rows, or a
+        # shallower key range, for the partition A/B of the multi-GPU notes)
+        pos0, n, stride = args.pos0, args.rows, 8200
         kv, sp = args.kv_heads, args.splits
         heads, qw, w = 6 * kv, 6 * kv * D, kv * D
         q = torch.randn(n, qw, device=dev, generator=g)
@@ -1194,7 +1196,7 @@ def profile_case(args):
         flops = attn_flops(chunk_pairs(pos0, n)) * kv / KV
         for r in range(args.reps):
             ms = ev[2 * r].elapsed_time(ev[2 * r + 1])
-            print(json.dumps({"case": "chunk 2048@6144", "mode": args.mode, "kv_heads": kv,
+            print(json.dumps({"case": f"chunk {n}@{pos0}", "mode": args.mode, "kv_heads": kv,
                               "splits": sp, "ms": ms, "algorithmic_tflops": flops / ms / 1e9}))
     else:
         depth = args.depth
@@ -1241,6 +1243,8 @@ def main():
     ap.add_argument("--mode", type=int, default=0)
     ap.add_argument("--splits", type=int, default=1)
     ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--pos0", type=int, default=6144, help="chunk case: position of the chunk's first row")
+    ap.add_argument("--rows", type=int, default=2048, help="chunk case: query rows of the chunk")
     ap.add_argument("--selector", type=int, default=0)
     ap.add_argument("--depth", type=int, default=100000)
     ap.add_argument("--gpus", type=int, default=1)

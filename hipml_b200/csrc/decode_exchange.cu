@@ -86,9 +86,6 @@ __global__ void __launch_bounds__(256) attn_decode_exchange_wide(DecodeParams p,
     if (w != 0) return;
     // ---- collect head h: warp r (and r + 8) polls rank r's cells, eight per lane
     const unsigned long long deadline = global_timer_ns() + 1000ull * p.xch.wait_us;
-    float part[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) part[i] = 0.0f;
     bool ok = true;
     float vals[2][8];
     for (int k = 0; k < 2; k++) {
