@@ -264,16 +264,28 @@ def prefill_e2e(torch, api, L, pf: Prefill, steps, warmup):
                          out=torch.empty(pf.tokens, pf.qw, device="cuda"),
                          ws=torch.empty_like(pf.ws)))
 
+    # the query rows this rank attends (all of them, or its share of every chunk) as byte ranges
+    row_bytes = pf.qw * 4
+    if pf.q_parts is None:
+        q_ranges = [(0, nbytes_q)]
+    else:
+        q_ranges = [((pf.chunks[ci][0] + off) * row_bytes, rows * row_bytes)
+                    for ci, (off, rows) in enumerate(pf.q_parts) if rows > 0]
+
     def step():
         for l in range(pf.layers):
             s, b = streams[l % 3], bufs[l % 3]
             sh = C.c_void_p(s.cuda_stream)
             with torch.cuda.stream(s):
-                lib.hipml_memcpy_async(C.c_void_p(b["q"].data_ptr()), host[l][0], nbytes_q, 1, sh)
+                for at, n in q_ranges:
+                    lib.hipml_memcpy_async(C.c_void_p(b["q"].data_ptr() + at), C.c_void_p(host[l][0].value + at),
+                                           n, 1, sh)
                 lib.hipml_memcpy_async(C.c_void_p(b["k"].data_ptr()), host[l][1], nbytes_kv, 1, sh)
                 lib.hipml_memcpy_async(C.c_void_p(b["v"].data_ptr()), host[l][2], nbytes_kv, 1, sh)
                 pf.layer(l, b["ws"], out=b["out"], q=b["q"], k=b["k"], v=b["v"])
-                lib.hipml_memcpy_async(host[l][3], C.c_void_p(b["out"].data_ptr()), nbytes_q, 2, sh)
+                for at, n in q_ranges:
+                    lib.hipml_memcpy_async(C.c_void_p(host[l][3].value + at), C.c_void_p(b["out"].data_ptr() + at),
+                                           n, 2, sh)
 
     def run():
         main = torch.cuda.current_stream()
@@ -287,8 +299,9 @@ def prefill_e2e(torch, api, L, pf: Prefill, steps, warmup):
     for ptrs in host:
         for p in ptrs:
             lib.hipml_host_free(p)
-    h2d = pf.layers * (nbytes_q + 2 * nbytes_kv)
-    d2h = pf.layers * nbytes_q
+    q_bytes = sum(n for _, n in q_ranges)
+    h2d = pf.layers * (q_bytes + 2 * nbytes_kv)
+    d2h = pf.layers * q_bytes
     return ms, h2d, d2h
 
 
@@ -898,9 +911,8 @@ def gpu_main(args):
     # the same job in the reference engine's loop order, through the drop-in entry, and the
     # layer-major form again right after it: the two are compared in the same power / clock
     # state (the device slows down over the first seconds of sustained tensor work)
-    half = max(args.steps // 2, 1)
-    ms_chunk_major = run_timed(torch, dist, lambda: pf.step_chunk_major(), half, 1)
-    ms_layer_major_again = run_timed(torch, dist, lambda: pf.step(), half, 1)
+    ms_chunk_major = run_timed(torch, dist, lambda: pf.step_chunk_major(), args.steps, 1)
+    ms_layer_major_again = run_timed(torch, dist, lambda: pf.step(), args.steps, 1)
     assert api.check_device_status() == 0
     # headline: the layer-major form, unless the drop-in order is more than 3 % slower
     headline = "layer-major (staged image kept across a layer's chunks)"
@@ -992,8 +1004,9 @@ def gpu_main(args):
     line["e2e"] = {"value": T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s",
                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
                    "d2h_bytes_per_step": d2h * world,
-                   "note": "per rank: its heads' Q/K/V up from pinned host memory and its output "
-                           "rows down, inside the timed region; bytes are the sum over ranks"}
+                   "note": "per rank: the Q rows it attends and its heads' K/V up from pinned host "
+                           "memory, its output rows down, inside the timed region; bytes are the "
+                           "sum over ranks"}
     if world == 1 and not args.no_decode:
         del pf
         torch.cuda.empty_cache()
