@@ -156,7 +156,14 @@ class Prefill:
             qslots = (max_rows + 31) // 32 * 32
             self.pa = self.torch.empty(splits * qslots * self.qw, device="cuda")
             self.pm = self.torch.empty(splits * qslots * self.heads * 2, device="cuda")
-            self.launches_per_step = self.layers * len(self.chunks) * 4
+        self.count_launches()
+
+    def count_launches(self):
+        """Launches of one step: append + staging for every chunk, the attention (and the
+        combine pass with key slices) for the chunks this rank attends."""
+        per_attend = 2 if self.splits >= 2 else 1
+        attended = len(self.chunks) if self.q_parts is None else sum(r > 0 for _, r in self.q_parts)
+        self.launches_per_step = self.layers * (2 * len(self.chunks) + per_attend * attended)
 
     def prepare(self, l, ci, ws, k=None, v=None):
         """Append chunk ci of layer l to the q8_0 cache and stage the new rows."""
@@ -172,6 +179,8 @@ class Prefill:
         """Chunk attention of this rank's query rows of chunk ci (all rows unless q_parts is set)."""
         pos0, n = self.chunks[ci]
         off, rows = (0, n) if self.q_parts is None else self.q_parts[ci]
+        if rows <= 0:
+            return
         q = self.q[l] if q is None else q
         out = self.out if out is None else out
         self.api.attn_chunk_staged(q[pos0 + off:pos0 + off + rows], out[pos0 + off:pos0 + off + rows],
@@ -204,6 +213,8 @@ class Prefill:
             for l in range(self.layers):
                 self.api.kv_encode_bulk(self.k[l][pos0:pos0 + n], self.v[l][pos0:pos0 + n], self.kc[l],
                                         self.vc[l], self.n_kv, D, self.stride, pos0, 0, n)
+                if rows <= 0:
+                    continue
                 self.api.attn_chunk(self.q[l][pos0 + off:pos0 + off + rows],
                                     self.kc[l], self.vc[l], self.out[pos0 + off:pos0 + off + rows],
                                     self.heads, self.n_kv, D, pos0 + off, rows, 1, self.stride, self.pa,
@@ -879,16 +890,25 @@ def gpu_main(args):
         return float(t.item())
 
     # KV-head sharding: each rank owns n_kv/world KV heads and their query heads; no data-path
-    # collective inside the attention. Beyond 4 ranks the query tiles are interleaved too.
+    # collective inside the attention. Beyond 4 ranks the ranks that share a KV head divide the
+    # chunks (or, --query-partition rows, every chunk's query rows) between them.
     from hipml_b200 import sharding
     kv_shards, q_shards, kv_index, q_index, n_kv_local, heads_local = sharding.kv_head_shard(
         H, KV, world, rank)
     pf = Prefill(torch, api, heads_local, n_kv_local, T_PREFILL, CHUNK, LAYERS,
                  seed=1 + 1000 * kv_index, stride=T_PREFILL + 8)
+    by_chunks = args.query_partition == "chunks"
+
+    def q_part(ci, n, n_chunks):
+        """This rank's query rows of chunk ci among the ranks that share its KV head."""
+        if by_chunks:
+            return sharding.chunk_part(ci, n_chunks, n, q_shards, q_index)
+        return sharding.query_part(ci, n, q_shards, q_index)
+
     if q_shards > 1:
-        # the ranks that share a KV head take rotating parts of every chunk's query rows
-        pf.q_parts = [sharding.query_part(ci, n, q_shards, q_index) for ci, (p, n) in enumerate(pf.chunks)]
-    key_splits = sharding.prefill_key_splits(CHUNK // q_shards, heads_local // n_kv_local, n_kv_local)
+        pf.q_parts = [q_part(ci, n, len(pf.chunks)) for ci, (p, n) in enumerate(pf.chunks)]
+    key_splits = sharding.prefill_key_splits(CHUNK if by_chunks else CHUNK // q_shards,
+                                             heads_local // n_kv_local, n_kv_local)
     pf.use_key_splits(key_splits, CHUNK)
 
     gpu_index = local
@@ -920,7 +940,9 @@ def gpu_main(args):
     if ms_chunk_major > 1.03 * ms_layer_major_again:
         headline, ms = "chunk-major through hipml_attn_chunk (full restage per call)", ms_chunk_major
     tok_s = T_PREFILL / (ms * 1e-3)
-    parallelism = (f"kv_head x{kv_shards}" + (f", query x{q_shards}" if q_shards > 1 else "")
+    parallelism = (f"kv_head x{kv_shards}"
+                   + (f", query x{q_shards} by {'chunk pairs' if by_chunks else 'rows of every chunk'}"
+                      if q_shards > 1 else "")
                    + (f", key slices x{key_splits} per query tile" if key_splits > 1 else ""))
 
     line = {
@@ -937,6 +959,11 @@ def gpu_main(args):
         "gpu_launches": pf.launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }
+
+    def share(c, n):
+        """This rank's part of chunk c's query rows (its causal work differs a little between
+        the halves of a chunk; the by-chunk rate is indicative)."""
+        return 1.0 if pf.q_parts is None else pf.q_parts[c][1] / n
 
     def roofline_of(per, issued):
         kernel_ms = rank_max(sum(sum(r) for r in per))       # the slowest rank's kernel time
@@ -959,8 +986,8 @@ def gpu_main(args):
             # the same per chunk position on this rank (mean over layers): [pos0, ms, TFLOP/s of
             # the rank's share]
             "by_chunk": [[p, sum(per[l][c] for l in range(LAYERS)) / LAYERS,
-                          attn_flops(chunk_pairs(p, n)) / world * LAYERS /
-                          (sum(per[l][c] for l in range(LAYERS)) * 1e9)]
+                          attn_flops(chunk_pairs(p, n)) / kv_shards * share(c, n) * LAYERS /
+                          max(sum(per[l][c] for l in range(LAYERS)) * 1e9, 1e-9)]
                          for c, (p, n) in enumerate(pf.chunks)],
         }
 
@@ -1021,7 +1048,8 @@ def gpu_main(args):
         torch.cuda.empty_cache()
         part = None
         if q_shards > 1:
-            part = lambda ci, n: sharding.query_part(ci, n, q_shards, q_index)  # noqa: E731
+            n_long = (100000 + CHUNK - 1) // CHUNK
+            part = lambda ci, n: q_part(ci, n, n_long)  # noqa: E731
         long_tokens = 100000
         ms_layer, long_parity = prefill_long(torch, api, long_tokens, heads_local, n_kv_local, part,
                                              key_splits=key_splits, kv_seed=4 + 1000 * kv_index)
@@ -1265,6 +1293,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="hipml_b200")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--query-partition", choices=["chunks", "rows"], default="chunks",
+                    help="N = 8: the ranks that share a KV head split the prefill by chunk pairs "
+                         "(i, n-1-i) or by rotating halves of every chunk's rows")
     ap.add_argument("--decode-only", action="store_true", help="N > 1: only the sequence-split decode leg")
     ap.add_argument("--all-depths", action="store_true", help="decode_steps: every depth and the batched cases")
     ap.add_argument("--body", type=int, default=0, help="decode cases: 1 values on mma.sync, 2 on tcgen05")

@@ -39,6 +39,26 @@ def query_part(chunk_index: int, chunk_rows: int, q_shards: int, q_index: int):
     return start, base + (1 if part < extra else 0)
 
 
+def chunk_part(chunk_index: int, n_chunks: int, chunk_rows: int, q_shards: int, q_index: int):
+    """(row offset, rows) of this rank's share of chunk `chunk_index` when the ranks that share
+    a KV head divide the CHUNKS of a prefill among themselves instead of every chunk's rows:
+    (0, chunk_rows) for a chunk the rank owns, (0, 0) for one it leaves to another rank. A chunk
+    at position p costs about p + chunk/2 key rows per query row, so chunks are dealt out in
+    pairs (i, n-1-i) of equal cost, the pairs going round the ranks: every rank gets the same
+    causal work, and every chunk it attends is a whole chunk (twice the query tiles of half a
+    chunk, so half the key slices and combine passes). What does not divide - the pairs beyond
+    a multiple of q_shards and the middle chunk of an odd count - is split by rows as
+    query_part does. The rank still appends every chunk's K/V rows to its cache: a later chunk
+    of its own reads them."""
+    if q_shards <= 1:
+        return 0, chunk_rows
+    pair = min(chunk_index, n_chunks - 1 - chunk_index)
+    whole_pairs = (n_chunks // 2) // q_shards * q_shards
+    if pair >= whole_pairs:
+        return query_part(chunk_index, chunk_rows, q_shards, q_index)
+    return (0, chunk_rows) if pair % q_shards == q_index else (0, 0)
+
+
 def decode_shard_range(capacity: int, world: int, rank: int):
     """Cache rows [lo, hi) of every KV head that `rank` holds, for a context of `capacity`
     rows: contiguous, as even as possible."""

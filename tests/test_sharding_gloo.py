@@ -111,6 +111,25 @@ def test_partition_arithmetic():
     assert sharding.query_part(0, 2048, 2, 0) != sharding.query_part(1, 2048, 2, 0)
     parts = sorted(sharding.query_part(0, 1697, 2, qi) for qi in range(2))
     assert parts == [(0, 849), (849, 848)]
+    # or whole chunks, dealt out in pairs (i, n-1-i) of equal causal cost; what does not divide
+    # (a pair beyond a multiple of the rank count, the middle chunk) is split by rows
+    for n_chunks, tokens in ((4, 8192), (49, 100000), (5, 10240), (2, 4096), (1, 100)):
+        chunks = [(p, min(2048, tokens - p)) for p in range(0, tokens, 2048)]
+        assert len(chunks) == n_chunks
+        work = [0, 0]
+        whole = 0
+        for ci, (p, n) in enumerate(chunks):
+            owned = [sharding.chunk_part(ci, n_chunks, n, 2, qi) for qi in range(2)]
+            covered = sorted((off, off + rows) for off, rows in owned if rows)
+            assert covered[0][0] == 0 and covered[-1][1] == n           # every row once
+            assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+            whole += len(covered) == 1
+            for qi, (off, rows) in enumerate(owned):                    # causal (query, key) pairs
+                work[qi] += rows * (p + off) + rows * (rows + 1) // 2
+        assert whole == n_chunks // 4 * 4
+        assert max(work) <= 1.02 * sum(work) / 2 or n_chunks < 4
+    assert [sharding.chunk_part(ci, 4, 2048, 2, 0)[1] for ci in range(4)] == [2048, 0, 0, 2048]
+    assert sharding.chunk_part(3, 4, 2048, 1, 0) == (0, 2048)
 
 
 def test_fold_handles_empty_shards():
