@@ -995,7 +995,7 @@ def gpu_main(args):
 
     # parity of the timed configuration + CPU baseline (the reference's own loop, one thread),
     # on every rank over its own share; the worst rank is reported
-    idx, want, cpu = prefill_oracle(pf)
+    idx, want, cpu = prefill_oracle(pf, per_chunk=80)   # ~10 s of one host core at N = 1
     pf.out.fill_(float("nan"))
     pf.layer(0, pf.ws)
     torch.cuda.synchronize()
