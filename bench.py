@@ -77,15 +77,22 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.rows, self.proc, self.index = [], None, index
+        self.first = threading.Event()
+        self.skip = 0
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
-                 "200", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                 "50", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
                 text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # the tool takes a moment to start: wait for its first line, and count only the
+            # lines that arrive after this point (while the work of the block is running)
+            self.first.wait(timeout=5.0)
+            self.skip = len(self.rows)
+            self.t0 = time.monotonic()
         except OSError:
             self.proc = None
         return self
@@ -93,6 +100,13 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
+            self.first.set()
+
+    def hold(self, fn, seconds=0.6):
+        """Keeps the same work running (untimed) until the block has lasted `seconds`, so that
+        a short timed region still leaves several samples taken under its load."""
+        while self.proc and time.monotonic() - self.t0 < seconds:
+            fn()
 
     def __exit__(self, *a):
         if self.proc:
@@ -105,7 +119,7 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], 0.0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in self.rows[self.skip:]:
             try:
                 sm.append(float(r[1]))
                 mx = max(mx, float(r[2]))
@@ -116,7 +130,9 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm),
+                "window": "every 50 ms while the warm-up and timed steps run, and the same step "
+                          "repeated (untimed) until the window is 0.6 s long"}
 
 
 # ------------------------------------------------------------------------------- GPU arm
@@ -914,6 +930,11 @@ def gpu_main(args):
     gpu_index = local
     with ClockSampler(gpu_index) as clocks:
         ms_layer_major = run_timed(torch, dist, lambda: pf.step(), args.steps, args.warmup)
+
+        def more():
+            pf.step()
+            torch.cuda.synchronize()
+        clocks.hold(more)
     assert api.check_device_status() == 0
 
     # per-launch timing of the dominant kernel (the tensor-core chunk attention; with key slices
