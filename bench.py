@@ -1055,6 +1055,38 @@ def gpu_main(args):
                    "note": "per rank: the Q rows it attends and its heads' K/V up from pinned host "
                            "memory, its output rows down, inside the timed region; bytes are the "
                            "sum over ranks"}
+    if world > 1:
+        # What a consumer that needs whole [T][6144] rows (the output projection) would add:
+        # an all-gather of every rank's output share of one layer. Not part of the attention
+        # step and not in the headline; reported on its own.
+        if pf.q_parts is None:
+            share = pf.out
+        else:
+            share = torch.cat([pf.out[p + off:p + off + rows] for (p, n), (off, rows)
+                               in zip(pf.chunks, pf.q_parts) if rows > 0]).contiguous()
+        sizes = torch.tensor([share.numel()], device="cuda", dtype=torch.int64)
+        dist.all_reduce(sizes, op=dist.ReduceOp.MAX)
+        if int(sizes.item()) == share.numel():          # equal shares (the partitions here give that)
+            gathered = torch.empty(world * share.numel(), device="cuda")
+            for _ in range(2):
+                dist.all_gather_into_tensor(gathered, share.reshape(-1))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0.record()
+            for _ in range(5):
+                dist.all_gather_into_tensor(gathered, share.reshape(-1))
+            e1.record()
+            torch.cuda.synchronize()
+            ms_gather = rank_max(e0.elapsed_time(e1) / 5)
+            line["gather_for_wo"] = {
+                "ms_per_layer": ms_gather, "bytes_per_rank": share.numel() * 4,
+                "bus_gbs": (world - 1) * share.numel() * 4 / (ms_gather * 1e-3) / 1e9,
+                "ms_per_step_16_layers": ms_gather * LAYERS,
+                "note": "NCCL all-gather of the ranks' output shares of one layer; outside the "
+                        "timed step (the attention itself needs no collective)"}
+            del gathered
+        del share
     if world == 1 and not args.no_decode:
         del pf
         torch.cuda.empty_cache()
