@@ -432,9 +432,10 @@ __device__ __forceinline__ void fold_tail(const DecodeParams &p, int *status, in
                                           int split, int runs, int group, int tid) {
     __shared__ int s_role;
     const int warp = tid >> 5, lane = tid & 31;
-    const int ngroups = (runs + kFoldGroup - 1) / kFoldGroup;
-    const int grp = split / kFoldGroup;
-    const int expect = min(kFoldGroup, runs - grp * kFoldGroup);
+    const int gsize = fold_group_of(runs);
+    const int ngroups = (runs + gsize - 1) / gsize;
+    const int grp = split / gsize;
+    const int expect = min(gsize, runs - grp * gsize);
     int *ctr = g_arrive + (size_t)p.arrive_region * kArriveRegionInts +
                (size_t)(slot * p.n_kv + kvh) * p.arrive_stride;
     // (every thread's partial stores precede the barrier; the arrival releases them)
@@ -453,9 +454,9 @@ __device__ __forceinline__ void fold_tail(const DecodeParams &p, int *status, in
     float *pa = p.part_acc + (size_t)slot * p.acc_slot + (size_t)h * p.splits * 256;
     float *ml = p.part_ml + (size_t)slot * p.ml_slot + (size_t)h * p.splits * 2;
     FoldAcc f;
-    if (warp < group) f = fold_warp(pa, ml, grp * kFoldGroup, 1, expect, lane);
+    if (warp < group) f = fold_warp(pa, ml, grp * gsize, 1, expect, lane);
     if (ngroups > 1) {
-        if (warp < group) fold_store_partial(pa, ml, grp * kFoldGroup, f, lane);
+        if (warp < group) fold_store_partial(pa, ml, grp * gsize, f, lane);
         __syncthreads();
         if (tid == 0) {
             const int role = arrive_acq_rel(ctr) == ngroups - 1;
@@ -464,7 +465,7 @@ __device__ __forceinline__ void fold_tail(const DecodeParams &p, int *status, in
         }
         __syncthreads();
         if (!s_role) return;
-        if (warp < group) f = fold_warp(pa, ml, 0, kFoldGroup, ngroups, lane);
+        if (warp < group) f = fold_warp(pa, ml, 0, gsize, ngroups, lane);
     }
     fold_finish(p, status, slot, kvh, group, f);
 }
@@ -1384,20 +1385,21 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fold_tree(DecodeParams p
         __syncthreads();
     }
     const int runs = live_runs(p, slot, p.share_slots > 0 ? s_quota : 0);
-    const int ngroups = (runs + kFoldGroup - 1) / kFoldGroup;
+    const int gsize = fold_group_of(runs);
+    const int ngroups = (runs + gsize - 1) / gsize;
     FoldAcc f;
     if (warp < group) {
         const int h = kvh * group + warp;
         float *pa = p.part_acc + (size_t)slot * p.acc_slot + (size_t)h * p.splits * 256;
         float *ml = p.part_ml + (size_t)slot * p.ml_slot + (size_t)h * p.splits * 2;
         for (int g = 0; g < ngroups; g++) {
-            f = fold_warp(pa, ml, g * kFoldGroup, 1, min(kFoldGroup, runs - g * kFoldGroup), lane);
-            if (ngroups > 1) fold_store_partial(pa, ml, g * kFoldGroup, f, lane);
+            f = fold_warp(pa, ml, g * gsize, 1, min(gsize, runs - g * gsize), lane);
+            if (ngroups > 1) fold_store_partial(pa, ml, g * gsize, f, lane);
         }
         if (ngroups > 1) {
             __threadfence();
             __syncwarp();
-            f = fold_warp(pa, ml, 0, kFoldGroup, ngroups, lane);
+            f = fold_warp(pa, ml, 0, gsize, ngroups, lane);
         }
     }
     fold_finish(p, status, slot, kvh, group, f);

@@ -39,7 +39,7 @@ struct DecodeParams {
     // Fold inside the split pass (tensor-core body). The CTA that completes a group of eight
     // runs of a (slot, KV head) folds them into the group's first slot, and the CTA that
     // completes the last group folds the groups and writes the output rows of the head group,
-    // so a decode step of a layer is one launch. The arrival counters live in library-owned
+    // so a decode step of a layer is one launch (a head with at most 30 runs is one group). The arrival counters live in library-owned
     // device memory (region `arrive_region`, `arrive_stride` counters per (slot, KV head):
     // one for the groups, then one per group) and return to zero by themselves.
     float *out = nullptr;            // nullptr: partials only, the caller launches the fold
@@ -146,6 +146,12 @@ int launch_decode_fold_tree(cudaStream_t stream, const DecodeParams &p, int slot
 // `counters` = slots * n_kv * arrive_stride must fit a region.
 int decode_arrive_region(cudaStream_t stream, long long counters);
 constexpr int kFoldGroup = 8;          // runs per first-level group of the fold
+constexpr int kFoldFlat = 30;          // up to this many runs a head is folded in one level
+// Runs per first-level group for a head with `runs` live runs: few runs are one group (one
+// arrival and up to three rounds of loads instead of two dependent levels).
+__host__ __device__ __forceinline__ int fold_group_of(int runs) {
+    return runs <= kFoldFlat ? 32 : kFoldGroup;
+}
 constexpr int kArriveRegionInts = 4096;
 // Fold of (acc, max, sum) triples over the split axis; all strides in floats.
 struct FoldParams {
