@@ -773,6 +773,17 @@ def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs)
                 step_buf[i], kn[i, l] if own else None, vn[i, l] if own else None, q[i, l], kc[l], vc[l],
                 acc, ml, out[i, l], H, KV, D, stride, SCALE, splits, peer_ws, rank)
 
+    def token_by_head(i):
+        # the result divided by head: head h's triples go to rank h / (H / world) alone, which
+        # writes that head's output row (what a row-parallel output projection reads): the split
+        # pass sends each triple once, so it is one launch per layer at any rank count
+        splits = api.decode_splits(max(step_host[i][1], 1))
+        own = owners[i] == rank
+        for l in range(layers):
+            api.attn_decode_kv_shard_exchange_append(
+                step_buf[i], kn[i, l] if own else None, vn[i, l] if own else None, q[i, l], kc[l], vc[l],
+                acc, ml, out[i, l], H, KV, D, stride, SCALE, splits, peer_ws, rank, phases=7)
+
     def measure(token):
         token(0)
         torch.cuda.synchronize()
@@ -818,6 +829,25 @@ def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs)
             stats, ms_step, mode = st_peer, st_peer["median"], mode_peer
             exchange = ("peer-memory stores inside the split pass" if one_launch else
                         "peer-memory stores by an exchange launch after the split pass")
+    finite = bool(torch.isfinite(out).all().item())     # of the replicated forms' outputs
+    by_head, out_by_head = None, None
+    if peer_ws is not None and H % world == 0:
+        out.fill_(float("nan"))
+        st_bh, mode_bh, last = measure(token_by_head)
+        ok = api.check_device_status() == 0
+        per = H // world
+        mine = last[0].view(H, D)[rank * per:(rank + 1) * per].contiguous()
+        rest_untouched = bool(torch.isnan(torch.cat([last[0].view(H, D)[:rank * per],
+                                                     last[0].view(H, D)[(rank + 1) * per:]])).all().item())
+        out_by_head = torch.empty(world, per, D, device=dev)
+        dist.all_gather_into_tensor(out_by_head, mine)
+        by_head = {"ms_per_step": st_bh["median"], "ms_per_step_min": st_bh["min"],
+                   "ms_per_step_max": st_bh["max"], "launch": mode_bh, "status_ok": ok,
+                   "launches_per_step": layers, "heads_per_rank": per,
+                   "other_rows_untouched": rest_untouched,
+                   "note": "every rank holds the output rows of its H / ranks heads only (the input "
+                           "layout of a row-parallel output projection); not the replicated "
+                           "result the other two forms give, so it is reported beside them"}
     # parity: layer 0's cache shards gathered on rank 0, last step against the oracle
     pad = max(sharding.decode_shard_range(capacity, world, r)[1] -
               sharding.decode_shard_range(capacity, world, r)[0] for r in range(world))
@@ -845,17 +875,21 @@ def decode_sharded(torch, dist, api, depth, steps, layers, world, rank, hbm_gbs)
         if out_peer is not None:
             parity["peer_form"] = {"max_abs": O.max_abs(want, out_peer[0].cpu().numpy()),
                                    "rel_l2": O.rel_l2(want, out_peer[0].cpu().numpy())}
+        if out_by_head is not None:
+            got = out_by_head.reshape(-1).cpu().numpy()      # rank order = head order
+            parity["by_head_form"] = {"max_abs": O.max_abs(want, got), "rel_l2": O.rel_l2(want, got)}
     del both
     kv_bytes = sum(layers * 2 * KV * (depth + i + 1) * ROW for i in range(steps)) / steps
     gbs = kv_bytes / (ms_step * 1e-3) / 1e9
     return {"depth": depth, "ranks": world, "partition": "sequence", "launch": mode,
             "exchange": exchange, "ms_per_step_nccl": ms_nccl, "peer_memory_exchange": peer,
+            "peer_memory_exchange_by_head": by_head,
             "symmetric_memory_error": symm_note,
             "ms_per_step": ms_step, "ms_per_step_min": stats["min"], "ms_per_step_max": stats["max"],
             "replays": stats["reps"], "tok_s": 1e3 / ms_step, "kv_bytes_per_step": kv_bytes,
             "kv_gbs": gbs, "frac_hbm_of_all_gpus": gbs / (hbm_gbs * world),
             "exchange_bytes_per_layer_step": world * H * (D + 2) * 4,
-            "parity": parity, "finite": bool(torch.isfinite(out).all().item())}
+            "parity": parity, "finite": finite}
 
 
 WORKLOAD = "prefill T=8192 in 2048-token chunks, q8_0 KV, 24/4/256, 16 layers (BASELINE configs[1])"

@@ -415,7 +415,7 @@ __device__ __forceinline__ void fold_finish(const DecodeParams &p, int *status, 
         }
     }
     if (p.xch.phases & 2) {
-        if (warp < group) {
+        if (warp < group && (!p.xch.by_head || exchange_owner(p.xch, p.n_heads, h) == p.xch.rank)) {
             const unsigned long long deadline = global_timer_ns() + 1000ull * p.xch.wait_us;
             if (exchange_collect_warp(p.xch, p.n_heads, h, e, deadline, lane, f))
                 fold_emit(p, slot, h, f, lane, true);

@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(256) attn_decode_collect(DecodeParams p, int *
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x * 8 + warp;
     if (h >= p.n_heads) return;
+    if (p.xch.by_head && exchange_owner(p.xch, p.n_heads, h) != p.xch.rank) return;
     const int e = *reinterpret_cast<volatile int *>(p.xch.ws[p.xch.rank]);
     const unsigned long long deadline = global_timer_ns() + 1000ull * p.xch.wait_us;
     FoldAcc f;

@@ -144,10 +144,18 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-// One warp stores head h's folded triple, tagged e, into every rank's table.
+// The rank that folds head h when the result is divided by head (x.by_head).
+__device__ __forceinline__ int exchange_owner(const DecodeParams::Exchange &x, int n_heads, int h) {
+    return h / (n_heads / x.shards);
+}
+
+// One warp stores head h's folded triple, tagged e, into every rank's table (by_head: into
+// the table of the rank that owns the head).
 __device__ __forceinline__ void exchange_publish_warp(const DecodeParams::Exchange &x, int n_heads,
                                                       int h, int e, const FoldAcc &f, int lane) {
-    for (int w = 0; w < x.shards; w++) {
+    const int w_lo = x.by_head ? exchange_owner(x, n_heads, h) : 0;
+    const int w_hi = x.by_head ? w_lo + 1 : x.shards;
+    for (int w = w_lo; w < w_hi; w++) {
         unsigned long long *row = cell_row(x.ws[w], e & 1, x.shards, n_heads, x.rank, h);
         unsigned long long *dst = row + lane * 8;
         st_cell2(dst, f.a[0], f.a[1], e);

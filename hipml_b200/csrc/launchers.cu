@@ -138,6 +138,7 @@ struct ExchangeArgs {
     void *const *peer_ws;
     int shards, rank, phases;
     unsigned wait_limit_us;
+    int by_head;
 };
 
 static int decode_kv(hipml_stream_t stream, const int *step, int selector, const float *q,
@@ -223,7 +224,10 @@ static int decode_kv(hipml_stream_t stream, const int *step, int selector, const
             p.xch.rank = xch->rank;
             p.xch.phases = xch->phases;
             p.xch.wait_us = xch->wait_limit_us;
-            if (xch->shards > kInKernelShards && xch->phases == 3) {
+            p.xch.by_head = xch->by_head;
+            // (divided by head a CTA publishes each of its heads once, to its owner: the split
+            // pass does that itself at any rank count)
+            if (xch->shards > kInKernelShards && xch->phases == 3 && !xch->by_head) {
                 // many ranks: the split pass leaves the folded triples in the workspace's staging
                 // rows and a grid of (head, rank) CTAs does the exchange
                 DecodeParams local = p;
@@ -331,9 +335,13 @@ static int shard_exchange(hipml_stream_t stream, const int *step, int selector, 
     if (shards < 1 || shards > 16 || rank < 0 || rank >= shards)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: rank %d of %d shards (1..16)", rank,
                     shards);
+    const int by_head = (phases >> 2) & 1;
+    phases &= ~4;
     if (phases < 1 || phases > 3)
-        return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: phases %d (1 publish, 2 collect, 3 both)",
-                    phases);
+        return fail(HIPML_ERR_INVALID_ARGUMENT,
+                    "exchange: phases %d (1 publish, 2 collect, 3 both; + 4 result divided by head)", phases);
+    if (by_head && (n_heads <= 0 || n_heads % shards != 0))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange by head: %d heads over %d ranks", n_heads, shards);
     if (!peer_ws) return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: no workspace table");
     for (int w = 0; w < shards; w++)
         if (!peer_ws[w] || (reinterpret_cast<size_t>(peer_ws[w]) & 255) != 0)
@@ -341,7 +349,7 @@ static int shard_exchange(hipml_stream_t stream, const int *step, int selector, 
     if (head_dim != 256)
         return fail(HIPML_ERR_INVALID_ARGUMENT, "exchange: head_dim %d, only 256", head_dim);
     if (wait_limit_us > 10000000u) wait_limit_us = 10000000u;
-    ExchangeArgs x = {peer_ws, shards, rank, phases, wait_limit_us};
+    ExchangeArgs x = {peer_ws, shards, rank, phases, wait_limit_us, by_head};
     if (phases == 2) {
         // collect only: no split pass, the partials are not read
         if (int e = check_heads(n_heads, n_kv, head_dim)) return e;
@@ -363,6 +371,7 @@ static int shard_exchange(hipml_stream_t stream, const int *step, int selector, 
         p.xch.rank = rank;
         p.xch.phases = 2;
         p.xch.wait_us = wait_limit_us;
+        p.xch.by_head = by_head;
         return launch_decode_collect(as_stream(stream), p, status);
     }
     if (k_row &&

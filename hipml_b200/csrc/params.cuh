@@ -50,10 +50,14 @@ struct DecodeParams {
     // Sequence-split decode across GPUs: instead of writing `out` directly the folding CTA
     // stores the head group's (acc, max, sum) triples into every rank's table (phase bit 0),
     // and/or waits for all ranks' triples and folds them into `out` (phase bit 1).
+    // by_head: head h's triples go only to rank h / (n_heads / shards), and only that rank
+    // folds them and writes head h's output row (the layout a row-parallel output projection
+    // wants); a rank's other output rows are left alone.
     struct Exchange {
         unsigned char *ws[16];
         int shards = 0, rank = 0, phases = 0;
         unsigned wait_us = 0;
+        int by_head = 0;
     } xch;
 };
 // Live runs of one slot in the tensor-core split pass, in 64-key tiles: `runs` runs deal the

@@ -326,7 +326,12 @@ int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, floa
  * arrived and folds the shards into out f32 [n_heads][head_dim]. head_dim 256, selectors 0, 1,
  * 4. All ranks must make the same sequence of calls. phases: 3 = all of it; 1 = split pass +
  * publish only and 2 = wait + final fold only, a small launch of its own (the two halves, for
- * hosts that drive several ranks from one stream). The wait is bounded in time by
+ * hosts that drive several ranks from one stream). Adding 4 to phases divides the result by
+ * head (n_heads must be a multiple of shards): head h's triples go only to rank
+ * h / (n_heads / shards), which alone folds them and writes row h of `out`; a rank's other rows
+ * of `out` are left as they were. That is the input layout of a row-parallel output
+ * projection, every triple crosses NVLink once instead of `shards` times, and the call stays
+ * one launch at any rank count. The wait is bounded in time by
  * wait_limit_us (capped at 10 s): when it runs out the kernel leaves `out` untouched and
  * hipml_check_device_status reports 31. If a rank misses a call the ranks' call numbers
  * differ for good: zero every rank's workspace (between steps, with a host barrier) to

@@ -253,12 +253,14 @@ def test_sequence_split_shards_fold_to_the_whole_cache(shards, seq):
     assert O.max_abs(mirror.ravel(), out.cpu().numpy()) < 1e-6
 
 
+@pytest.mark.parametrize("by_head", [0, 4], ids=["replicated", "by_head"])
 @pytest.mark.parametrize("shards,seq", [(2, 700), (4, 3000), (8, 5)])
-def test_peer_memory_exchange_on_one_gpu_in_two_phases(shards, seq):
+def test_peer_memory_exchange_on_one_gpu_in_two_phases(shards, seq, by_head):
     """The fused fold + exchange + fold of the multi-GPU decode, with every rank's workspace
     on this one GPU. The two halves run as separate calls in stream order (all ranks publish,
     then all collect), so no kernel ever waits for a later one; three tokens in a row check
-    the epoch counters and the alternating table slots."""
+    the epoch counters and the alternating table slots. by_head: head h's triples go to rank
+    h / (heads / shards) alone, which writes that head's output row and no other."""
     from hipml_b200 import api, sharding
     heads, n_kv, hd, scale = 24, 4, 256, 0.0625
     capacity = seq + 9
@@ -293,10 +295,18 @@ def test_peer_memory_exchange_on_one_gpu_in_two_phases(shards, seq):
                 acc, ml = scratch[r]
                 api.attn_decode_kv_shard_exchange(_step(max(n - 1, 0), n), dq, kc, vc, acc, ml,
                                                   outs[r], heads, n_kv, hd, stride, scale, splits,
-                                                  table, r, phases=phase, wait_limit_us=1000)
+                                                  table, r, phases=phase | by_head, wait_limit_us=1000)
         assert api.check_device_status() == 0
+        per = heads // shards
         for r in range(shards):
-            _assert_close(expected, outs[r].cpu().numpy())
+            got = outs[r].cpu().numpy().reshape(heads, hd)
+            if by_head:
+                own = slice(r * per, (r + 1) * per)
+                _assert_close(expected.reshape(heads, hd)[own].ravel(), got[own].ravel())
+                rest = np.delete(got, np.arange(r * per, (r + 1) * per), axis=0)
+                assert np.all(np.isnan(rest)), "a rank wrote a head it does not own"
+            else:
+                _assert_close(expected, got.ravel())
     # header of every workspace: epoch 3, CTA counter back at 0
     for w in ws:
         hdr = w[:256].view(torch.int32).cpu().numpy()
