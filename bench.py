@@ -1183,8 +1183,8 @@ def reference_main(args):
     # q8_0 cache as the engine holds it; the oracle attends over the dequantised values
     kq = O.dequantize_q8(O.quantize_q8(kf)).reshape(KV, tokens, D).transpose(1, 0, 2).reshape(tokens, W)
     vq = O.dequantize_q8(O.quantize_q8(vf)).reshape(KV, tokens, D).transpose(1, 0, 2).reshape(tokens, W)
-    # 256 rows per step (a second or two on all threads), a whole number of rounds of the threads
-    n_rows = cores * ((256 + cores - 1) // cores)
+    # 1024 rows per step (a few seconds on all threads), a whole number of rounds of the threads
+    n_rows = cores * ((1024 + cores - 1) // cores)
     step = max(tokens // n_rows, 1)
     row0 = step // 2
     rows = np.arange(row0, tokens, step)
