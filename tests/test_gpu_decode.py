@@ -723,9 +723,11 @@ def test_slot_without_rows_gets_a_zero_output_row():
         _assert_close(want, got[s])
 
 
-def test_exchange_in_one_launch_with_a_single_rank():
+@pytest.mark.parametrize("phases", [3, 7], ids=["replicated", "by_head"])
+def test_exchange_in_one_launch_with_a_single_rank(phases):
     """phases = 3 on one rank: the folding CTA publishes to its own table and collects from it
-    inside the split pass (nothing to wait for), with the append fused in."""
+    inside the split pass (nothing to wait for), with the append fused in. phases = 7 divides
+    the result by head, which with one rank is the same thing."""
     from hipml_b200 import api
     heads, n_kv, hd, scale, seq = 24, 4, 256, 0.0625, 1500
     stride = seq + 8
@@ -745,7 +747,7 @@ def test_exchange_in_one_launch_with_a_single_rank():
         rows = (_dev(k_row), _dev(v_row)) if tok == 0 else (None, None)
         api.attn_decode_kv_shard_exchange_append(_step(seq - 1, seq), rows[0], rows[1], _dev(q), dk, dv,
                                                  acc, ml, out, heads, n_kv, hd, stride, scale, splits,
-                                                 [ws.data_ptr()], 0, phases=3, wait_limit_us=1000)
+                                                 [ws.data_ptr()], 0, phases=phases, wait_limit_us=1000)
         assert api.check_device_status() == 0
         kb = dk.cpu().numpy().reshape(n_kv, stride, 272)
         vb = dv.cpu().numpy().reshape(n_kv, stride, 272)

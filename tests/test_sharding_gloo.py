@@ -88,6 +88,83 @@ def test_two_rank_sequence_split_decode_matches_the_oracle(capacity, seq):
     assert O.max_abs(want, out.ravel()) < 2e-6
 
 
+def _prefill_inputs(tokens):
+    rng = O.Rng(0x9F1)
+    q = rng.normals(tokens * HEADS * HD).reshape(tokens, HEADS * HD)
+    k = rng.normals(tokens * N_KV * HD, 0.3).reshape(tokens, N_KV * HD)
+    v = rng.normals(tokens * N_KV * HD).reshape(tokens, N_KV * HD)
+    return q, k, v
+
+
+def chunk_rows_numpy(q, k, v, pos0, off, rows):
+    """numpy stand-in for the chunk attention of query rows [pos0 + off, pos0 + off + rows):
+    row t sees cache rows 0 .. t inclusive (the position is on the query side only)."""
+    group = HEADS // N_KV
+    out = np.zeros((rows, HEADS * HD), dtype=np.float32)
+    for r in range(rows):
+        t = pos0 + off + r
+        for h in range(HEADS):
+            kv = h // group
+            kk = k[:t + 1, kv * HD:(kv + 1) * HD].astype(np.float64)
+            vv = v[:t + 1, kv * HD:(kv + 1) * HD].astype(np.float64)
+            s = kk @ q[t, h * HD:(h + 1) * HD].astype(np.float64) * SCALE
+            w = np.exp(s - s.max())
+            out[r, h * HD:(h + 1) * HD] = (w / w.sum()) @ vv
+    return out
+
+
+def _prefill_worker(rank, world, port, tokens, chunk, by_chunks, result):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    q, k, v = _prefill_inputs(tokens)
+    chunks = [(p, min(chunk, tokens - p)) for p in range(0, tokens, chunk)]
+    mine = np.full((tokens, HEADS * HD), np.nan, dtype=np.float32)
+    work = 0
+    for ci, (p, n) in enumerate(chunks):
+        off, rows = (sharding.chunk_part(ci, len(chunks), n, world, rank) if by_chunks
+                     else sharding.query_part(ci, n, world, rank))
+        if rows > 0:
+            mine[p + off:p + off + rows] = chunk_rows_numpy(q, k, v, p, off, rows)
+            work += rows * (p + off) + rows * (rows + 1) // 2
+    parts = [torch.empty(tokens, HEADS * HD) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(mine))
+    works = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(works, torch.tensor([work]))
+    if rank == 0:
+        result.put((torch.stack(parts).numpy(), [int(w.item()) for w in works]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("tokens,chunk,by_chunks", [(64, 16, True), (75, 16, True), (75, 16, False)],
+                         ids=["4_chunks_in_pairs", "5_chunks_middle_split", "row_halves"])
+def test_two_ranks_that_share_the_kv_heads_cover_the_prefill_once(tokens, chunk, by_chunks):
+    """The 8-GPU prefill partition on two gloo ranks: the ranks that share a KV head divide the
+    chunks in pairs (or every chunk's rows); no exchange. Every output row is produced by
+    exactly one rank, the merged rows equal the oracle's causal attention over the whole job,
+    and the ranks' causal work is balanced."""
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_prefill_worker, args=(r, 2, port, tokens, chunk, by_chunks, result))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    parts, works = result.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    owned = ~np.isnan(parts[:, :, 0])
+    assert np.all(owned.sum(axis=0) == 1), "a row was produced twice or not at all"
+    merged = np.where(np.isnan(parts[0]), parts[1], parts[0])
+    q, k, v = _prefill_inputs(tokens)
+    want = O.attn_chunk_f32(q, k, v, HEADS, N_KV, HD, 0, tokens, SCALE)
+    assert O.max_abs(want.ravel(), merged.ravel()) < 2e-5
+    if tokens % chunk == 0:       # (a ragged last chunk makes its pair lighter at this tiny size)
+        assert max(works) <= 1.06 * sum(works) / 2, works
+
+
 def test_partition_arithmetic():
     # decode ranges tile [0, capacity) in order; each position has exactly one owner
     for cap, world in [(100000, 8), (100136, 4), (7, 8), (672, 2)]:
