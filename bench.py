@@ -514,6 +514,10 @@ def front_end_bench(torch, api, hbm_gbs, tokens=CHUNK, reps=5):
     def gate_pass():
         api.q_gate(q, gate, q, tokens * QW)
 
+    def append_only():
+        # the q8_0 quantise + append of the chunk's K/V rows on its own (kv_encode_bulk)
+        api.kv_encode_bulk(k, v, kc, vc, KV, D, stride, 0, 0, tokens)
+
     def timed(fn):
         best = float("inf")
         for _ in range(reps):
@@ -531,9 +535,13 @@ def front_end_bench(torch, api, hbm_gbs, tokens=CHUNK, reps=5):
     separate()
     same = bool(torch.equal(want_k, kc))
     ms_fused, ms_sep, ms_gate = timed(fused), timed(separate), timed(gate_pass)
+    ms_append = timed(append_only)
     bytes_fused = tokens * (H * 2 * D * 4 + 2 * QW * 4 + 2 * W * 4 + 2 * KV * ROW)
     bytes_gate = tokens * QW * 4 * 3
+    bytes_append = tokens * (2 * W * 4 + 2 * KV * ROW)      # 8,192 B read + 2,176 B written per token
     return {"tokens": tokens, "fused_ms": ms_fused, "separate_launches_ms": ms_sep,
+            "kv_append_bulk_ms": ms_append, "kv_append_bulk_gbs": bytes_append / ms_append / 1e6,
+            "kv_append_bulk_frac_hbm": bytes_append / ms_append / 1e6 / hbm_gbs,
             "fused_gbs": bytes_fused / ms_fused / 1e6, "frac_hbm": bytes_fused / ms_fused / 1e6 / hbm_gbs,
             "gate_pass_ms": ms_gate, "gate_pass_gbs": bytes_gate / ms_gate / 1e6,
             "cache_rows_match_separate_form": same,
