@@ -135,6 +135,15 @@ __device__ __forceinline__ void split_half(float x, __half &hi, __half &lo) {
     hi = __float2half_rn(x);
     lo = __float2half_rn(x - __half2float(hi));
 }
+// The same for two values at once, as packed pairs {a in the low half, b in the high half}:
+// one two-way conversion each way instead of two scalar ones.
+__device__ __forceinline__ void split_half2(float a, float b, unsigned &hi, unsigned &lo) {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 f = __half22float2(h);
+    const __half2 l = __floats2half2_rn(a - f.x, b - f.y);
+    hi = *reinterpret_cast<const unsigned *>(&h);
+    lo = *reinterpret_cast<const unsigned *>(&l);
+}
 
 // Dequantised (or copied) values of 8 consecutive dims of one cache row; zeros past n_keys.
 __device__ __forceinline__ void stage_fetch(const StageParams &p, const void *cache, int kvh,
@@ -314,30 +323,47 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
     // while the grid before its predecessor has not finished): nothing is read before this.
     griddep_wait();
     // Q tile: f32 -> scaled hi/lo f16 in the swizzled K-major image. Row r = query r/group,
-    // head r%group; rows past the live queries are zero.
-    for (int i = tid; i < 128 * (kD / 8); i += kTcThreads) {
-        const int r = i >> 5, seg = i & 31;  // 8 dims per item
-        float x[8];
-        if (r < rows_live) {
-            const int qi = r / p.group, hh = r - qi * p.group;
-            const float4 *src = reinterpret_cast<const float4 *>(
-                p.q + ((size_t)(t0 + qi) * p.n_heads + kvh * p.group + hh) * kD + seg * 8);
-            const float4 a = src[0], b = src[1];
-            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-            x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-        } else {
+    // head r%group; rows past the live queries are zero. An item is 8 dims of a row; a thread's
+    // items are taken in batches whose loads are all issued before the first is converted (one
+    // item at a time the loop cost a memory round trip per item: 9.8 us per CTA, measured).
+    {
+        constexpr int kItems = 128 * (kD / 8);
+        constexpr int kPer = (kItems + kTcThreads - 1) / kTcThreads;
+        constexpr int kBatch = kPer;   // all of a thread's items: one round trip
+#pragma unroll 1
+        for (int b0 = 0; b0 < kPer; b0 += kBatch) {
+            float4 lo4[kBatch], hi4[kBatch];
 #pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = 0.0f;
+            for (int j = 0; j < kBatch; j++) {
+                const int i = tid + (b0 + j) * kTcThreads;
+                const int r = i >> 5, seg = i & 31;
+                lo4[j] = hi4[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (b0 + j < kPer && i < kItems && r < rows_live) {
+                    const int qi = r / p.group, hh = r - qi * p.group;
+                    const float4 *src = reinterpret_cast<const float4 *>(
+                        p.q + ((size_t)(t0 + qi) * p.n_heads + kvh * p.group + hh) * kD + seg * 8);
+                    lo4[j] = __ldg(src);
+                    hi4[j] = __ldg(src + 1);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kBatch; j++) {
+                const int i = tid + (b0 + j) * kTcThreads;
+                if (b0 + j >= kPer || i >= kItems) continue;
+                const int r = i >> 5, seg = i & 31;
+                const float x[8] = {lo4[j].x, lo4[j].y, lo4[j].z, lo4[j].w,
+                                    hi4[j].x, hi4[j].y, hi4[j].z, hi4[j].w};
+                unsigned h[4], l[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    split_half2(x[2 * e] * p.scale_log2, x[2 * e + 1] * p.scale_log2, h[e], l[e]);
+                const int chunk = seg >> 3, col = (seg & 7) * 8;
+                const int off = sw128_offset(r, col);
+                *reinterpret_cast<uint4 *>(q_smem + chunk * kTileBytes + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4 *>(q_smem + (4 + chunk) * kTileBytes + off) =
+                    make_uint4(l[0], l[1], l[2], l[3]);
+            }
         }
-        __half h[8], l[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) split_half(x[j] * p.scale_log2, h[j], l[j]);
-        const int chunk = seg >> 3, col = (seg & 7) * 8;
-        const int off = sw128_offset(r, col);
-        *reinterpret_cast<uint4 *>(q_smem + chunk * kTileBytes + off) =
-            make_uint4(pack2(h[0], h[1]), pack2(h[2], h[3]), pack2(h[4], h[5]), pack2(h[6], h[7]));
-        *reinterpret_cast<uint4 *>(q_smem + (4 + chunk) * kTileBytes + off) =
-            make_uint4(pack2(l[0], l[1]), pack2(l[2], l[3]), pack2(l[4], l[5]), pack2(l[6], l[7]));
     }
     // Make the generic-proxy writes of Q visible to the tensor-core (async) proxy.
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -654,11 +680,7 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                         const float pa = va ? exp2f(__uint_as_float(v[ka]) - m_used) : 0.0f;
                         const float pb = vb ? exp2f(__uint_as_float(v[ka + 1]) - m_used) : 0.0f;
                         l += pa + pb;
-                        __half ha, la, hb, lb;
-                        split_half(pa, ha, la);
-                        split_half(pb, hb, lb);
-                        o[hh * 16 + e] = pack2(ha, hb);
-                        o[hh * 16 + 8 + e] = pack2(la, lb);
+                        split_half2(pa, pb, o[hh * 16 + e], o[hh * 16 + 8 + e]);
                     }
                 }
                 tmem_st32(s_addr + 32 * j, o);
@@ -681,49 +703,94 @@ attn_chunk_tc(const __grid_constant__ CUtensorMap map_k_hi, const __grid_constan
                            peer_abort, p.status, 7);
         }
         ok = __all_sync(0xffffffffu, ok);
+        // O leaves TMEM through shared memory: a thread owns half a row (lane = row), so its own
+        // stores to memory would be 16-byte pieces 1 KB apart (8,192 write transactions per CTA,
+        // 6.3 us measured); staged, whole 1 KB rows leave by bulk copies, which a CTA only has
+        // to see read, not written, before it makes room for the next one (rows that add to a
+        // part already in memory, or take the output gate, are written by the warps instead).
+        // The query tile and the ring are dead by now (every MMA of the pair has completed, every
+        // copy was consumed).
+        const bool bulk_rows = n_tiles <= kFlushTiles && !(norm && p.gate);   // the same in every thread
+        constexpr int kPitch = kD + 4;                       // floats; 16-byte stores of 8 rows hit 8 bank groups
+        float *const stage = reinterpret_cast<float *>(smem);
+        float *const row_scale = stage + 128 * kPitch;        // per row: {weight of the flushed part (< 0: none), 1 / l}
         if (ok) {
             griddep_wait();   // (already satisfied unless the CTA had no key tiles to wait for)
             tc_fence_after();
             const float inv = norm ? (l > 0.0f ? 1.0f / l : 0.0f) : 1.0f;
-            const bool flushed = m_glob != -INFINITY;   // part of O is in memory already
-            const float cg = flushed ? exp2f(m_glob - m_used) : 0.0f;
-            const float *gsrc =
-                (norm && p.gate) ? p.gate + ((size_t)(t0 + rq) * p.n_heads + h) * kD + 128 * half : nullptr;
 #pragma unroll 1
             for (int j = 0; j < 4; j++) {
-                if (n_tiles > 0) tmem_ld32(tmem_o + lane_addr + 128 * half + 32 * j, v);
-                if (live) {
+                if (n_tiles > 0) {
+                    tmem_ld32(tmem_o + lane_addr + 128 * half + 32 * j, v);
+                } else {
 #pragma unroll
-                    for (int e = 0; e < 32; e += 4) {
-                        float4 w = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                        if (n_tiles > 0)
-                            w = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
-                                            __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
-                        if (flushed) {
-                            const float4 g = *reinterpret_cast<const float4 *>(dst + 32 * j + e);
-                            w.x = fmaf(g.x, cg, w.x);
-                            w.y = fmaf(g.y, cg, w.y);
-                            w.z = fmaf(g.z, cg, w.z);
-                            w.w = fmaf(g.w, cg, w.w);
-                        }
-                        w.x *= inv;
-                        w.y *= inv;
-                        w.z *= inv;
-                        w.w *= inv;
-                        if (gsrc) {   // the layer's output gate, applied where the row is produced
-                            const float4 g = *reinterpret_cast<const float4 *>(gsrc + 32 * j + e);
-                            w.x *= 1.0f / (1.0f + expf(-g.x));
-                            w.y *= 1.0f / (1.0f + expf(-g.y));
-                            w.z *= 1.0f / (1.0f + expf(-g.z));
-                            w.w *= 1.0f / (1.0f + expf(-g.w));
-                        }
-                        *reinterpret_cast<float4 *>(dst + 32 * j + e) = w;
-                    }
+                    for (int e = 0; e < 32; e++) v[e] = 0u;
+                }
+                if (live) {
+                    float *at = stage + r * kPitch + 128 * half + 32 * j;
+                    const float pre = bulk_rows ? inv : 1.0f;
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4)
+                        *reinterpret_cast<float4 *>(at + e) =
+                            make_float4(__uint_as_float(v[e]) * pre, __uint_as_float(v[e + 1]) * pre,
+                                        __uint_as_float(v[e + 2]) * pre, __uint_as_float(v[e + 3]) * pre);
                 }
             }
-            if (!norm && live && half == 0) {
-                p.part_ml[slot * 2] = m_used;
-                p.part_ml[slot * 2 + 1] = l;
+            if (bulk_rows) fence_async_shared();   // these rows are read by the bulk copies below
+            if (live && half == 0) {
+                const bool flushed = m_glob != -INFINITY;   // part of O is in memory already
+                row_scale[2 * r] = flushed ? exp2f(m_glob - m_used) : -1.0f;
+                row_scale[2 * r + 1] = inv;
+                if (!norm) {
+                    p.part_ml[slot * 2] = m_used;
+                    p.part_ml[slot * 2 + 1] = l;
+                }
+            }
+        }
+        // (the eight softmax warps; a warp that gave up still arrives, and nothing is written then)
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (*abort_flag == 0 && bulk_rows) {
+            if (lane == 0) {
+                for (int rr = warp; rr < rows_live; rr += 8) {
+                    const int q2 = rr / p.group, h2 = kvh * p.group + (rr - q2 * p.group);
+                    const size_t row = norm ? ((size_t)(t0 + q2) * p.n_heads + h2)
+                                            : (((size_t)sp * p.qslots + (t0 + q2)) * p.n_heads + h2);
+                    bulk_store((norm ? p.out : p.part_acc) + row * kD, smem_u32(stage + rr * kPitch), kD * 4);
+                }
+                bulk_store_commit_wait_read();
+            }
+        } else if (*abort_flag == 0) {
+            for (int rr = warp; rr < rows_live; rr += 8) {
+                const int q2 = rr / p.group, h2 = kvh * p.group + (rr - q2 * p.group);
+                const size_t row = norm ? ((size_t)(t0 + q2) * p.n_heads + h2)
+                                        : (((size_t)sp * p.qslots + (t0 + q2)) * p.n_heads + h2);
+                float *const drow = (norm ? p.out : p.part_acc) + row * kD;
+                const float *const grow = (norm && p.gate) ? p.gate + row * kD : nullptr;
+                const float cg = row_scale[2 * rr], inv = row_scale[2 * rr + 1];
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const int col = 128 * c + 4 * lane;
+                    float4 w = *reinterpret_cast<const float4 *>(stage + rr * kPitch + col);
+                    if (cg >= 0.0f) {
+                        const float4 g = *reinterpret_cast<const float4 *>(drow + col);
+                        w.x = fmaf(g.x, cg, w.x);
+                        w.y = fmaf(g.y, cg, w.y);
+                        w.z = fmaf(g.z, cg, w.z);
+                        w.w = fmaf(g.w, cg, w.w);
+                    }
+                    w.x *= inv;
+                    w.y *= inv;
+                    w.z *= inv;
+                    w.w *= inv;
+                    if (grow) {   // the layer's output gate, applied where the row is produced
+                        const float4 g = *reinterpret_cast<const float4 *>(grow + col);
+                        w.x *= 1.0f / (1.0f + expf(-g.x));
+                        w.y *= 1.0f / (1.0f + expf(-g.y));
+                        w.z *= 1.0f / (1.0f + expf(-g.z));
+                        w.w *= 1.0f / (1.0f + expf(-g.w));
+                    }
+                    *reinterpret_cast<float4 *>(drow + col) = w;
+                }
             }
         }
     }

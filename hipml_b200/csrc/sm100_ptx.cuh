@@ -257,6 +257,18 @@ __device__ __forceinline__ void bulk_load(unsigned dst, const void *src, unsigne
         ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
+// Linear shared -> global copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) in
+// the thread's current bulk group; bulk_store_commit_wait_read ends the group and returns once
+// the shared-memory source has been read (the writes to memory drain on their own and are
+// complete when the grid is).
+__device__ __forceinline__ void bulk_store(void *dst, unsigned src, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit_wait_read() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 // Generic-proxy shared-memory writes -> visible to the async proxy (bulk copies, tensor cores).
 __device__ __forceinline__ void fence_async_shared() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
