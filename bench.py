@@ -168,6 +168,7 @@ class Prefill:
         """Cut every query tile's key range into `splits` slices (partials + combine pass): a
         rank that owns few KV heads has fewer query-tile pairs than the device has SM pairs."""
         self.splits = splits
+        self.splits_by_chunk = None      # optional: slices per chunk position (<= splits)
         if splits >= 2:
             qslots = (max_rows + 31) // 32 * 32
             self.pa = self.torch.empty(splits * qslots * self.qw, device="cuda")
@@ -177,9 +178,14 @@ class Prefill:
     def count_launches(self):
         """Launches of one step: append + staging for every chunk, the attention (and the
         combine pass with key slices) for the chunks this rank attends."""
-        per_attend = 2 if self.splits >= 2 else 1
-        attended = len(self.chunks) if self.q_parts is None else sum(r > 0 for _, r in self.q_parts)
-        self.launches_per_step = self.layers * (2 * len(self.chunks) + per_attend * attended)
+        n = 0
+        for ci in range(len(self.chunks)):
+            if self.q_parts is None or self.q_parts[ci][1] > 0:
+                n += 2 if self.splits_of(ci) >= 2 else 1
+        self.launches_per_step = self.layers * (2 * len(self.chunks) + n)
+
+    def splits_of(self, ci):
+        return self.splits if self.splits_by_chunk is None else self.splits_by_chunk[ci]
 
     def prepare(self, l, ci, ws, k=None, v=None):
         """Append chunk ci of layer l to the q8_0 cache and stage the new rows."""
@@ -201,7 +207,7 @@ class Prefill:
         out = self.out if out is None else out
         self.api.attn_chunk_staged(q[pos0 + off:pos0 + off + rows], out[pos0 + off:pos0 + off + rows],
                                    self.heads, self.n_kv, D, pos0 + off, rows, self.cap, ws, self.pa,
-                                   self.pm, self.splits, mode=mode)
+                                   self.pm, self.splits_of(ci), mode=mode)
 
     def layer(self, l, ws, mode=0, timed=None, out=None, q=None, k=None, v=None):
         for ci in range(len(self.chunks)):
@@ -234,7 +240,7 @@ class Prefill:
                 self.api.attn_chunk(self.q[l][pos0 + off:pos0 + off + rows],
                                     self.kc[l], self.vc[l], self.out[pos0 + off:pos0 + off + rows],
                                     self.heads, self.n_kv, D, pos0 + off, rows, 1, self.stride, self.pa,
-                                    self.pm, self.splits, mode, self.ws)
+                                    self.pm, self.splits_of(ci), mode, self.ws)
 
 
 def run_timed(torch, dist, fn, steps, warmup):
@@ -626,7 +632,7 @@ def decode_batched(torch, api, slots_list, layers, hbm_gbs, steps=32):
 
 
 def prefill_long(torch, api, tokens, heads, n_kv, q_part=None, layers=1, reps=2, key_splits=1,
-                 kv_seed=4):
+                 kv_seed=4, slices_at=None):
     """A `tokens`-token causal prefill in 2048-token chunks over the q8_0 cache (stride
     tokens + 8), timed per layer. The same Q/K/V serve every repetition; (heads, n_kv) are this
     rank's shard; q_part(ci, n) -> (offset, rows) selects the rank's share of a chunk's query
@@ -661,7 +667,8 @@ def prefill_long(torch, api, tokens, heads, n_kv, q_part=None, layers=1, reps=2,
             off, rows = (0, n) if q_part is None else q_part(ci, n)
             if rows > 0:
                 api.attn_chunk_staged(q[pos0 + off:pos0 + off + rows], out[pos0 + off:pos0 + off + rows],
-                                      heads, n_kv, D, pos0 + off, rows, cap, ws, pa, pm, key_splits)
+                                      heads, n_kv, D, pos0 + off, rows, cap, ws, pa, pm,
+                                      key_splits if slices_at is None else min(key_splits, slices_at(pos0)))
 
     layer()
     torch.cuda.synchronize()
@@ -968,6 +975,12 @@ def gpu_main(args):
     key_splits = sharding.prefill_key_splits(CHUNK if by_chunks else CHUNK // q_shards,
                                              heads_local // n_kv_local, n_kv_local)
     pf.use_key_splits(key_splits, CHUNK)
+    if key_splits > 1:
+        # fewer slices where the query tiles see few key tiles (the first chunk)
+        pf.splits_by_chunk = [sharding.prefill_key_splits(CHUNK if by_chunks else CHUNK // q_shards,
+                                                          heads_local // n_kv_local, n_kv_local, pos0=p)
+                              for p, n in pf.chunks]
+        pf.count_launches()
 
     gpu_index = local
     with ClockSampler(gpu_index) as clocks:
@@ -1006,7 +1019,8 @@ def gpu_main(args):
     parallelism = (f"kv_head x{kv_shards}"
                    + (f", query x{q_shards} by {'chunk pairs' if by_chunks else 'rows of every chunk'}"
                       if q_shards > 1 else "")
-                   + (f", key slices x{key_splits} per query tile" if key_splits > 1 else ""))
+                   + (f", key slices x{key_splits} per query tile ({pf.splits_by_chunk} by chunk)"
+                      if key_splits > 1 else ""))
 
     line = {
         "metric": "attn prefill tok/s", "value": tok_s, "unit": "tok/s", "n_gpus": world,
@@ -1147,7 +1161,11 @@ def gpu_main(args):
             part = lambda ci, n: q_part(ci, n, n_long)  # noqa: E731
         long_tokens = 100000
         ms_layer, long_parity = prefill_long(torch, api, long_tokens, heads_local, n_kv_local, part,
-                                             key_splits=key_splits, kv_seed=4 + 1000 * kv_index)
+                                             key_splits=key_splits, kv_seed=4 + 1000 * kv_index,
+                                             slices_at=(lambda p0: sharding.prefill_key_splits(
+                                                 CHUNK if by_chunks else CHUNK // q_shards,
+                                                 heads_local // n_kv_local, n_kv_local, pos0=p0))
+                                             if key_splits > 1 else None)
         ms_layer = rank_max(ms_layer)
         long_parity["max_abs"] = rank_max(long_parity["max_abs"])
         long_parity["rel_l2"] = rank_max(long_parity["rel_l2"])

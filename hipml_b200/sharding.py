@@ -96,14 +96,23 @@ def fold_triples(gathered: np.ndarray) -> np.ndarray:
     return out.astype(np.float32)
 
 
-def prefill_key_splits(chunk_rows: int, group: int, local_n_kv: int, sm_pairs: int = 74) -> int:
+def prefill_key_splits(chunk_rows: int, group: int, local_n_kv: int, sm_pairs: int = 74,
+                       pos0: int | None = None) -> int:
     """Key slices per query tile for a rank's share of a prefill chunk. The tensor-core chunk
     kernel runs one CTA pair per two query tiles of 128 // group queries; a rank that owns
     all 4 KV heads has more pairs than SM pairs and runs unsplit, a rank with fewer pairs cuts
     the key axis so that about two waves of the device are filled (measured on the 2048-token
-    chunk: 1 / 2 / 3 slices are the fastest for 4 / 2 / 1 local KV heads)."""
+    chunk: 1 / 2 / 3 slices are the fastest for 4 / 2 / 1 local KV heads). With the chunk's
+    position given, a slice also keeps at least about four 128-key tiles on average: a CTA
+    pair costs ~13 us besides its 4.4 us per key tile, and the first chunk of a prefill, whose
+    query tiles see 8.5 key tiles on average, is faster in 2 slices than in 3 (66 against 81 us
+    for one KV head, measured)."""
     qtile = max(128 // group, 1)
     pairs = -(-(-(-chunk_rows // qtile)) // 2) * local_n_kv
     if pairs >= 2 * sm_pairs:
         return 1
-    return max(1, min(8, round(2 * sm_pairs / pairs)))
+    fill = max(1, min(8, round(2 * sm_pairs / pairs)))
+    if pos0 is None:
+        return fill
+    mean_tiles = (pos0 + chunk_rows / 2) / 128
+    return max(1, min(fill, int(mean_tiles // 4)))

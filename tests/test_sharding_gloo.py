@@ -227,3 +227,9 @@ def test_prefill_key_split_policy_fills_two_waves():
     assert sharding.prefill_key_splits(1024, 6, 1) == 6
     assert sharding.prefill_key_splits(1, 6, 1) == 8          # capped
     assert sharding.prefill_key_splits(100000, 6, 4) == 1
+    # with the position: a slice keeps about four key tiles on average, so the first chunk of a
+    # one-head rank takes 2 slices where the later ones take 3
+    assert [sharding.prefill_key_splits(2048, 6, 1, pos0=p) for p in (0, 2048, 6144, 98304)] == [2, 3, 3, 3]
+    assert [sharding.prefill_key_splits(2048, 6, 2, pos0=p) for p in (0, 2048)] == [2, 2]
+    assert sharding.prefill_key_splits(2048, 6, 4, pos0=0) == 1
+    assert sharding.prefill_key_splits(64, 6, 1, pos0=0) == 1
