@@ -660,15 +660,18 @@ def prefill_long(torch, api, tokens, heads, n_kv, q_part=None, layers=1, reps=2,
         pa = torch.empty(key_splits * qslots * qw, device=dev)
         pm = torch.empty(key_splits * qslots * heads * 2, device=dev)
 
+    # (the policy is evaluated once, outside the timed loop: it is host arithmetic)
+    slices = [key_splits if slices_at is None else min(key_splits, slices_at(p)) for p, _ in chunks]
+    parts = [(0, n) if q_part is None else q_part(ci, n) for ci, (_, n) in enumerate(chunks)]
+
     def layer():
         for ci, (pos0, n) in enumerate(chunks):
             api.kv_encode_bulk(k[pos0:pos0 + n], v[pos0:pos0 + n], kc, vc, n_kv, D, stride, pos0, 0, n)
             api.attn_chunk_stage(kc, vc, n_kv, D, 1, stride, pos0, pos0 + n, cap, ws)
-            off, rows = (0, n) if q_part is None else q_part(ci, n)
+            off, rows = parts[ci]
             if rows > 0:
                 api.attn_chunk_staged(q[pos0 + off:pos0 + off + rows], out[pos0 + off:pos0 + off + rows],
-                                      heads, n_kv, D, pos0 + off, rows, cap, ws, pa, pm,
-                                      key_splits if slices_at is None else min(key_splits, slices_at(pos0)))
+                                      heads, n_kv, D, pos0 + off, rows, cap, ws, pa, pm, slices[ci])
 
     layer()
     torch.cuda.synchronize()
@@ -972,15 +975,17 @@ def gpu_main(args):
 
     if q_shards > 1:
         pf.q_parts = [q_part(ci, n, len(pf.chunks)) for ci, (p, n) in enumerate(pf.chunks)]
-    key_splits = sharding.prefill_key_splits(CHUNK if by_chunks else CHUNK // q_shards,
-                                             heads_local // n_kv_local, n_kv_local)
+    # key slices per query tile, by chunk position (the cost model of sharding.py: fewer where the
+    # query tiles see few key tiles, more where a rank has few tiles or the tiles are very long)
+    def slices_at(p0):
+        return sharding.prefill_key_splits(CHUNK if by_chunks else CHUNK // q_shards,
+                                           heads_local // n_kv_local, n_kv_local, pos0=p0)
+
+    by_chunk_splits = [slices_at(p) for p, n in pf.chunks]
+    key_splits = max(by_chunk_splits)
     pf.use_key_splits(key_splits, CHUNK)
-    if key_splits > 1:
-        # fewer slices where the query tiles see few key tiles (the first chunk)
-        pf.splits_by_chunk = [sharding.prefill_key_splits(CHUNK if by_chunks else CHUNK // q_shards,
-                                                          heads_local // n_kv_local, n_kv_local, pos0=p)
-                              for p, n in pf.chunks]
-        pf.count_launches()
+    pf.splits_by_chunk = by_chunk_splits
+    pf.count_launches()
 
     gpu_index = local
     with ClockSampler(gpu_index) as clocks:
@@ -1019,8 +1024,7 @@ def gpu_main(args):
     parallelism = (f"kv_head x{kv_shards}"
                    + (f", query x{q_shards} by {'chunk pairs' if by_chunks else 'rows of every chunk'}"
                       if q_shards > 1 else "")
-                   + (f", key slices x{key_splits} per query tile ({pf.splits_by_chunk} by chunk)"
-                      if key_splits > 1 else ""))
+                   + (f", key slices {pf.splits_by_chunk} by chunk" if key_splits > 1 else ""))
 
     line = {
         "metric": "attn prefill tok/s", "value": tok_s, "unit": "tok/s", "n_gpus": world,
@@ -1160,12 +1164,10 @@ def gpu_main(args):
             n_long = (100000 + CHUNK - 1) // CHUNK
             part = lambda ci, n: q_part(ci, n, n_long)  # noqa: E731
         long_tokens = 100000
+        long_splits = [slices_at(p0) for p0 in range(0, long_tokens, CHUNK)]
         ms_layer, long_parity = prefill_long(torch, api, long_tokens, heads_local, n_kv_local, part,
-                                             key_splits=key_splits, kv_seed=4 + 1000 * kv_index,
-                                             slices_at=(lambda p0: sharding.prefill_key_splits(
-                                                 CHUNK if by_chunks else CHUNK // q_shards,
-                                                 heads_local // n_kv_local, n_kv_local, pos0=p0))
-                                             if key_splits > 1 else None)
+                                             key_splits=max(long_splits), kv_seed=4 + 1000 * kv_index,
+                                             slices_at=slices_at)
         ms_layer = rank_max(ms_layer)
         long_parity["max_abs"] = rank_max(long_parity["max_abs"])
         long_parity["rel_l2"] = rank_max(long_parity["rel_l2"])
@@ -1173,6 +1175,7 @@ def gpu_main(args):
         flop_layer = attn_flops(chunk_pairs(0, long_tokens))
         line["long_context_prefill"] = {
             "tokens": long_tokens, "chunk": CHUNK, "layers_timed": 1, "ms_per_layer": ms_layer,
+            "key_slices_by_chunk": "".join(str(x) for x in long_splits),
             "tok_s_16_layers": long_tokens / (LAYERS * ms_layer * 1e-3),
             "algorithmic_tflops_all_gpus": flop_layer / (ms_layer * 1e-3) / 1e12,
             "frac_of_peak_all_gpus": flop_layer / (ms_layer * 1e-3) / 1e12 / (pk["tflops"] * world),

@@ -96,6 +96,35 @@ def fold_triples(gathered: np.ndarray) -> np.ndarray:
     return out.astype(np.float32)
 
 
+# Cost model of one launch of the tensor-core chunk kernel (B200, measured with a per-CTA time
+# line): a CTA pair spends ~13 us outside its key-tile loop and 4.4 us per 128-key tile in it;
+# slicing the key axis adds a combine pass, the partials' round trip and a launch (~30 us).
+PAIR_FIXED_US, PAIR_STEP_US, SLICED_EXTRA_US = 13.0, 4.4, 30.0
+
+
+def chunk_launch_estimate_us(chunk_rows: int, group: int, local_n_kv: int, pos0: int, slices: int,
+                             sm_pairs: int = 74) -> float:
+    """Estimated duration of the chunk attention of `chunk_rows` query rows at position `pos0`
+    with `slices` key slices per query tile, for a rank that owns `local_n_kv` KV heads: the
+    jobs (one per pair of query tiles, KV head and slice) are dealt to the device's SM pairs
+    longest first, as the launch order does."""
+    qtile = max(128 // group, 1)
+    tiles = -(-chunk_rows // qtile)
+    jobs = []
+    for pair in range(-(-tiles // 2)):
+        last_query = min((2 * pair + 2) * qtile, chunk_rows)
+        key_tiles = -(-(pos0 + last_query) // 128)
+        for sl in range(slices):
+            lo, hi = key_tiles * sl // slices, key_tiles * (sl + 1) // slices
+            jobs.append(PAIR_FIXED_US + PAIR_STEP_US * (hi - lo))
+    jobs = sorted(jobs * local_n_kv, reverse=True)
+    slots = [0.0] * sm_pairs
+    for job in jobs:
+        k = min(range(sm_pairs), key=slots.__getitem__)
+        slots[k] += job
+    return max(slots) + (SLICED_EXTRA_US if slices > 1 else 0.0)
+
+
 def prefill_key_splits(chunk_rows: int, group: int, local_n_kv: int, sm_pairs: int = 74,
                        pos0: int | None = None) -> int:
     """Key slices per query tile for a rank's share of a prefill chunk. The tensor-core chunk
@@ -103,16 +132,22 @@ def prefill_key_splits(chunk_rows: int, group: int, local_n_kv: int, sm_pairs: i
     all 4 KV heads has more pairs than SM pairs and runs unsplit, a rank with fewer pairs cuts
     the key axis so that about two waves of the device are filled (measured on the 2048-token
     chunk: 1 / 2 / 3 slices are the fastest for 4 / 2 / 1 local KV heads). With the chunk's
-    position given, a slice also keeps at least about four 128-key tiles on average: a CTA
-    pair costs ~13 us besides its 4.4 us per key tile, and the first chunk of a prefill, whose
-    query tiles see 8.5 key tiles on average, is faster in 2 slices than in 3 (66 against 81 us
-    for one KV head, measured)."""
+    position given the count comes from the cost model above instead: the first chunk of a
+    prefill, whose query tiles see 1 - 16 key tiles, wants fewer slices than the later ones
+    (measured, 2048 rows: one KV head 2 / 3 / 3 / 3 slices at positions 0 / 2048 / 4096 / 6144,
+    two KV heads 1 / 1 / 2 - 3 / 3, four KV heads always 1; the model picks the same)."""
     qtile = max(128 // group, 1)
     pairs = -(-(-(-chunk_rows // qtile)) // 2) * local_n_kv
-    if pairs >= 2 * sm_pairs:
-        return 1
-    fill = max(1, min(8, round(2 * sm_pairs / pairs)))
-    if pos0 is None:
-        return fill
-    mean_tiles = (pos0 + chunk_rows / 2) / 128
-    return max(1, min(fill, int(mean_tiles // 4)))
+    # (past 8,192 visible keys a query tile moves its accumulators to memory every 64 key tiles,
+    # which the model does not price: three slices of a 100,000-token prefill on a rank with all
+    # four KV heads took 499 ms per layer against 300 ms unsliced; the fill rule stays there)
+    if pos0 is None or pos0 + chunk_rows > 8192:
+        if pairs >= 2 * sm_pairs:
+            return 1
+        return max(1, min(8, round(2 * sm_pairs / pairs)))
+    best, best_us = 1, None
+    for slices in range(1, 9):
+        us = chunk_launch_estimate_us(chunk_rows, group, local_n_kv, pos0, slices, sm_pairs)
+        if best_us is None or us < best_us - 1e-9:
+            best, best_us = slices, us
+    return best

@@ -227,9 +227,10 @@ def test_prefill_key_split_policy_fills_two_waves():
     assert sharding.prefill_key_splits(1024, 6, 1) == 6
     assert sharding.prefill_key_splits(1, 6, 1) == 8          # capped
     assert sharding.prefill_key_splits(100000, 6, 4) == 1
-    # with the position: a slice keeps about four key tiles on average, so the first chunk of a
-    # one-head rank takes 2 slices where the later ones take 3
-    assert [sharding.prefill_key_splits(2048, 6, 1, pos0=p) for p in (0, 2048, 6144, 98304)] == [2, 3, 3, 3]
-    assert [sharding.prefill_key_splits(2048, 6, 2, pos0=p) for p in (0, 2048)] == [2, 2]
-    assert sharding.prefill_key_splits(2048, 6, 4, pos0=0) == 1
+    # with the position the count comes from the launch cost model: the measured optima
+    assert [sharding.prefill_key_splits(2048, 6, 1, pos0=p) for p in (0, 2048, 4096, 6144)] == [2, 3, 3, 3]
+    assert [sharding.prefill_key_splits(2048, 6, 2, pos0=p) for p in (0, 2048, 6144)] == [1, 1, 3]
+    assert [sharding.prefill_key_splits(2048, 6, 4, pos0=p) for p in (0, 2048, 4096, 6144)] == [1, 1, 1, 1]
     assert sharding.prefill_key_splits(64, 6, 1, pos0=0) == 1
+    # the estimate itself: unsliced, four KV heads, first chunk (measured 154 us)
+    assert 130 < sharding.chunk_launch_estimate_us(2048, 6, 4, 0, 1) < 170
