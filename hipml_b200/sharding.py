@@ -135,18 +135,19 @@ def prefill_key_splits(chunk_rows: int, group: int, local_n_kv: int, sm_pairs: i
     position given the count comes from the cost model above instead: the first chunk of a
     prefill, whose query tiles see 1 - 16 key tiles, wants fewer slices than the later ones
     (measured, 2048 rows: one KV head 2 / 3 / 3 / 3 slices at positions 0 / 2048 / 4096 / 6144,
-    two KV heads 1 / 1 / 2 - 3 / 3, four KV heads always 1; the model picks the same)."""
+    two KV heads 1 / 1 / 2 - 3 / 3, four KV heads 1 up to 8,192 keys; the model picks the same)."""
     qtile = max(128 // group, 1)
     pairs = -(-(-(-chunk_rows // qtile)) // 2) * local_n_kv
-    # (past 8,192 visible keys a query tile moves its accumulators to memory every 64 key tiles,
-    # which the model does not price: three slices of a 100,000-token prefill on a rank with all
-    # four KV heads took 499 ms per layer against 300 ms unsliced; the fill rule stays there)
-    if pos0 is None or pos0 + chunk_rows > 8192:
+    if pos0 is None:
         if pairs >= 2 * sm_pairs:
             return 1
         return max(1, min(8, round(2 * sm_pairs / pairs)))
+    # (deep chunks: the jobs are long and alike, so what matters is that jobs / SM pairs comes
+    # out just under a whole number - 196, 98 or 49 pairs x 3 slices = 7.9, 4.0, 2.0 rounds;
+    # measured on the 100,000-token prefill: 302 -> 289 ms per layer with all four KV heads,
+    # 150 -> 142 ms with two, 3 the best of 2 .. 8 with one)
     best, best_us = 1, None
-    for slices in range(1, 9):
+    for slices in range(1, 7):
         us = chunk_launch_estimate_us(chunk_rows, group, local_n_kv, pos0, slices, sm_pairs)
         if best_us is None or us < best_us - 1e-9:
             best, best_us = slices, us
