@@ -708,6 +708,8 @@ static int chunk_staged(hipml_stream_t stream, const float *q, float *out, int n
     if (tokens == 0) return 0;
     if (splits >= 2 && (!part_acc || !part_ml))
         return fail(HIPML_ERR_INVALID_ARGUMENT, "split attention needs part_acc and part_ml");
+    if (splits >= 2 && ((reinterpret_cast<size_t>(part_acc) & 15) != 0 || (reinterpret_cast<size_t>(part_ml) & 7) != 0))
+        return fail(HIPML_ERR_INVALID_ARGUMENT, "split attention: part_acc must be 16-byte, part_ml 8-byte aligned");
     const size_t need = chunk_tc_workspace_bytes(n_kv, key_capacity);
     if (!workspace || workspace_bytes < need)
         return fail(HIPML_ERR_WORKSPACE, "chunk attention workspace: %zu bytes given, %zu needed",
