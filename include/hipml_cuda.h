@@ -413,7 +413,9 @@ size_t hipml_attn_chunk_workspace_bytes(int n_kv, int head_dim, int pos0, int to
  * tolerance), 1 = tensor-core kernel, single half-precision pass (the reference kernel's own
  * precision), 2 = scalar f32 kernel (any head_dim multiple of 32 up to 256; no workspace),
  * 3 = as 0 but one CTA per query tile instead of CTA pairs (A/B form of the same arithmetic).
- * workspace: device memory of at least hipml_attn_chunk_workspace_bytes(...) for modes 0/1/3. */
+ * workspace: device memory of at least hipml_attn_chunk_workspace_bytes(...) for modes 0/1/3,
+ * 256-byte aligned. The tensor-core modes want q, out, the caches and part_acc 16-byte aligned
+ * and part_ml 8-byte aligned (rows leave the kernel as whole 1 KB bulk copies). */
 int hipml_attn_chunk(hipml_stream_t stream, const float *q, const void *k_cache,
                      const void *v_cache, float *out, int n_heads, int n_kv, int head_dim,
                      int pos0, int tokens, int kv_dtype, int stride, float *part_acc,
