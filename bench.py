@@ -4,7 +4,7 @@ python bench.py --gpus N --steps K --warmup W            this library on N B200s
 python bench.py --impl reference --gpus N ...            the reference's CPU attention
                                                          (oracle port) on the host cores
 
-Workload: BASELINE configs[1] -- prefill of T=8192 tokens in 2048-token chunks against
+Workload (the 8K-context prefill of the reference's bench grid): T=8192 tokens in 2048-token chunks against
 the growing q8_0 cache, 24 query / 4 KV heads, head_dim 256, 16 layers with independent
 seeds. One step = all 16 layers: per chunk kv_encode_bulk (quantise + append), stage the new
 rows, tensor-core chunk attention. `value` = tokens/s with Q/K/V resident in HBM; `e2e` =
