@@ -268,7 +268,7 @@ def run_timed(torch, dist, fn, steps, warmup):
     return ms
 
 
-def prefill_e2e(torch, api, L, pf: Prefill, steps, warmup):
+def prefill_e2e(torch, api, L, pf: Prefill, steps, warmup, check=None):
     """The same step through the C ABI with HOST buffers: per layer, Q/K/V go host->device
     from pinned memory and the output comes back, inside the timed region. Three streams
     take the layers in turn, so the host->device engine never waits: with two, the upload of
@@ -329,13 +329,23 @@ def prefill_e2e(torch, api, L, pf: Prefill, steps, warmup):
             main.wait_stream(s)
 
     ms = run_timed(torch, None, run, steps, warmup)
+    parity = None
+    if check is not None:
+        # layer 0's output rows as they arrived in HOST memory, against the oracle rows
+        import numpy as np
+
+        import oracle as O
+        idx, want = check
+        rows = np.ctypeslib.as_array(C.cast(host[0][3], C.POINTER(C.c_float)), shape=(pf.tokens, pf.qw))
+        got = np.array(rows[idx])
+        parity = {"rows": int(len(idx)), "max_abs": O.max_abs(want, got), "rel_l2": O.rel_l2(want, got)}
     for ptrs in host:
         for p in ptrs:
             lib.hipml_host_free(p)
     q_bytes = sum(n for _, n in q_ranges)
     h2d = pf.layers * (q_bytes + 2 * nbytes_kv)
     d2h = pf.layers * q_bytes
-    return ms, h2d, d2h
+    return ms, h2d, d2h, parity
 
 
 def sampled_rows(pf: Prefill, per_chunk=6):
@@ -1107,11 +1117,15 @@ def gpu_main(args):
             "algorithmic_tflops": r1["achieved"], "issued_tflops": r1["achieved"],
             "frac_of_peak": r1["frac"], "ms_per_step": ms_mode1}}
 
-    e2e_ms, h2d, d2h = prefill_e2e(torch, api, L, pf, max(args.steps // 2, 1), 1)
+    e2e_ms, h2d, d2h, e2e_parity = prefill_e2e(torch, api, L, pf, max(args.steps // 2, 1), 1,
+                                               check=(idx, want))
     e2e_ms = rank_max(e2e_ms)
+    e2e_parity["max_abs"] = rank_max(e2e_parity["max_abs"])
+    e2e_parity["rel_l2"] = rank_max(e2e_parity["rel_l2"])
     line["e2e"] = {"value": T_PREFILL / (e2e_ms * 1e-3), "unit": "tok/s",
                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
                    "d2h_bytes_per_step": d2h * world,
+                   "parity_of_host_output": e2e_parity,
                    "note": "per rank: the Q rows it attends and its heads' K/V up from pinned host "
                            "memory, its output rows down, inside the timed region; bytes are the "
                            "sum over ranks"}
