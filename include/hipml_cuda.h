@@ -319,12 +319,14 @@ int hipml_attn_decode_combine(hipml_stream_t stream, const float *gathered, floa
  * workspace of hipml_decode_exchange_bytes(...) bytes, 256-byte aligned, zero-filled once
  * before the first call, that every other rank has mapped (peer access, IPC handle or
  * symmetric memory); peer_ws is a HOST array of `shards` device pointers, peer_ws[w] = rank w's
- * workspace as mapped in this process, peer_ws[rank] = the local one. One call = ONE launch:
- * the split pass over the local rows, whose last CTA per KV head folds the local partials,
- * stores the folded triples into every rank's workspace (each value tagged with the call's
- * number in the same 64-bit store), waits until every rank's values of the same call have
- * arrived and folds the shards into out f32 [n_heads][head_dim]. head_dim 256, selectors 0, 1,
- * 4. All ranks must make the same sequence of calls. phases: 3 = all of it; 1 = split pass +
+ * workspace as mapped in this process, peer_ws[rank] = the local one. One call: the split
+ * pass over the local rows, whose last CTA per KV head folds the local partials, stores the
+ * folded triples into every rank's workspace (each value tagged with the call's number in the
+ * same 64-bit store), waits until every rank's values of the same call have arrived and folds
+ * the shards into out f32 [n_heads][head_dim] - ONE launch up to 2 ranks; with more, the
+ * split pass leaves its triples in the workspace's staging rows and a second launch of
+ * (head, rank) CTAs does the stores and the collect (one SM cannot feed NVLink for many
+ * peers). head_dim 256, selectors 0, 1, 4. All ranks must make the same sequence of calls. phases: 3 = all of it; 1 = split pass +
  * publish only and 2 = wait + final fold only, a small launch of its own (the two halves, for
  * hosts that drive several ranks from one stream). Adding 4 to phases divides the result by
  * head (n_heads must be a multiple of shards): head h's triples go only to rank
